@@ -1,0 +1,85 @@
+// Host-side helpers shared by the kernels: error codes, driver entry point for tensor-map
+// encoding (resolved at run time so the library loads on machines without a driver), and
+// tensor-map builders for 128-byte-swizzled tiles.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+namespace tp {
+
+enum ErrorCode : int {
+  kOk = 0,
+  kErrBadArgument = -1,
+  kErrDriver = -2,
+  kErrLaunch = -3,
+  kErrTooLarge = -4,
+  // device-side wait time-outs (written to the caller's error word)
+  kErrWaitProducer = 101,
+  kErrWaitMma = 102,
+  kErrWaitEpilogue = 103,
+  kErrWaitTmemEmpty = 104,
+  kErrWaitPeer = 105,
+  kErrWaitAttn = 106,
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+inline EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) ==
+            cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 16-bit elements, 128B swizzle.  dims/strides innermost first; strides[i] is the byte stride
+// of dimension i+1.  Returns false on failure.
+inline bool make_tmap_16b(CUtensorMap* out, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box, bool bf16) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint32_t estr[5] = {1, 1, 1, 1, 1};
+  CUresult r = fn(out, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16,
+                  rank, const_cast<void*>(base), reinterpret_cast<const cuuint64_t*>(dims),
+                  reinterpret_cast<const cuuint64_t*>(strides_bytes), box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "terapipe_b200: cuTensorMapEncodeTiled failed (%d) rank=%d dims=%llu,%llu box=%u,%u stride=%llu base=%p\n",
+            (int)r, rank, (unsigned long long)dims[0], (unsigned long long)dims[1], box[0], box[1],
+            (unsigned long long)strides_bytes[0], base);
+    return false;
+  }
+  return true;
+}
+
+inline bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uint64_t outer,
+                         uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer, bool bf16) {
+  uint64_t dims[2] = {inner, outer};
+  uint64_t strides[1] = {ld_elems * 2};
+  uint32_t box[2] = {box_inner, box_outer};
+  return make_tmap_16b(out, base, 2, dims, strides, box, bf16);
+}
+
+inline int num_sms() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+}  // namespace tp

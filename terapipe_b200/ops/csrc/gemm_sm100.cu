@@ -1,0 +1,383 @@
+// Persistent warp-specialised GEMM for sm_100a: TMA -> shared-memory ring -> tcgen05.mma
+// with fp32 accumulators in TMEM (double buffered) -> fused epilogue.
+//
+//   out[m][n] = epilogue( alpha * sum_k A(m,k) * B(n,k) )
+//
+// Operand storage (16-bit elements, fp16 or bf16):
+//   a_mn = 0: A is [M][K] row-major (K contiguous);  a_mn = 1: A is stored [K][M] (M contiguous)
+//   b_mn = 0: B is [N][K] row-major (a Linear weight); b_mn = 1: B is stored [K][N]
+// which covers forward (0,0), data-gradient (0,1) and weight-gradient (1,1) products of a
+// Linear layer without any transposed copies.
+//
+// Epilogue (all optional): + bias[n]; activation (ReLU / exact GeLU, optionally storing the
+// pre-activation); + residual[m][n]; multiplication by the activation derivative evaluated
+// on an auxiliary tensor (backward of the FFN nonlinearity); 16-bit or fp32 output; fp32
+// output may accumulate (out += ...), which is how weight gradients of successive token
+// slices add up in the main-gradient buffer.
+//
+// One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
+// warps 2..5 = epilogue (one TMEM lane quarter each).
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace tp {
+
+struct GemmParams {
+  int M, N, K;
+  int num_m_tiles, num_tiles;
+  void* out;
+  long long ldo;
+  const void* bias;
+  const void* residual;
+  long long ldr;
+  void* aux_out;
+  const void* aux_in;
+  long long ld_aux;
+  float alpha;
+  int act;         // 0 none, 1 relu, 2 gelu
+  int dact;        // 0 none, 1 relu' (aux_in = activation output), 2 gelu' (aux_in = pre-activation)
+  int accumulate;  // fp32 output only
+  int* err;
+};
+
+constexpr int kBM = 128;
+constexpr int kBK = 64;
+constexpr int kGemmThreads = 192;
+
+template <int BN> struct GemmCfg {
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = BN == 64 ? 128 : 2 * BN;  // two accumulators, power of two
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+__device__ __forceinline__ float gelu_f(float z) {
+  return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
+}
+__device__ __forceinline__ float gelu_grad_f(float z) {
+  const float cdf = 0.5f * (1.0f + erff(z * 0.70710678118654752f));
+  const float pdf = 0.3989422804014327f * __expf(-0.5f * z * z);
+  return cdf + z * pdf;
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+            const GemmParams p) {
+  using Cfg = GemmCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + S;
+  uint64_t* tfull = bars + 2 * S;
+  uint64_t* tempty = bars + 2 * S + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const WaitCtx wctx{abort_flag, p.err};
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 4);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        const int m0 = (tile % p.num_m_tiles) * kBM;
+        const int n0 = (tile / p.num_m_tiles) * BN;
+        bool ok = true;
+        for (int kb = 0; kb < num_kb && ok; ++kb) {
+          ok = mbar_wait(&empty[stage], phase ^ 1, wctx, kErrWaitProducer);
+          if (!ok) break;
+          uint8_t* sA = smem + stage * Cfg::kStageBytes;
+          uint8_t* sB = sA + Cfg::kABytes;
+          mbar_expect_tx(&full[stage], Cfg::kStageBytes);
+          if (!A_MN) {
+            tma_load_2d(sA, &tmA, &full[stage], kb * kBK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              tma_load_2d(sA + c * (kBK * 128), &tmA, &full[stage], m0 + c * 64, kb * kBK);
+          }
+          if (!B_MN) {
+            tma_load_2d(sB, &tmB, &full[stage], kb * kBK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < BN / 64; ++c)
+              tma_load_2d(sB + c * (kBK * 128), &tmB, &full[stage], n0 + c * 64, kb * kBK);
+          }
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_f16(Elem<T>::fmt, A_MN ? 1 : 0, B_MN ? 1 : 0, kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(&tempty[acc], acc_phase ^ 1, wctx, kErrWaitTmemEmpty);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full[stage], phase, wctx, kErrWaitMma);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_base = a_base + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = A_MN ? umma_desc_sw128(a_base + k * 2048, kBK * 128, 1024)
+                                     : umma_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(b_base + k * 2048, kBK * 128, 1024)
+                                     : umma_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % p.num_m_tiles) * kBM;
+      const int n0 = (tile / p.num_m_tiles) * BN;
+      ok = mbar_wait(&tfull[acc], acc_phase, wctx, kErrWaitEpilogue);
+      if (!ok) break;
+      tc_fence_after();
+      const long long row = m0 + row_in_tile;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c0, r);
+        tmem_ld_wait();
+        const int n = n0 + c0;
+        if (!row_ok || n >= p.N) continue;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {  // groups of 8 columns
+          const int ng = n + g * 8;
+          if (ng + 8 > p.N) break;
+          float v[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+          if (p.bias) {
+            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + ng));
+            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = Elem<T>::unpack2(bw[j]);
+              v[2 * j] += f.x;
+              v[2 * j + 1] += f.y;
+            }
+          }
+          if (p.act == 2) {
+            if (p.aux_out) {
+              uint4 zv;
+              zv.x = Elem<T>::pack2(v[0], v[1]);
+              zv.y = Elem<T>::pack2(v[2], v[3]);
+              zv.z = Elem<T>::pack2(v[4], v[5]);
+              zv.w = Elem<T>::pack2(v[6], v[7]);
+              *reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + ng) = zv;
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j]);
+          } else if (p.act == 1) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
+          }
+          if (p.residual) {
+            const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) +
+                                                             row * p.ldr + ng);
+            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = Elem<T>::unpack2(rw[j]);
+              v[2 * j] += f.x;
+              v[2 * j + 1] += f.y;
+            }
+          }
+          if (p.dact) {
+            const uint4 av = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) +
+                                                             row * p.ld_aux + ng);
+            const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 f = Elem<T>::unpack2(aw[j]);
+              if (p.dact == 1) {
+                v[2 * j] = f.x > 0.0f ? v[2 * j] : 0.0f;
+                v[2 * j + 1] = f.y > 0.0f ? v[2 * j + 1] : 0.0f;
+              } else {
+                v[2 * j] *= gelu_grad_f(f.x);
+                v[2 * j + 1] *= gelu_grad_f(f.y);
+              }
+            }
+          }
+          if (OUT_F32) {
+            float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + row * p.ldo + ng);
+            float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
+            float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
+            if (p.accumulate) {
+              const float4 c0v = o[0], c1v = o[1];
+              o0.x += c0v.x; o0.y += c0v.y; o0.z += c0v.z; o0.w += c0v.w;
+              o1.x += c1v.x; o1.y += c1v.y; o1.z += c1v.z; o1.w += c1v.w;
+            }
+            o[0] = o0;
+            o[1] = o1;
+          } else {
+            uint4 ov;
+            ov.x = Elem<T>::pack2(v[0], v[1]);
+            ov.y = Elem<T>::pack2(v[2], v[3]);
+            ov.z = Elem<T>::pack2(v[4], v[5]);
+            ov.w = Elem<T>::pack2(v[6], v[7]);
+            *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.ldo + ng) = ov;
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+    }
+  }
+
+  // teardown: on an aborted run give in-flight bulk copies time to land before the CTA's
+  // shared memory is released, then free TMEM.
+  __syncthreads();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                       cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
+        cudaSuccess)
+      return kErrLaunch;
+    configured = true;
+  }
+  int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+template <typename T, int BN>
+static int dispatch_layout(int a_mn, int b_mn, int out_f32, const CUtensorMap& tmA,
+                           const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
+  if (!a_mn && !b_mn && !out_f32) return launch_gemm<T, BN, false, false, false>(tmA, tmB, p, s);
+  if (!a_mn && b_mn && !out_f32) return launch_gemm<T, BN, false, true, false>(tmA, tmB, p, s);
+  if (a_mn && b_mn && out_f32) return launch_gemm<T, BN, true, true, true>(tmA, tmB, p, s);
+  if (!a_mn && !b_mn && out_f32) return launch_gemm<T, BN, false, false, true>(tmA, tmB, p, s);
+  if (a_mn && b_mn && !out_f32) return launch_gemm<T, BN, true, true, false>(tmA, tmB, p, s);
+  return kErrBadArgument;
+}
+
+static int pick_bn(int M, int N, int forced) {
+  if (forced == 64 || forced == 128 || forced == 256) return forced;
+  const int sms = num_sms();
+  const int mt = (M + kBM - 1) / kBM;
+  const int cand[3] = {256, 128, 64};
+  const float cost[3] = {2.0f, 1.1f, 0.7f};
+  int best = 128;
+  float best_t = 1e30f;
+  for (int i = 0; i < 3; ++i) {
+    const int tiles = mt * ((N + cand[i] - 1) / cand[i]);
+    const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
+    if (t < best_t) { best_t = t; best = cand[i]; }
+  }
+  return best;
+}
+
+}  // namespace tp
+
+extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const void* B,
+                       long long ldb, void* out, long long ldo, int out_f32, int accumulate, int M,
+                       int N, int K, float alpha, const void* bias, const void* residual,
+                       long long ldr, int act, void* aux_out, int dact, const void* aux_in,
+                       long long ld_aux, int force_bn, int* err_flag, void* stream) {
+  using namespace tp;
+  if (M <= 0 || N <= 0 || K <= 0) return kErrBadArgument;
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % (out_f32 ? 4 : 8))) return kErrBadArgument;
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) |
+       reinterpret_cast<uintptr_t>(out)) & 15)
+    return kErrBadArgument;
+  if (accumulate && !out_f32) return kErrBadArgument;
+  const bool bf16 = dtype == 1;
+  const int BN = pick_bn(M, N, force_bn);
+  CUtensorMap tmA, tmB;
+  bool ok;
+  if (!a_mn) ok = make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16);
+  else ok = make_tmap_2d(&tmA, A, M, K, lda, 64, kBK, bf16);
+  if (!ok) return kErrDriver;
+  if (!b_mn) ok = make_tmap_2d(&tmB, B, K, N, ldb, kBK, BN, bf16);
+  else ok = make_tmap_2d(&tmB, B, N, K, ldb, 64, kBK, bf16);
+  if (!ok) return kErrDriver;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_tiles = (M + kBM - 1) / kBM;
+  p.num_tiles = p.num_m_tiles * ((N + BN - 1) / BN);
+  p.out = out; p.ldo = ldo;
+  p.bias = bias; p.residual = residual; p.ldr = ldr;
+  p.aux_out = aux_out; p.aux_in = aux_in; p.ld_aux = ld_aux;
+  p.alpha = alpha; p.act = act; p.dact = dact; p.accumulate = accumulate;
+  p.err = err_flag;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define TP_DISPATCH(T)                                                                   \
+  (BN == 256 ? dispatch_layout<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)              \
+             : BN == 128 ? dispatch_layout<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
+                         : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, p, s))
+  return bf16 ? TP_DISPATCH(__nv_bfloat16) : TP_DISPATCH(__half);
+#undef TP_DISPATCH
+}

@@ -1,0 +1,74 @@
+"""ctypes loaders for the native libraries and the error type of the kernels."""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+from . import build
+
+_cuda = None
+_host = None
+
+
+class KernelError(RuntimeError):
+    """A native entry point returned a non-zero status."""
+
+
+class CommTimeout(KernelError):
+    """A bounded device-side wait ran out (status word written by the kernel)."""
+
+
+_ERRORS = {-1: "bad argument", -2: "driver call failed (tensor map)", -3: "launch failed",
+           -4: "size beyond the built-in maximum", 101: "producer wait timed out",
+           102: "MMA wait timed out", 103: "epilogue wait timed out",
+           104: "TMEM-empty wait timed out", 105: "peer wait timed out",
+           106: "attention wait timed out"}
+
+
+def check(status: int, what: str) -> None:
+    if status != 0:
+        raise KernelError(f"{what}: {_ERRORS.get(status, 'error')} ({status})")
+
+
+def cuda_lib() -> ctypes.CDLL:
+    """The sm_100a kernel library; built on first use when nvcc is present."""
+    global _cuda
+    if _cuda is None:
+        if not build.CUDA_LIB.exists() or os.environ.get("TERAPIPE_REBUILD"):
+            build.build_cuda()
+        _cuda = ctypes.CDLL(str(build.CUDA_LIB))
+        _declare(_cuda)
+    return _cuda
+
+
+def host_lib() -> ctypes.CDLL:
+    global _host
+    if _host is None:
+        if not build.HOST_LIB.exists():
+            build.build_host()
+        _host = ctypes.CDLL(str(build.HOST_LIB))
+        f = _host.tp_plan_slices
+        f.restype = ctypes.c_double
+        f.argtypes = [c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_longlong,
+                      ctypes.c_double, c_void_p, c_void_p, c_void_p]
+    return _host
+
+
+def _declare(lib: ctypes.CDLL) -> None:
+    P, I, L, F = c_void_p, c_int, c_longlong, c_float
+    sigs = {
+        "tp_gemm": [I, I, I, P, L, P, L, P, L, I, I, I, I, I, F, P, P, L, I, P, I, P, L, I, P, P],
+        "tp_layernorm_fwd": [I, P, P, P, P, P, P, I, I, F, P],
+        "tp_layernorm_bwd_parts": [I],
+        "tp_layernorm_bwd": [I, P, P, P, P, P, P, P, P, P, P, I, I, P],
+        "tp_colsum": [I, P, L, I, I, P, P],
+        "tp_adam_tick": [P, F, F, P],
+        "tp_fused_adam": [I, P, P, P, P, P, L, P, F, F, F, F, F, F, P],
+        "tp_fill": [I, P, L, F, P],
+    }
+    for name, argtypes in sigs.items():
+        if hasattr(lib, name):
+            fn = getattr(lib, name)
+            fn.restype = c_int
+            fn.argtypes = argtypes

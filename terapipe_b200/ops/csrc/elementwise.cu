@@ -50,7 +50,7 @@ template <typename T> __device__ __forceinline__ void store8(T* p, const float (
 // ------------------------------------------------------------------ LayerNorm forward
 // y = (x - mean) * rstd * gamma + beta, one CTA per row; each thread keeps NV vectors of 8.
 template <typename T, int NV>
-__global__ void layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+__global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
                                      const T* __restrict__ beta, T* __restrict__ y,
                                      float* __restrict__ mean_out, float* __restrict__ rstd_out,
                                      int rows, int H, float eps) {
@@ -106,7 +106,7 @@ __global__ void layernorm_fwd_kernel(const T* __restrict__ x, const T* __restric
 // and dbeta = sum dy in registers; partials go to `scratch[gridDim.x][2][H]` and a second
 // kernel folds them into the fp32 gradient accumulators.
 template <typename T, int NV, bool SMEM_PART>
-__global__ void layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+__global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                                      const float* __restrict__ mean, const float* __restrict__ rstd,
                                      const T* __restrict__ gamma, const T* __restrict__ dres,
                                      T* __restrict__ dx, float* __restrict__ scratch, int rows,
@@ -303,7 +303,7 @@ extern "C" int tp_layernorm_fwd(int dtype, const void* x, const void* gamma, con
                                 void* y, float* mean, float* rstd, int rows, int H, float eps,
                                 void* stream) {
   if (rows <= 0) return kOk;
-  if (H % 8 || H > 16384) return kErrBadArgument;
+  if (H % 8 || H > 12288) return kErrBadArgument;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int nv = H > 8192 ? 2 : 1;
   const int threads = ln_threads(H, nv);
@@ -329,7 +329,7 @@ static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const 
                                 float* dgamma, float* dbeta, float* scratch, int rows, int H,
                                 cudaStream_t s) {
   if (rows <= 0) return kOk;
-  if (H % 8 || H > 16384) return kErrBadArgument;
+  if (H % 8 || H > 12288) return kErrBadArgument;
   const int nv = H > 8192 ? 2 : 1;
   const int threads = ln_threads(H, nv);
   const int parts = tp_layernorm_bwd_parts(rows);

@@ -132,3 +132,35 @@ def fused_adam(grad, master, m, v, model, state, lr, beta1=0.9, beta2=0.999, eps
 def fill(t, value: float):
     check(cuda_lib().tp_fill(_dt(t), t.data_ptr(), t.numel(), float(value), _stream()), "tp_fill")
     return t
+
+
+def attn_fwd(qkv, b: int, h: int, D: int, t: int, c: int, o, lse2):
+    """Slice-causal attention forward.
+
+    ``qkv``: full-length projection buffer ``[L, b, h*3*D]`` (per head q,k,v interleaved);
+    rows ``[0, c+t)`` are read, the slice's queries are rows ``[c, c+t)``.
+    ``o``: ``[t*b, h*D]`` output of the slice (row = position*b + batch).
+    ``lse2``: fp32 ``[b*h, L]`` base-2 log-sum-exp, written at positions ``[c, c+t)``."""
+    st = cuda_lib().tp_attn_fwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, o.data_ptr(), o.stride(0),
+                                lse2.data_ptr(), lse2.stride(0),
+                                status_word(qkv.device).data_ptr(), _stream())
+    check(st, "tp_attn_fwd")
+    return o
+
+
+def attn_bwd(qkv, b: int, h: int, D: int, t: int, c: int, o, d_o, lse2, delta, dkv_acc, dqkv,
+             first: bool):
+    """Slice-causal attention backward for the slice ``[c, c+t)``.
+
+    Adds this slice's dK/dV for all ``c+t`` visible positions into ``dkv_acc`` (fp32
+    ``[L, b, h*2*D]``; overwritten instead when ``first``, i.e. for the last slice of the
+    sequence, which is the first one processed) and writes the slice's final
+    ``d(qkv)`` ``[t*b, h*3*D]``.  ``delta`` is an fp32 workspace of ``b*h*t`` elements."""
+    assert delta.numel() >= b * h * t
+    st = cuda_lib().tp_attn_bwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, o.data_ptr(), o.stride(0),
+                                d_o.data_ptr(), d_o.stride(0), lse2.data_ptr(), lse2.stride(0),
+                                delta.data_ptr(), dkv_acc.data_ptr(), dqkv.data_ptr(),
+                                dqkv.stride(0), int(first), status_word(qkv.device).data_ptr(),
+                                _stream())
+    check(st, "tp_attn_bwd")
+    return dqkv

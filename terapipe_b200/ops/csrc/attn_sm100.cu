@@ -12,7 +12,7 @@
 // Backward recomputes P from Q, K and the saved log-sum-exp (base 2).  Two kernels, both
 // deterministic (no floating-point atomics):
 //   * dK/dV: one CTA per (128-key block, head); loops over the slice's query blocks and adds
-//     its result into a persistent fp32 accumulator dkv[L][b][h][2][D] that lives across the
+//     its result into a persistent fp32 accumulator dkv[b][h][L][2][D] that lives across the
 //     slices of one backward pass; rows of the current slice are final and are also written
 //     as 16-bit values into the slice's d(qkv) buffer for the QKV weight/data gradients.
 //   * dQ:    one CTA per (128-query block, head); loops over key blocks.
@@ -37,7 +37,8 @@ struct AttnParams {
   float* lse2;          // [b*h][lse_stride], indexed by absolute position
   long long lse_stride;
   const float* delta;   // bwd: [b*h][t] = rowsum(dO * O)
-  float* dkv_acc;       // [L][b][h][2][D] fp32
+  float* dkv_acc;       // [b*h][dkv_rows][2][D] fp32 (head-major: a CTA's key rows are contiguous)
+  long long dkv_rows;
   void* dqkv;           // [t*b][ld_dqkv], same column order as qkv
   long long ld_dqkv;
   int first;            // dK/dV: overwrite the accumulator instead of adding to it
@@ -460,7 +461,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmKV128,
       tc_fence_after();
       const bool row_ok = kpos < p.c + p.t;
       const bool final_row = kpos >= p.c;
-      float* acc = p.dkv_acc + ((static_cast<long long>(kpos) * p.b + bi) * p.h + hi) * 2 * D;
+      float* acc = p.dkv_acc + (static_cast<long long>(bh) * p.dkv_rows + kpos) * 2 * D;
       T* drow = static_cast<T*>(p.dqkv) +
                 (static_cast<long long>(kpos - p.c) * p.b + bi) * p.ld_dqkv + hi * 3 * D;
 #pragma unroll 1
@@ -475,13 +476,17 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmKV128,
           tmem_ld_wait();
           if (!row_ok) continue;
           float* a = acc + which * D + ch * 32;
+          float4 oldv[8];
+          if (!p.first) {
+#pragma unroll
+            for (int g = 0; g < 8; ++g) oldv[g] = __ldcg(reinterpret_cast<const float4*>(a + g * 4));
+          }
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             float4 v = make_float4(__uint_as_float(raw[g * 4 + 0]) * mul, __uint_as_float(raw[g * 4 + 1]) * mul,
                                    __uint_as_float(raw[g * 4 + 2]) * mul, __uint_as_float(raw[g * 4 + 3]) * mul);
             if (!p.first) {
-              const float4 old = *reinterpret_cast<const float4*>(a + g * 4);
-              v.x += old.x; v.y += old.y; v.z += old.z; v.w += old.w;
+              v.x += oldv[g].x; v.y += oldv[g].y; v.z += oldv[g].z; v.w += oldv[g].w;
             }
             if (final_row) {
               uint2 u;
@@ -489,7 +494,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmKV128,
               u.y = Elem<T>::pack2(v.z, v.w);
               *reinterpret_cast<uint2*>(drow + (1 + which) * D + ch * 32 + g * 4) = u;
             } else {
-              *reinterpret_cast<float4*>(a + g * 4) = v;
+              __stcg(reinterpret_cast<float4*>(a + g * 4), v);
             }
           }
         }
@@ -774,17 +779,17 @@ extern "C" int tp_attn_fwd(int dtype, int D, const void* qkv, int b, int h, int 
 }
 
 // o / d_o: this slice's [t*b][ld] attention output and its gradient; delta: fp32 [b*h*t]
-// workspace; dkv_acc: persistent fp32 [L][b][h][2][D]; dqkv: this slice's [t*b][ld_dqkv] output.
+// workspace; dkv_acc: persistent fp32 [b*h][dkv_rows][2][D] (dkv_rows >= c+t); dqkv: this slice's [t*b][ld_dqkv] output.
 extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int t, int c,
                            const void* o, long long ld_o, const void* d_o, long long ld_do,
                            const float* lse2, long long lse_stride, float* delta, float* dkv_acc,
-                           void* dqkv, long long ld_dqkv, int first, int* err, void* stream) {
+                           long long dkv_rows, void* dqkv, long long ld_dqkv, int first, int* err, void* stream) {
   if ((D != 64 && D != 128) || t <= 0 || c < 0 || b <= 0 || h <= 0) return kErrBadArgument;
   if (ld_o % 8 || ld_do % 8 || ld_dqkv % 8) return kErrBadArgument;
   AttnParams p = base_params(D, b, h, t, c, err);
   p.o = const_cast<void*>(o); p.ld_o = ld_o;
   p.lse2 = const_cast<float*>(lse2); p.lse_stride = lse_stride;
-  p.delta = delta; p.dkv_acc = dkv_acc; p.dqkv = dqkv; p.ld_dqkv = ld_dqkv; p.first = first;
+  p.delta = delta; p.dkv_acc = dkv_acc; p.dkv_rows = dkv_rows; p.dqkv = dqkv; p.ld_dqkv = ld_dqkv; p.first = first;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == 1;
   if (D == 128) return bf16 ? attn_bwd_launch<__nv_bfloat16, 128>(qkv, o, d_o, ld_do, delta, p, true, s)

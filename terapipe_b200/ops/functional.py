@@ -153,13 +153,13 @@ def attn_bwd(qkv, b: int, h: int, D: int, t: int, c: int, o, d_o, lse2, delta, d
     """Slice-causal attention backward for the slice ``[c, c+t)``.
 
     Adds this slice's dK/dV for all ``c+t`` visible positions into ``dkv_acc`` (fp32
-    ``[L, b, h*2*D]``; overwritten instead when ``first``, i.e. for the last slice of the
+    ``[b*h, L, 2*D]``; overwritten instead when ``first``, i.e. for the last slice of the
     sequence, which is the first one processed) and writes the slice's final
     ``d(qkv)`` ``[t*b, h*3*D]``.  ``delta`` is an fp32 workspace of ``b*h*t`` elements."""
     assert delta.numel() >= b * h * t
     st = cuda_lib().tp_attn_bwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, o.data_ptr(), o.stride(0),
                                 d_o.data_ptr(), d_o.stride(0), lse2.data_ptr(), lse2.stride(0),
-                                delta.data_ptr(), dkv_acc.data_ptr(), dqkv.data_ptr(),
+                                delta.data_ptr(), dkv_acc.data_ptr(), dkv_acc.shape[1], dqkv.data_ptr(),
                                 dqkv.stride(0), int(first), status_word(qkv.device).data_ptr(),
                                 _stream())
     check(st, "tp_attn_bwd")

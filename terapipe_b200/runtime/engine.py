@@ -1,0 +1,503 @@
+"""The sm_100a training engine: one pipeline stage per GPU, explicit forward/backward.
+
+What one rank owns
+------------------
+* Flat parameter state for its layers: a 16-bit model copy, fp32 master weights, Adam
+  moments and an fp32 main-gradient buffer.  One fused Adam launch updates the whole
+  stage; weight-gradient GEMMs accumulate straight into the main-gradient buffer.
+* Full-length activation buffers ``[L*B, width]`` per layer.  A token slice is a contiguous
+  row range, so the "KV cache" is simply the QKV projection buffer: slice *j* writes rows
+  ``[c, c+t)`` and attends over rows ``[0, c+t)`` in place.
+* A persistent fp32 ``dK/dV`` accumulator per layer that carries gradients from later
+  slices back to earlier ones while the backward pass walks the slices in reverse.
+
+Schedule (same as the reference, test_transformer_terapipe.py:107-175,270-287): for each
+batch slice all token slices forward in order; backward visits batch slices and token
+slices in reverse; data-parallel gradient reduction; optimizer.  There is no autograd graph:
+every kernel of the forward and backward pass is launched explicitly, which lets the whole
+iteration be captured in one CUDA graph when the stage does not communicate.
+
+Tensor parallelism keeps activations replicated inside the TP group (as the reference
+does); the partial products of row-parallel layers and the data gradients of
+column-parallel layers are summed either by NCCL all-reduce or by the fused
+GEMM + all-reduce kernel over NVLink peer memory (``tp_comm="fused"``).
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .. import parallel as mpu
+from ..models import TransformerConfig
+from ..ops import functional as F
+from ..ops.lib import cuda_lib
+
+LOSS_SCALE_FACTOR = 128.0
+_ACT = {"none": 0, "relu": 1, "gelu": 2}
+
+# parameter order inside a layer (names match the portable layer's state dict)
+PARAM_ORDER = ("attn_ln.weight", "attn_ln.bias", "attn.in_proj.weight", "attn.in_proj.bias",
+               "attn.out_proj.weight", "attn.out_proj.bias", "fc_ln.weight", "fc_ln.bias",
+               "fc1.weight", "fc1.bias", "fc2.weight", "fc2.bias")
+
+
+def _align(n: int, a: int = 8) -> int:
+    return (n + a - 1) // a * a
+
+
+class _Layout:
+    """Offsets (in elements) of every parameter of the stage inside the flat buffers."""
+
+    def __init__(self, n_layers: int, H: int, F_: int, tp: int):
+        hl, fl = H // tp, F_ // tp
+        self.shapes = {
+            "attn_ln.weight": (H,), "attn_ln.bias": (H,),
+            "attn.in_proj.weight": (3 * hl, H), "attn.in_proj.bias": (3 * hl,),
+            "attn.out_proj.weight": (H, hl), "attn.out_proj.bias": (H,),
+            "fc_ln.weight": (H,), "fc_ln.bias": (H,),
+            "fc1.weight": (fl, H), "fc1.bias": (fl,),
+            "fc2.weight": (H, fl), "fc2.bias": (H,),
+        }
+        self.offsets: List[Dict[str, int]] = []
+        off = 0
+        for _ in range(n_layers):
+            entry = {}
+            for name in PARAM_ORDER:
+                entry[name] = off
+                off += _align(math.prod(self.shapes[name]))
+            self.offsets.append(entry)
+        self.total = _align(off, 8)
+
+
+class StageEngine:
+    def __init__(self, config: TransformerConfig, batch_slices: Sequence[int],
+                 seq_slices: Sequence[int], dtype=torch.float16, loss_scale=LOSS_SCALE_FACTOR,
+                 lr=1e-10, seed=0, init="device", use_graph: Optional[bool] = None,
+                 tp_comm="nccl", device=None):
+        assert torch.cuda.is_available(), "StageEngine needs a CUDA device (sm_100a)"
+        self.cfg = config
+        self.batch_slices, self.seq_slices = list(batch_slices), list(seq_slices)
+        assert sum(self.batch_slices) == config.batch_size and sum(self.seq_slices) == config.seq_len
+        self.dtype, self.dt = dtype, (0 if dtype == torch.float16 else 1)
+        self.loss_scale, self.lr, self.seed = float(loss_scale), lr, seed
+        self.device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
+        self.lib = cuda_lib()
+        self.topo = mpu.get_topology()
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.dp_idx, self.pp_idx, self.tp_idx = self.topo.coords(self.rank)
+        self.tp, self.pp, self.dp = self.topo.tp, self.topo.pp, self.topo.dp
+        self.is_first, self.is_last = self.pp_idx == 0, self.pp_idx == self.pp - 1
+        self.layer_ids = self.topo.layers_of_stage(config.n_layers, self.pp_idx)
+        self.n_layers = len(self.layer_ids)
+        self.tp_comm = tp_comm if self.tp > 1 else "none"
+
+        H, Fw = config.embedding_dim, config.ffn_embedding_dim
+        heads = config.num_attention_heads
+        assert heads % self.tp == 0 and Fw % self.tp == 0
+        self.H, self.D = H, H // heads
+        self.h = heads // self.tp
+        self.Hl, self.Fl = self.h * self.D, Fw // self.tp
+        if self.D not in (64, 128):
+            raise ValueError(f"head dim {self.D} is not supported by the attention kernels (64 or 128)")
+        self.L, self.B = config.seq_len, config.batch_size
+        self.rows = self.L * self.B
+        self.act = config.activation
+        self.es = 2  # bytes per 16-bit element
+
+        self.layout = _Layout(self.n_layers, H, Fw, self.tp)
+        n = self.layout.total
+        dev = self.device
+        self.model = torch.zeros(n, dtype=dtype, device=dev)
+        self.master = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.adam_state = torch.zeros(3, dtype=torch.float32, device=dev)
+        self._init_weights(init)
+        self._alloc_activations()
+        self.status = F.status_word(dev)
+        self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
+        self.use_graph = (self.pp == 1 and self.tp == 1 and self.dp == 1) if use_graph is None else use_graph
+        self._graph = None
+        self.step_count = 0
+        self._streams_ready = False
+        # launches of this library's own kernels (NCCL and torch kernels are not counted):
+        # per layer and slice 7 forward (2 LN, 4 GEMM, attention) and 19 backward (8 GEMM,
+        # 4 bias column sums, 2x2 LN, 3 attention), plus 2 for the optimizer
+        n_slices = len(self.batch_slices) * len(self.seq_slices)
+        self.launches_per_step = n_slices * self.n_layers * 26 + 2
+        self.launch_count = 0
+
+    # ------------------------------------------------------------------ parameters
+    def param(self, layer: int, name: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        buf = self.model if buf is None else buf
+        shape = self.layout.shapes[name]
+        off = self.layout.offsets[layer][name]
+        return buf[off:off + math.prod(shape)].view(shape)
+
+    def _init_weights(self, init: str) -> None:
+        """``"reference"``: the full master matrix of every layer is drawn on the CPU from
+        the global generator seeded with ``seed`` in the portable layer's order, then sliced
+        (bit-identical to the portable path for any TP/PP layout).  ``"device"``: the full
+        matrix is drawn on the GPU from a generator keyed by (seed, layer, matrix); still
+        independent of the TP/PP layout, and fast enough for 10^10-parameter stacks."""
+        H, Fw = self.H, self.cfg.ffn_embedding_dim
+        full = {"attn.in_proj.weight": (3 * H, H), "attn.out_proj.weight": (H, H),
+                "fc1.weight": (Fw, H), "fc2.weight": (H, Fw)}
+        if init == "reference":
+            torch.manual_seed(self.seed)
+        for li, gid in enumerate(range(self.cfg.n_layers)):
+            mine = gid in self.layer_ids
+            local = gid - self.layer_ids.start
+            for mi, (name, shape) in enumerate(full.items()):
+                if init == "reference":
+                    w = torch.empty(shape)
+                    torch.nn.init.xavier_normal_(w)
+                    if not mine:
+                        continue
+                    w = w.to(self.device)
+                else:
+                    if not mine:
+                        continue
+                    g = torch.Generator(device=self.device)
+                    g.manual_seed((self.seed * 1000003 + gid) * 8 + mi)
+                    std = math.sqrt(2.0 / (shape[0] + shape[1]))
+                    w = torch.randn(shape, device=self.device, generator=g) * std
+                if name in ("attn.in_proj.weight", "fc1.weight"):
+                    nrow = shape[0] // self.tp
+                    w = w[self.tp_idx * nrow:(self.tp_idx + 1) * nrow]
+                else:
+                    ncol = shape[1] // self.tp
+                    w = w[:, self.tp_idx * ncol:(self.tp_idx + 1) * ncol]
+                self.param(local, name, self.master).copy_(w)
+                del w
+            if mine:
+                for name in ("attn_ln.weight", "fc_ln.weight"):
+                    self.param(local, name, self.master).fill_(1.0)
+        self.model.copy_(self.master)
+        if self.dtype != torch.float32:
+            # the 16-bit copy is authoritative at start, as when a model is cast with .half()
+            self.master.copy_(self.model)
+
+    def state_dict(self) -> Dict[str, torch.Tensor]:
+        return {f"layers.layers.{l}.{name}": self.param(l, name).clone()
+                for l in range(self.n_layers) for name in PARAM_ORDER}
+
+    def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
+        for l in range(self.n_layers):
+            for name in PARAM_ORDER:
+                src = sd[f"layers.layers.{l}.{name}"].to(self.device)
+                self.param(l, name, self.master).copy_(src)
+        self.model.copy_(self.master)
+        if self.dtype != torch.float32:
+            self.master.copy_(self.model)
+
+    def named_grads(self, unscale=True) -> Dict[str, torch.Tensor]:
+        s = 1.0 / self.loss_scale if unscale else 1.0
+        return {f"layers.layers.{l}.{name}": self.param(l, name, self.grad).clone() * s
+                for l in range(self.n_layers) for name in PARAM_ORDER}
+
+    # ------------------------------------------------------------------ buffers
+    def _alloc_activations(self) -> None:
+        dev, dt, rows = self.device, self.dtype, self.rows
+        H, Hl, Fl = self.H, self.Hl, self.Fl
+
+        def buf(width, dtype=dt):
+            return torch.empty(rows, width, dtype=dtype, device=dev)
+
+        self.X = [buf(H) for _ in range(self.n_layers + 1)]
+        self.ln1 = [buf(H) for _ in range(self.n_layers)]
+        self.ln2 = [buf(H) for _ in range(self.n_layers)]
+        self.xmid = [buf(H) for _ in range(self.n_layers)]
+        self.qkv = [buf(3 * Hl) for _ in range(self.n_layers)]
+        self.ao = [buf(Hl) for _ in range(self.n_layers)]
+        self.fa = [buf(Fl) for _ in range(self.n_layers)]
+        self.fz = [buf(Fl) for _ in range(self.n_layers)] if self.act == "gelu" else None
+        self.stats = [torch.empty(4, rows, dtype=torch.float32, device=dev) for _ in range(self.n_layers)]
+        self.lse = [torch.empty(self.B * self.h, self.L, dtype=torch.float32, device=dev)
+                    for _ in range(self.n_layers)]
+        self.dkv = [buf(2 * Hl, torch.float32) for _ in range(self.n_layers)]
+        self.dY = buf(H) if not self.is_last else None     # gradients received from the next stage
+        self.dX0 = buf(H) if not self.is_first else None   # gradients sent to the previous stage
+        tmax = max(self.seq_slices) * max(self.batch_slices)
+        self.tmax = tmax
+
+        def scratch(width, dtype=dt):
+            return torch.empty(tmax, width, dtype=dtype, device=dev)
+
+        self.dA, self.dB, self.dln = scratch(H), scratch(H), scratch(H)
+        self.dfc, self.dao, self.dqkv = scratch(Fl), scratch(Hl), scratch(3 * Hl)
+        self.delta = torch.empty(max(self.batch_slices) * self.h * max(self.seq_slices),
+                                 dtype=torch.float32, device=dev)
+        self.ln_scratch = torch.empty(F.layernorm_bwd_scratch_floats(tmax, H), dtype=torch.float32,
+                                      device=dev)
+        numel = self.L * self.B * H
+        self.dy_seed = torch.full((tmax, H), self.loss_scale / numel, dtype=dt, device=dev) \
+            if self.is_last else None
+        # slice bookkeeping: (batch offset, b, token offset c, t, first row)
+        self.slices = []
+        boff = 0
+        for b in self.batch_slices:
+            c = 0
+            per_batch = []
+            for t in self.seq_slices:
+                per_batch.append((boff, b, c, t, self.L * boff + c * b))
+                c += t
+            self.slices.append(per_batch)
+            boff += b
+
+    # ------------------------------------------------------------------ raw launches
+    def _gemm(self, a, lda, b, ldb, out, ldo, M, N, K, a_mn=0, b_mn=0, out_f32=0, accumulate=0,
+              bias=None, residual=None, ldr=0, act=0, aux_out=None, dact=0, aux_in=None, ld_aux=0):
+        st = self.lib.tp_gemm(self.dt, a_mn, b_mn, a, lda, b, ldb, out, ldo, out_f32, accumulate,
+                              M, N, K, 1.0, bias, residual, ldr, act, aux_out, dact, aux_in, ld_aux,
+                              0, self._status_ptr, self._stream)
+        if st:
+            F.check(st, "tp_gemm")
+
+    def _p(self, layer, name, buf=None):
+        base = (self.model if buf is None else buf)
+        return base.data_ptr() + self.layout.offsets[layer][name] * base.element_size()
+
+    def _all_reduce_rows(self, tensor, r0, T):
+        dist.all_reduce(tensor[r0:r0 + T], group=mpu.get_model_parallel_group())
+
+    # ------------------------------------------------------------------ forward of one slice
+    def _forward_slice(self, sl) -> None:
+        boff, b, c, t, r0 = sl
+        T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
+        lib, dt, s = self.lib, self.dt, self._stream
+        tp0 = self.tp_idx == 0
+        for l in range(self.n_layers):
+            x = self.X[l].data_ptr() + r0 * H * es
+            ln1 = self.ln1[l].data_ptr() + r0 * H * es
+            st = self.stats[l].data_ptr()
+            lib.tp_layernorm_fwd(dt, x, self._p(l, "attn_ln.weight"), self._p(l, "attn_ln.bias"), ln1,
+                                 st + r0 * 4, st + (self.rows + r0) * 4, T, H, 1e-5, s)
+            qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
+            qkv = self.qkv[l].data_ptr() + r0 * 3 * Hl * es
+            self._gemm(ln1, H, self._p(l, "attn.in_proj.weight"), H, qkv, 3 * Hl, T, 3 * Hl, H,
+                       bias=self._p(l, "attn.in_proj.bias"))
+            ao = self.ao[l].data_ptr() + r0 * Hl * es
+            lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
+            rc = lib.tp_attn_fwd(dt, self.D, qkv_base, b, self.h, t, c, ao, Hl, lse, self.L,
+                                 self._status_ptr, s)
+            if rc:
+                F.check(rc, "tp_attn_fwd")
+            xmid = self.xmid[l].data_ptr() + r0 * H * es
+            self._gemm(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl, xmid, H, T, H, Hl,
+                       bias=self._p(l, "attn.out_proj.bias") if tp0 else None,
+                       residual=x if tp0 else None, ldr=H)
+            if self.tp > 1:
+                self._all_reduce_rows(self.xmid[l], r0, T)
+            ln2 = self.ln2[l].data_ptr() + r0 * H * es
+            lib.tp_layernorm_fwd(dt, xmid, self._p(l, "fc_ln.weight"), self._p(l, "fc_ln.bias"), ln2,
+                                 st + (2 * self.rows + r0) * 4, st + (3 * self.rows + r0) * 4, T, H,
+                                 1e-5, s)
+            fa = self.fa[l].data_ptr() + r0 * Fl * es
+            fz = self.fz[l].data_ptr() + r0 * Fl * es if self.fz is not None else None
+            self._gemm(ln2, H, self._p(l, "fc1.weight"), H, fa, Fl, T, Fl, H,
+                       bias=self._p(l, "fc1.bias"), act=_ACT[self.act], aux_out=fz, ld_aux=Fl)
+            xo = self.X[l + 1].data_ptr() + r0 * H * es
+            self._gemm(fa, Fl, self._p(l, "fc2.weight"), Fl, xo, H, T, H, Fl,
+                       bias=self._p(l, "fc2.bias") if tp0 else None,
+                       residual=xmid if tp0 else None, ldr=H)
+            if self.tp > 1:
+                self._all_reduce_rows(self.X[l + 1], r0, T)
+
+    # ------------------------------------------------------------------ backward of one slice
+    def _backward_slice(self, sl, first: bool) -> None:
+        boff, b, c, t, r0 = sl
+        T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
+        lib, dt, s = self.lib, self.dt, self._stream
+        g = self.grad
+        dA, dB, dln = self.dA.data_ptr(), self.dB.data_ptr(), self.dln.data_ptr()
+        dfc, dao, dqkv = self.dfc.data_ptr(), self.dao.data_ptr(), self.dqkv.data_ptr()
+        if self.is_last:
+            dcur = self.dy_seed.data_ptr()
+        else:
+            dcur = self.dY.data_ptr() + r0 * H * es
+        for l in reversed(range(self.n_layers)):
+            st = self.stats[l].data_ptr()
+            fa = self.fa[l].data_ptr() + r0 * Fl * es
+            aux = (self.fz[l].data_ptr() + r0 * Fl * es) if self.fz is not None else fa
+            xmid = self.xmid[l].data_ptr() + r0 * H * es
+            ln2 = self.ln2[l].data_ptr() + r0 * H * es
+            ln1 = self.ln1[l].data_ptr() + r0 * H * es
+            x = self.X[l].data_ptr() + r0 * H * es
+            ao = self.ao[l].data_ptr() + r0 * Hl * es
+            # ---- FFN
+            self._gemm(dcur, H, self._p(l, "fc2.weight"), Fl, dfc, Fl, T, Fl, H, b_mn=1,
+                       dact=_ACT[self.act], aux_in=aux, ld_aux=Fl)
+            self._gemm(dcur, H, fa, Fl, self._p(l, "fc2.weight", g), Fl, H, Fl, T, a_mn=1, b_mn=1,
+                       out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dcur, H, T, H, self._p(l, "fc2.bias", g), s)
+            self._gemm(dfc, Fl, self._p(l, "fc1.weight"), H, dln, H, T, H, Fl, b_mn=1)
+            if self.tp > 1:
+                self._all_reduce_rows(self.dln, 0, T)
+            self._gemm(dfc, Fl, ln2, H, self._p(l, "fc1.weight", g), H, Fl, H, T, a_mn=1, b_mn=1,
+                       out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dfc, Fl, T, Fl, self._p(l, "fc1.bias", g), s)
+            lib.tp_layernorm_bwd(dt, dln, xmid, st + (2 * self.rows + r0) * 4,
+                                 st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur, dB,
+                                 self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g),
+                                 self.ln_scratch.data_ptr(), T, H, s)
+            # ---- attention
+            self._gemm(dB, H, self._p(l, "attn.out_proj.weight"), Hl, dao, Hl, T, Hl, H, b_mn=1)
+            self._gemm(dB, H, ao, Hl, self._p(l, "attn.out_proj.weight", g), Hl, H, Hl, T, a_mn=1,
+                       b_mn=1, out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dB, H, T, H, self._p(l, "attn.out_proj.bias", g), s)
+            qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
+            lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
+            dkv = self.dkv[l].data_ptr() + self.L * boff * 2 * Hl * 4
+            rc = lib.tp_attn_bwd(dt, self.D, qkv_base, b, self.h, t, c, ao, Hl, dao, Hl, lse, self.L,
+                                 self.delta.data_ptr(), dkv, self.L, dqkv, 3 * Hl, int(first),
+                                 self._status_ptr, s)
+            if rc:
+                F.check(rc, "tp_attn_bwd")
+            self._gemm(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, dln, H, T, H, 3 * Hl, b_mn=1)
+            if self.tp > 1:
+                self._all_reduce_rows(self.dln, 0, T)
+            self._gemm(dqkv, 3 * Hl, ln1, H, self._p(l, "attn.in_proj.weight", g), H, 3 * Hl, H, T,
+                       a_mn=1, b_mn=1, out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dqkv, 3 * Hl, T, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
+            dnext = dA if (l > 0 or self.is_first) else self.dX0.data_ptr() + r0 * H * es
+            lib.tp_layernorm_bwd(dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
+                                 self._p(l, "attn_ln.weight"), dB, dnext,
+                                 self._p(l, "attn_ln.weight", g), self._p(l, "attn_ln.bias", g),
+                                 self.ln_scratch.data_ptr(), T, H, s)
+            dcur = dnext
+
+    # ------------------------------------------------------------------ one iteration
+    def _refresh_handles(self):
+        self._stream = torch.cuda.current_stream().cuda_stream
+        self._status_ptr = self.status.data_ptr()
+
+    def _setup_streams(self):
+        if self._streams_ready:
+            return
+        self.recv_stream = torch.cuda.Stream()
+        self._streams_ready = True
+
+    def _post_recvs(self, forward: bool):
+        """Pre-post every receive of a pass on a side stream so that transfers overlap the
+        compute of earlier slices; returns the work handles in consumption order."""
+        works = {}
+        src = mpu.get_pipeline_prev_rank() if forward else mpu.get_pipeline_next_rank()
+        buf = self.X[0] if forward else self.dY
+        order = [(bi, si) for bi in range(len(self.batch_slices)) for si in range(len(self.seq_slices))]
+        if not forward:
+            order = order[::-1]
+        with torch.cuda.stream(self.recv_stream):
+            for bi, si in order:
+                _, b, _, t, r0 = self.slices[bi][si]
+                works[(bi, si)] = dist.irecv(buf[r0:r0 + t * b], src)
+        return works
+
+    def _forward_backward(self):
+        pipelined = self.pp > 1
+        if pipelined:
+            self._setup_streams()
+        nb, ns = len(self.batch_slices), len(self.seq_slices)
+        sends = []
+        recvs = self._post_recvs(True) if (pipelined and not self.is_first) else None
+        for bi in range(nb):
+            for si in range(ns):
+                sl = self.slices[bi][si]
+                if recvs is not None:
+                    recvs[(bi, si)].wait()
+                self._forward_slice(sl)
+                if pipelined and not self.is_last:
+                    _, b, _, t, r0 = sl
+                    sends.append(dist.isend(self.X[self.n_layers][r0:r0 + t * b],
+                                            mpu.get_pipeline_next_rank()))
+        if self.is_last:
+            self.loss_buf.copy_(self.X[self.n_layers].sum(dtype=torch.float32))
+        recvs = self._post_recvs(False) if (pipelined and not self.is_last) else None
+        for bi in reversed(range(nb)):
+            for si in reversed(range(ns)):
+                sl = self.slices[bi][si]
+                if recvs is not None:
+                    recvs[(bi, si)].wait()
+                self._backward_slice(sl, first=(si == ns - 1))
+                if pipelined and not self.is_first:
+                    _, b, _, t, r0 = sl
+                    sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank()))
+        for w in sends:
+            w.wait()
+
+    def _reduce_and_update(self):
+        if self.dp > 1:
+            dist.all_reduce(self.grad, group=mpu.get_data_parallel_group())
+        F.adam_tick(self.adam_state)
+        F.fused_adam(self.grad, self.master, self.exp_avg, self.exp_avg_sq, self.model,
+                     self.adam_state, lr=self.lr, grad_scale=1.0 / (self.loss_scale * self.dp))
+
+    def _iteration(self, update=True):
+        self._refresh_handles()
+        self._forward_backward()
+        if update:
+            self._reduce_and_update()
+
+    def set_input(self, x: torch.Tensor) -> None:
+        """Copy this replica's ``[L, B, H]`` input into the stage-0 activation buffer.  Rows are
+        regrouped per batch slice (each batch slice owns a contiguous ``[L, b, H]`` block)."""
+        assert self.is_first
+        x = x.to(self.device, self.dtype, non_blocking=True)
+        if len(self.batch_slices) == 1:
+            self.X[0].view(self.L, self.B, self.H).copy_(x)
+        else:
+            boff = 0
+            for b in self.batch_slices:
+                dst = self.X[0][self.L * boff:self.L * (boff + b)].view(self.L, b, self.H)
+                dst.copy_(x[:, boff:boff + b])
+                boff += b
+
+    def output(self) -> torch.Tensor:
+        """The stage output as ``[L, B, H]`` (a copy when several batch slices exist)."""
+        y = self.X[self.n_layers]
+        if len(self.batch_slices) == 1:
+            return y.view(self.L, self.B, self.H)
+        parts, boff = [], 0
+        for b in self.batch_slices:
+            parts.append(y[self.L * boff:self.L * (boff + b)].view(self.L, b, self.H))
+            boff += b
+        return torch.cat(parts, dim=1)
+
+    def loss(self) -> torch.Tensor:
+        """Device scalar: mean of the final output (valid on the last stage after a step)."""
+        return self.loss_buf / float(self.L * self.B * self.H)
+
+    def compute_grads(self) -> None:
+        """Forward + backward without the optimizer; scaled grads stay in ``self.grad``."""
+        self.grad.zero_()
+        self._iteration(update=False)
+        if self.dp > 1:
+            dist.all_reduce(self.grad, group=mpu.get_data_parallel_group())
+            self.grad.div_(self.dp)
+
+    def step(self) -> None:
+        """One training iteration on the current stream.  With ``use_graph`` the first call
+        runs eagerly (it also sets up kernel attributes) and records the iteration into a
+        CUDA graph; later calls replay the graph."""
+        if self.use_graph and self._graph is not None:
+            self._graph.replay()
+        else:
+            self._iteration()
+            if self.use_graph:
+                self._capture()
+        self.step_count += 1
+        self.launch_count += self.launches_per_step
+
+    def _capture(self):
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            self._iteration()
+        self._graph = graph
+
+    def check_status(self):
+        F.check_device_status(self.device)

@@ -1,0 +1,86 @@
+"""Public training API: build the parallel layout and the sm_100a engine, feed inputs, step.
+
+    trainer = Trainer("gpt3-1b", batch_size=8, tp=1, pp=world_size,
+                      batch_slices=[8], seq_slices=[128] * 16)
+    loss = trainer.train_step(host_input)      # H2D copy, forward, backward, Adam, loss D2H
+
+``batch_size`` is the batch of ONE data-parallel replica; the data-parallel size is
+``world_size // (tp * pp)``.  Inputs are hidden states ``[seq, batch, hidden]`` (the
+benchmark harness has no embedding, as in the reference, terapipe.py:48-49); the loss is
+the mean of the final output.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from .. import parallel as mpu
+from ..models import TransformerConfig
+from .engine import StageEngine
+
+_DTYPES = {"fp16": torch.float16, "bf16": torch.bfloat16,
+           torch.float16: torch.float16, torch.bfloat16: torch.bfloat16}
+
+
+class Trainer:
+    def __init__(self, model: str, batch_size: int, tp: int = 1, pp: int = 1,
+                 batch_slices: Optional[Sequence[int]] = None,
+                 seq_slices: Optional[Sequence[int]] = None, dtype="fp16",
+                 n_layers: Optional[int] = None, activation: str = "gelu", use_graph=None,
+                 tp_comm: str = "nccl", lr: float = 1e-10, seed: int = 0, init: str = "device",
+                 loss_scale: float = 128.0):
+        if dist.is_initialized():
+            if not mpu.model_parallel_is_initialized():
+                mpu.initialize_model_parallel(tp, pp, verbose=False)
+        elif tp * pp != 1:
+            raise RuntimeError("tp*pp > 1 needs torch.distributed to be initialised")
+        self.topo = mpu.get_topology()
+        self.config = TransformerConfig.from_predefined_model(
+            model, n_devices=self.topo.world_size, batch_size=batch_size, n_layers=n_layers,
+            activation=activation)
+        batch_slices = list(batch_slices) if batch_slices else [batch_size]
+        seq_slices = list(seq_slices) if seq_slices else [self.config.seq_len]
+        self.dtype = _DTYPES[dtype]
+        self.seed = seed
+        self.engine = StageEngine(self.config, batch_slices, seq_slices, dtype=self.dtype,
+                                  loss_scale=loss_scale, lr=lr, seed=seed, init=init,
+                                  use_graph=use_graph, tp_comm=tp_comm)
+        self._staging = None
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.engine.is_first
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.engine.is_last
+
+    def synthetic_input(self, step: int, pinned: bool = False) -> Optional[torch.Tensor]:
+        """N(0,1) hidden states on the host for this replica (None on later stages).  All
+        tensor-parallel ranks of a replica draw the same values (seeded by replica and step)."""
+        if not self.is_first_stage:
+            return None
+        c = self.config
+        g = torch.Generator().manual_seed(1000003 * (self.seed + 1) + 7919 * self.engine.dp_idx + step)
+        x = torch.randn(c.seq_len, c.batch_size, c.embedding_dim, generator=g).to(self.dtype)
+        return x.pin_memory() if pinned else x
+
+    def load_input(self, x: Optional[torch.Tensor]) -> None:
+        if self.is_first_stage and x is not None:
+            self.engine.set_input(x)
+
+    def train_step(self, x: Optional[torch.Tensor] = None) -> Optional[float]:
+        """One iteration end to end.  ``x`` is the replica's host (ideally pinned) or device
+        input on first-stage ranks; returns the loss as a Python float on last-stage ranks."""
+        self.load_input(x)
+        self.engine.step()
+        if self.is_last_stage:
+            return float(self.engine.loss().item())
+        return None
+
+    def compute_grads(self, x: Optional[torch.Tensor] = None):
+        self.load_input(x)
+        self.engine.compute_grads()
+        return self.engine.named_grads()

@@ -47,7 +47,7 @@ def test_attention_slices_match_full_causal(dtype, D, b, h, slices):
 
     g = torch.randn(L * b, h * D, device="cuda", dtype=dtype)
     ref.backward(g.float().view(L, b, h * D))
-    dkv = torch.full((L, b, h * 2 * D), float("nan"), device="cuda")
+    dkv = torch.full((b * h, L, 2 * D), float("nan"), device="cuda")
     dqkv = torch.zeros(L * b, h * 3 * D, device="cuda", dtype=dtype)
     delta = torch.empty(b * h * max(slices), device="cuda")
     c = L

@@ -9,16 +9,14 @@
 // handed to the second MMA through shared memory, the running output stays in TMEM and is
 // rescaled lazily (only when the row maximum grows by more than 2^8).
 //
-// Backward recomputes P from Q, K and the saved log-sum-exp (base 2).  Two kernels, both
-// deterministic (no floating-point atomics):
-//   * dK/dV: one CTA per (128-key block, head); loops over the slice's query blocks and adds
-//     its result into a persistent fp32 accumulator dkv[b][h][L][2][D] that lives across the
-//     slices of one backward pass; rows of the current slice are final and are also written
-//     as 16-bit values into the slice's d(qkv) buffer for the QKV weight/data gradients.
-//   * dQ:    one CTA per (128-query block, head); loops over key blocks.
+// Backward recomputes P from Q, K and the saved log-sum-exp (base 2); see the comment above
+// attn_bwd_kernel.  No gradient accumulator crosses slices: the backward pass walks the
+// slices in reverse, so when slice j is processed the attention-output gradients dO of all
+// later slices already sit in a full-length buffer, and dK/dV of slice j's keys are computed
+// in one go by streaming over those later queries.
 //
-// CTA = 5 warps: warps 0..3 own one TMEM lane quarter each (one row per thread: softmax needs
-// no shuffles), warp 4 elects one thread that issues all TMA copies and MMAs.
+// Forward CTA = 5 warps: warps 0..3 own one TMEM lane quarter each (one row per thread: softmax
+// needs no shuffles), warp 4 elects one thread that issues all TMA copies and MMAs.
 #include <math.h>
 #include <string.h>
 
@@ -36,12 +34,10 @@ struct AttnParams {
   long long ld_o;
   float* lse2;          // [b*h][lse_stride], indexed by absolute position
   long long lse_stride;
-  const float* delta;   // bwd: [b*h][t] = rowsum(dO * O)
-  float* dkv_acc;       // [b*h][dkv_rows][2][D] fp32 (head-major: a CTA's key rows are contiguous)
-  long long dkv_rows;
+  float* delta;         // bwd: [b*h][lse_stride] = rowsum(dO * O), indexed by absolute position
+  int q_end;            // bwd: end (absolute position) of the rows already back-propagated
   void* dqkv;           // [t*b][ld_dqkv], same column order as qkv
   long long ld_dqkv;
-  int first;            // dK/dV: overwrite the accumulator instead of adding to it
   int* err;
 };
 
@@ -290,8 +286,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 // ============================================================================ delta = rowsum(dO * O)
 template <typename T>
 __global__ void attn_delta_kernel(const T* __restrict__ o, long long ld_o, const T* __restrict__ d_o,
-                                  long long ld_do, float* __restrict__ delta, int t, int b, int h,
-                                  int D) {
+                                  long long ld_do, float* __restrict__ delta,
+                                  long long delta_stride, int c, int t, int b, int h, int D) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= t * b * h) return;
@@ -308,56 +304,86 @@ __global__ void attn_delta_kernel(const T* __restrict__ o, long long ld_o, const
   }
 #pragma unroll
   for (int o2 = 16; o2 > 0; o2 >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o2);
-  if (lane == 0) delta[static_cast<long long>(bi * h + hi) * t + i] = acc;
+  if (lane == 0) delta[static_cast<long long>(bi * h + hi) * delta_stride + c + i] = acc;
 }
 
-// ============================================================================ backward: dK, dV
-template <typename T, int D>
-__global__ void __launch_bounds__(kAttnThreads, 1)
-attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmKV128,
-                     const __grid_constant__ CUtensorMap tmQ64,
-                     const __grid_constant__ CUtensorMap tmdO64, const AttnParams p) {
+// ============================================================================ backward
+// One streaming kernel, two modes (both deterministic, no floating-point atomics):
+//   MODE 0 (dK/dV): stationary = 128 keys of the current slice (K, V tiles); streams, in
+//     blocks of 64, the queries q >= k of this slice and of every later slice (Q and dO rows,
+//     which later slices left in the full-length buffers).  dK/dV of a key block are therefore
+//     complete when the CTA ends and are written once, as 16-bit values.
+//   MODE 1 (dQ): stationary = 128 queries of the current slice (Q, dO tiles); streams the keys
+//     k <= q (K, V tiles of 64 rows).
+// Per streamed block:  S = X1 Y1^T, dP = X2 Y2^T (TMEM, double buffered);
+//   P = exp2(S*scale2 - lse), dS = P (dP - delta)  -> 16-bit tiles in shared memory;
+//   MODE 0: dV += P^T-tile * dO, dK += dS^T-tile * Q;   MODE 1: dQ += dS * K.
+// 10 warps: two worker groups of 4 warps alternate over the streamed blocks (each owns one
+// S/dP buffer), warp 8 elects the TMA thread, warp 9 the MMA thread.
+constexpr int kBwdThreads = 320;
+constexpr int kBwdStages = 3;
+
+struct BwdShared {
+  uint64_t bar_x, bar_y[kBwdStages], bar_yfree[kBwdStages], bar_s[2], bar_sfree[2], bar_p[2],
+      bar_acc[2], bar_done;
+  float lse[2][2][64];
+  float delta[2][2][64];
+  uint32_t tmem_slot;
+  int abort_flag;
+};
+
+template <typename T, int D, int MODE>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
+                const __grid_constant__ CUtensorMap tmQKV64,
+                const __grid_constant__ CUtensorMap tmDO128,
+                const __grid_constant__ CUtensorMap tmDO64, const AttnParams p) {
   constexpr int DH = D / 64;
-  constexpr int kKSub = 128 * 128, kQSub = 64 * 128;
-  constexpr uint32_t kTmemCols = D == 128 ? 512 : 256;
+  constexpr int kXSub = 128 * 128, kYSub = 64 * 128;
+  constexpr int kStageBytes = 2 * DH * kYSub;
+  constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* sK = smem;
-  uint8_t* sV = sK + DH * kKSub;
-  uint8_t* sQ = sV + DH * kKSub;         // [2][DH][kQSub]
-  uint8_t* sdO = sQ + 2 * DH * kQSub;    // [2][DH][kQSub]
-  uint8_t* sPt = sdO + 2 * DH * kQSub;   // [128][128B]
-  uint8_t* sdSt = sPt + 128 * 128;
-  float* s_lse = reinterpret_cast<float*>(sdSt + 128 * 128);  // [2][64]
-  float* s_delta = s_lse + 128;                               // [2][64]
-  AttnShared* sh = reinterpret_cast<AttnShared*>(s_delta + 128);
-  uint64_t* bar_kv = &sh->bars[0];
-  uint64_t* bar_qdo = &sh->bars[1];  // [2]
-  uint64_t* bar_s = &sh->bars[3];
-  uint64_t* bar_p = &sh->bars[4];
-  uint64_t* bar_m2 = &sh->bars[5];
+  uint8_t* sX1 = smem;
+  uint8_t* sX2 = sX1 + DH * kXSub;
+  uint8_t* sY = sX2 + DH * kXSub;                 // [stages][Y1 | Y2][DH][kYSub]
+  uint8_t* sP = sY + kBwdStages * kStageBytes;    // [128][128B]
+  uint8_t* sdS = sP + 128 * 128;
+  BwdShared* sh = reinterpret_cast<BwdShared*>(sdS + 128 * 128);
 
   const int warp = threadIdx.x >> 5;
   const WaitCtx wctx{&sh->abort_flag, p.err};
-  const int k0 = blockIdx.x * 128;
   const int bh = blockIdx.y;
   const int bi = bh / p.h, hi = bh % p.h;
-  const int qb_start = (k0 > p.c ? (k0 - p.c) : 0) / 64;
-  const int nqb = (p.t + 63) / 64;
-  const int nit = nqb - qb_start;
+  const int x0 = p.c + blockIdx.x * 128;  // first stationary row (absolute position)
+  int ystart, n_iter;
+  if (MODE == 0) {
+    ystart = x0;
+    n_iter = (p.q_end - x0 + 63) / 64;
+  } else {
+    ystart = 0;
+    n_iter = (p.c + min(p.t, static_cast<int>(blockIdx.x) * 128 + 128) + 63) / 64;
+  }
 
   if (threadIdx.x == 0) {
-    mbar_init(bar_kv, 1);
-    mbar_init(&bar_qdo[0], 1);
-    mbar_init(&bar_qdo[1], 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_m2, 1);
+    mbar_init(&sh->bar_x, 1);
+    for (int i = 0; i < kBwdStages; ++i) {
+      mbar_init(&sh->bar_y[i], 1);
+      mbar_init(&sh->bar_yfree[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh->bar_s[i], 1);
+      mbar_init(&sh->bar_sfree[i], 128);
+      mbar_init(&sh->bar_p[i], 128);
+    }
+    mbar_init(&sh->bar_acc[0], 1);
+    mbar_init(&sh->bar_acc[1], 1);
+    mbar_init(&sh->bar_done, 1);
     sh->abort_flag = 0;
     fence_barrier_init();
   }
-  if (warp == 4) {
+  if (warp == 9) {
     tmem_alloc(&sh->tmem_slot, kTmemCols);
     tmem_relinquish();
   }
@@ -365,65 +391,96 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmKV128,
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_slot;
-  const uint32_t tSt = tmem, tdPt = tmem + 64, tdV = tmem + 128, tdK = tmem + 128 + D;
+  // columns: S[0] 0, S[1] 64, dP[0] 128, dP[1] 192, Acc1 256, Acc2 256 + D
+  const uint32_t tA1 = tmem + 256, tA2 = tmem + 256 + D;
 
-  if (warp == 4) {
+  if (warp == 8) {
+    if (elect_one()) {
+      mbar_expect_tx(&sh->bar_x, 2 * DH * kXSub);
+      for (int hh = 0; hh < DH; ++hh) {
+        if (MODE == 0) {
+          tma_load_3d(sX1 + hh * kXSub, &tmQKV128, &sh->bar_x, D + hh * 64, bh, x0);
+          tma_load_3d(sX2 + hh * kXSub, &tmQKV128, &sh->bar_x, 2 * D + hh * 64, bh, x0);
+        } else {
+          tma_load_3d(sX1 + hh * kXSub, &tmQKV128, &sh->bar_x, hh * 64, bh, x0);
+          tma_load_3d(sX2 + hh * kXSub, &tmDO128, &sh->bar_x, hi * D + hh * 64, bi, x0);
+        }
+      }
+      for (int i = 0; i < n_iter; ++i) {
+        const int st = i % kBwdStages;
+        if (!mbar_wait(&sh->bar_yfree[st], ((i / kBwdStages) & 1) ^ 1, wctx, kErrWaitAttn)) break;
+        uint8_t* y1 = sY + st * kStageBytes;
+        uint8_t* y2 = y1 + DH * kYSub;
+        const int y0 = ystart + i * 64;
+        mbar_expect_tx(&sh->bar_y[st], kStageBytes);
+        for (int hh = 0; hh < DH; ++hh) {
+          if (MODE == 0) {
+            tma_load_3d(y1 + hh * kYSub, &tmQKV64, &sh->bar_y[st], hh * 64, bh, y0);
+            tma_load_3d(y2 + hh * kYSub, &tmDO64, &sh->bar_y[st], hi * D + hh * 64, bi, y0);
+          } else {
+            tma_load_3d(y1 + hh * kYSub, &tmQKV64, &sh->bar_y[st], D + hh * 64, bh, y0);
+            tma_load_3d(y2 + hh * kYSub, &tmQKV64, &sh->bar_y[st], 2 * D + hh * 64, bh, y0);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_f16(Elem<T>::fmt, 0, 0, 128, 64);
       constexpr uint32_t idesc_g = umma_idesc_f16(Elem<T>::fmt, 0, 1, 128, D);
-      mbar_expect_tx(bar_kv, 2 * DH * kKSub);
-      for (int hh = 0; hh < DH; ++hh) {
-        tma_load_3d(sK + hh * kKSub, &tmKV128, bar_kv, D + hh * 64, bh, k0);
-        tma_load_3d(sV + hh * kKSub, &tmKV128, bar_kv, 2 * D + hh * 64, bh, k0);
-      }
-      auto load_q = [&](int qb, int st) {
-        mbar_expect_tx(&bar_qdo[st], 2 * DH * kQSub);
-        for (int hh = 0; hh < DH; ++hh) {
-          tma_load_3d(sQ + (st * DH + hh) * kQSub, &tmQ64, &bar_qdo[st], hh * 64, bh,
-                      p.c + qb * 64);
-          tma_load_3d(sdO + (st * DH + hh) * kQSub, &tmdO64, &bar_qdo[st], hi * D + hh * 64, bi,
-                      qb * 64);
-        }
+      bool ok = mbar_wait(&sh->bar_x, 0, wctx, kErrWaitAttn);
+      auto issue_acc = [&](int j) -> bool {
+        if (!mbar_wait(&sh->bar_p[j & 1], (j >> 1) & 1, wctx, kErrWaitAttn)) return false;
+        tc_fence_after();
+        const int st = j % kBwdStages;
+        const uint32_t y1 = smem_u32(sY + st * kStageBytes);
+        const uint32_t y2 = y1 + DH * kYSub;
+        if (MODE == 0) mma_kn(tA1, smem_u32(sP), y2, kYSub, idesc_g, j > 0);
+        mma_kn(tA2, smem_u32(sdS), y1, kYSub, idesc_g, j > 0);
+        umma_commit(&sh->bar_yfree[st]);
+        umma_commit(&sh->bar_acc[j & 1]);
+        return true;
       };
-      load_q(qb_start, 0);
-      bool ok = mbar_wait(bar_kv, 0, wctx, kErrWaitAttn);
-      for (int it = 0; it < nit && ok; ++it) {
-        const int st = it & 1;
-        if (it + 1 < nit) load_q(qb_start + it + 1, st ^ 1);
-        ok = mbar_wait(&bar_qdo[st], (it >> 1) & 1, wctx, kErrWaitAttn);
+      for (int i = 0; i < n_iter && ok; ++i) {
+        const int st = i % kBwdStages, buf = i & 1;
+        ok = mbar_wait(&sh->bar_y[st], (i / kBwdStages) & 1, wctx, kErrWaitAttn) &&
+             mbar_wait(&sh->bar_sfree[buf], ((i >> 1) & 1) ^ 1, wctx, kErrWaitAttn);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t q_base = smem_u32(sQ + st * DH * kQSub);
-        const uint32_t do_base = smem_u32(sdO + st * DH * kQSub);
-        mma_kk<DH>(tSt, smem_u32(sK), kKSub, q_base, kQSub, idesc_s);
-        mma_kk<DH>(tdPt, smem_u32(sV), kKSub, do_base, kQSub, idesc_s);
-        umma_commit(bar_s);
-        ok = mbar_wait(bar_p, it & 1, wctx, kErrWaitAttn);
-        if (!ok) break;
-        tc_fence_after();
-        mma_kn(tdV, smem_u32(sPt), do_base, kQSub, idesc_g, it > 0);
-        mma_kn(tdK, smem_u32(sdSt), q_base, kQSub, idesc_g, it > 0);
-        umma_commit(bar_m2);
-        ok = mbar_wait(bar_m2, it & 1, wctx, kErrWaitAttn);
+        const uint32_t y1 = smem_u32(sY + st * kStageBytes);
+        const uint32_t y2 = y1 + DH * kYSub;
+        mma_kk<DH>(tmem + buf * 64, smem_u32(sX1), kXSub, y1, kYSub, idesc_s);
+        mma_kk<DH>(tmem + 128 + buf * 64, smem_u32(sX2), kXSub, y2, kYSub, idesc_s);
+        umma_commit(&sh->bar_s[buf]);
+        if (i >= 1) ok = issue_acc(i - 1);
       }
+      if (ok && n_iter > 0) ok = issue_acc(n_iter - 1);
+      if (ok) umma_commit(&sh->bar_done);
     }
   } else {
-    const int r = threadIdx.x;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int kpos = k0 + r;
+    const int grp = warp >> 2;                 // worker group 0 / 1
+    const int r = threadIdx.x & 127;           // row of the stationary tile = TMEM lane
+    const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const int xabs = x0 + r;                   // absolute position of this thread's row
+    const bool x_ok = xabs < p.c + p.t;
+    float lse_r = 0.0f, delta_r = 0.0f;
+    if (MODE == 1 && x_ok) {
+      lse_r = p.lse2[static_cast<long long>(bh) * p.lse_stride + xabs];
+      delta_r = p.delta[static_cast<long long>(bh) * p.lse_stride + xabs];
+    }
     bool ok = true;
-    for (int it = 0; it < nit; ++it) {
-      const int st = it & 1;
-      const int qb = qb_start + it;
-      {
-        const int qi = qb * 64 + (r & 63);
-        if (r < 64)
-          s_lse[st * 64 + r] = qi < p.t ? p.lse2[static_cast<long long>(bh) * p.lse_stride + p.c + qi] : 0.0f;
-        else
-          s_delta[st * 64 + (r - 64)] = qi < p.t ? p.delta[static_cast<long long>(bh) * p.t + qi] : 0.0f;
+    for (int i = grp; i < n_iter; i += 2) {
+      const int y0 = ystart + i * 64;
+      const int lb = (i >> 1) & 1;
+      if (MODE == 0) {
+        const int yi = y0 + (r & 63);
+        const bool in = yi < p.q_end;
+        const long long off = static_cast<long long>(bh) * p.lse_stride + yi;
+        if (r < 64) sh->lse[grp][lb][r] = in ? p.lse2[off] : 0.0f;
+        else sh->delta[grp][lb][r - 64] = in ? p.delta[off] : 0.0f;
+        named_bar_sync(1 + grp, 128);  // reached in every iteration, aborted or not
       }
-      named_bar_sync(1, 128);  // every worker reaches this in every iteration, aborted or not
-      if (ok) ok = mbar_wait(bar_s, it & 1, wctx, kErrWaitAttn);
+      if (ok) ok = mbar_wait(&sh->bar_s[grp], (i >> 1) & 1, wctx, kErrWaitAttn);
       if (!ok) continue;
       tc_fence_after();
       float sv[64], dv[64];
@@ -432,235 +489,74 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmKV128,
         __syncwarp();
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          tmem_ld_32x32(tSt + lane_base + half * 32, raw);
+          tmem_ld_32x32(tmem + grp * 64 + lane_base + half * 32, raw);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) sv[half * 32 + i] = __uint_as_float(raw[i]);
-          tmem_ld_32x32(tdPt + lane_base + half * 32, raw);
+          for (int k = 0; k < 32; ++k) sv[half * 32 + k] = __uint_as_float(raw[k]);
+          tmem_ld_32x32(tmem + 128 + grp * 64 + lane_base + half * 32, raw);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) dv[half * 32 + i] = __uint_as_float(raw[i]);
+          for (int k = 0; k < 32; ++k) dv[half * 32 + k] = __uint_as_float(raw[k]);
         }
       }
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const int qi = qb * 64 + i;
-        const bool valid = (qi < p.t) && (kpos <= p.c + qi);
-        const float pr = valid ? exp2f(sv[i] * p.scale2 - s_lse[st * 64 + i]) : 0.0f;
-        sv[i] = pr;
-        dv[i] = pr * (dv[i] - s_delta[st * 64 + i]);
-      }
-      store_row64<T>(sPt, r, sv);
-      store_row64<T>(sdSt, r, dv);
-      fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bar_p);
-    }
-    if (ok && nit > 0) ok = mbar_wait(bar_m2, (nit - 1) & 1, wctx, kErrWaitAttn);
-    if (ok && nit > 0) {
-      tc_fence_after();
-      const bool row_ok = kpos < p.c + p.t;
-      const bool final_row = kpos >= p.c;
-      float* acc = p.dkv_acc + (static_cast<long long>(bh) * p.dkv_rows + kpos) * 2 * D;
-      T* drow = static_cast<T*>(p.dqkv) +
-                (static_cast<long long>(kpos - p.c) * p.b + bi) * p.ld_dqkv + hi * 3 * D;
-#pragma unroll 1
-      for (int which = 0; which < 2; ++which) {  // 0: dK (scaled), 1: dV
-        const uint32_t tsrc = which == 0 ? tdK : tdV;
-        const float mul = which == 0 ? p.scale : 1.0f;
-#pragma unroll 1
-        for (int ch = 0; ch < D / 32; ++ch) {
-          uint32_t raw[32];
-          __syncwarp();
-          tmem_ld_32x32(tsrc + lane_base + ch * 32, raw);
-          tmem_ld_wait();
-          if (!row_ok) continue;
-          float* a = acc + which * D + ch * 32;
-          float4 oldv[8];
-          if (!p.first) {
+      mbar_arrive(&sh->bar_sfree[grp]);
 #pragma unroll
-            for (int g = 0; g < 8; ++g) oldv[g] = __ldcg(reinterpret_cast<const float4*>(a + g * 4));
-          }
-#pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float4 v = make_float4(__uint_as_float(raw[g * 4 + 0]) * mul, __uint_as_float(raw[g * 4 + 1]) * mul,
-                                   __uint_as_float(raw[g * 4 + 2]) * mul, __uint_as_float(raw[g * 4 + 3]) * mul);
-            if (!p.first) {
-              v.x += oldv[g].x; v.y += oldv[g].y; v.z += oldv[g].z; v.w += oldv[g].w;
-            }
-            if (final_row) {
-              uint2 u;
-              u.x = Elem<T>::pack2(v.x, v.y);
-              u.y = Elem<T>::pack2(v.z, v.w);
-              *reinterpret_cast<uint2*>(drow + (1 + which) * D + ch * 32 + g * 4) = u;
-            } else {
-              __stcg(reinterpret_cast<float4*>(a + g * 4), v);
-            }
-          }
+      for (int k = 0; k < 64; ++k) {
+        const int yabs = y0 + k;
+        float pr;
+        if (MODE == 0) {
+          const bool valid = (yabs < p.q_end) && (xabs <= yabs);
+          pr = valid ? exp2f(sv[k] * p.scale2 - sh->lse[grp][lb][k]) : 0.0f;
+          dv[k] = pr * (dv[k] - sh->delta[grp][lb][k]);
+        } else {
+          const bool valid = x_ok && (yabs <= xabs);
+          pr = valid ? exp2f(sv[k] * p.scale2 - lse_r) : 0.0f;
+          dv[k] = pr * (dv[k] - delta_r);
         }
+        sv[k] = pr;
       }
-    }
-  }
-
-  tc_fence_before();
-  __syncthreads();
-  if (sh->abort_flag) {
-    const unsigned long long t0 = globaltimer_ns();
-    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
-  }
-  tc_fence_after();
-  if (warp == 4) tmem_dealloc(tmem, kTmemCols);
-}
-
-// ============================================================================ backward: dQ
-template <typename T, int D>
-__global__ void __launch_bounds__(kAttnThreads, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128,
-                   const __grid_constant__ CUtensorMap tmKV64,
-                   const __grid_constant__ CUtensorMap tmdO128, const AttnParams p) {
-  constexpr int DH = D / 64;
-  constexpr int kQSub = 128 * 128, kKSub = 64 * 128;
-  constexpr uint32_t kTmemCols = D == 128 ? 256 : 256;
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
-  uint8_t* sQ = smem;
-  uint8_t* sdO = sQ + DH * kQSub;
-  uint8_t* sK = sdO + DH * kQSub;       // [2][DH][kKSub]
-  uint8_t* sV = sK + 2 * DH * kKSub;    // [2][DH][kKSub]
-  uint8_t* sdS = sV + 2 * DH * kKSub;   // [128][128B]
-  AttnShared* sh = reinterpret_cast<AttnShared*>(sdS + 128 * 128);
-  uint64_t* bar_q = &sh->bars[0];
-  uint64_t* bar_kv = &sh->bars[1];  // [2]
-  uint64_t* bar_s = &sh->bars[3];
-  uint64_t* bar_p = &sh->bars[4];
-  uint64_t* bar_m2 = &sh->bars[5];
-
-  const int warp = threadIdx.x >> 5;
-  const WaitCtx wctx{&sh->abort_flag, p.err};
-  const int q0 = blockIdx.x * 128;
-  const int bh = blockIdx.y;
-  const int bi = bh / p.h, hi = bh % p.h;
-  const int q_hi = min(p.t, q0 + 128);
-  const int nkb = (p.c + q_hi + 63) / 64;
-
-  if (threadIdx.x == 0) {
-    mbar_init(bar_q, 1);
-    mbar_init(&bar_kv[0], 1);
-    mbar_init(&bar_kv[1], 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_m2, 1);
-    sh->abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 4) {
-    tmem_alloc(&sh->tmem_slot, kTmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem = sh->tmem_slot;
-  const uint32_t tS = tmem, tdP = tmem + 64, tdQ = tmem + 128;
-
-  if (warp == 4) {
-    if (elect_one()) {
-      constexpr uint32_t idesc_s = umma_idesc_f16(Elem<T>::fmt, 0, 0, 128, 64);
-      constexpr uint32_t idesc_g = umma_idesc_f16(Elem<T>::fmt, 0, 1, 128, D);
-      mbar_expect_tx(bar_q, 2 * DH * kQSub);
-      for (int hh = 0; hh < DH; ++hh) {
-        tma_load_3d(sQ + hh * kQSub, &tmQ128, bar_q, hh * 64, bh, p.c + q0);
-        tma_load_3d(sdO + hh * kQSub, &tmdO128, bar_q, hi * D + hh * 64, bi, q0);
-      }
-      auto load_kv = [&](int j, int st) {
-        mbar_expect_tx(&bar_kv[st], 2 * DH * kKSub);
-        for (int hh = 0; hh < DH; ++hh) {
-          tma_load_3d(sK + (st * DH + hh) * kKSub, &tmKV64, &bar_kv[st], D + hh * 64, bh, j * 64);
-          tma_load_3d(sV + (st * DH + hh) * kKSub, &tmKV64, &bar_kv[st], 2 * D + hh * 64, bh, j * 64);
-        }
-      };
-      load_kv(0, 0);
-      bool ok = mbar_wait(bar_q, 0, wctx, kErrWaitAttn);
-      for (int j = 0; j < nkb && ok; ++j) {
-        const int st = j & 1;
-        if (j + 1 < nkb) load_kv(j + 1, st ^ 1);
-        ok = mbar_wait(&bar_kv[st], (j >> 1) & 1, wctx, kErrWaitAttn);
-        if (!ok) break;
-        tc_fence_after();
-        const uint32_t k_base = smem_u32(sK + st * DH * kKSub);
-        const uint32_t v_base = smem_u32(sV + st * DH * kKSub);
-        mma_kk<DH>(tS, smem_u32(sQ), kQSub, k_base, kKSub, idesc_s);
-        mma_kk<DH>(tdP, smem_u32(sdO), kQSub, v_base, kKSub, idesc_s);
-        umma_commit(bar_s);
-        ok = mbar_wait(bar_p, j & 1, wctx, kErrWaitAttn);
-        if (!ok) break;
-        tc_fence_after();
-        mma_kn(tdQ, smem_u32(sdS), k_base, kKSub, idesc_g, j > 0);
-        umma_commit(bar_m2);
-        ok = mbar_wait(bar_m2, j & 1, wctx, kErrWaitAttn);
-      }
-    }
-  } else {
-    const int r = threadIdx.x;
-    const uint32_t lane_base = static_cast<uint32_t>(warp * 32) << 16;
-    const int qi = q0 + r;
-    const int qpos = p.c + qi;
-    const bool q_ok = qi < p.t;
-    const float lse_r = q_ok ? p.lse2[static_cast<long long>(bh) * p.lse_stride + qpos] : 0.0f;
-    const float delta_r = q_ok ? p.delta[static_cast<long long>(bh) * p.t + qi] : 0.0f;
-    bool ok = true;
-    for (int j = 0; j < nkb; ++j) {
-      ok = mbar_wait(bar_s, j & 1, wctx, kErrWaitAttn);
-      if (!ok) break;
-      tc_fence_after();
-      float sv[64], dv[64];
-      {
-        uint32_t raw[32];
-        __syncwarp();
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_ld_32x32(tS + lane_base + half * 32, raw);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) sv[half * 32 + i] = __uint_as_float(raw[i]);
-          tmem_ld_32x32(tdP + lane_base + half * 32, raw);
-          tmem_ld_wait();
-#pragma unroll
-          for (int i = 0; i < 32; ++i) dv[half * 32 + i] = __uint_as_float(raw[i]);
-        }
-      }
-      const int kbase = j * 64;
-#pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        const bool valid = q_ok && (kbase + i <= qpos);
-        const float pr = valid ? exp2f(sv[i] * p.scale2 - lse_r) : 0.0f;
-        dv[i] = pr * (dv[i] - delta_r);
-      }
+      // the operand tiles are free once the accumulating MMAs of the previous block are done
+      if (i >= 1) ok = mbar_wait(&sh->bar_acc[(i - 1) & 1], ((i - 1) >> 1) & 1, wctx, kErrWaitAttn);
+      if (!ok) continue;
+      if (MODE == 0) store_row64<T>(sP, r, sv);
       store_row64<T>(sdS, r, dv);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bar_p);
+      mbar_arrive(&sh->bar_p[grp]);
     }
-    if (ok) ok = mbar_wait(bar_m2, (nkb - 1) & 1, wctx, kErrWaitAttn);
-    if (ok) {
+    if (ok && n_iter > 0) ok = mbar_wait(&sh->bar_done, 0, wctx, kErrWaitAttn);
+    if (ok && n_iter > 0) {
       tc_fence_after();
-      T* drow = static_cast<T*>(p.dqkv) + (static_cast<long long>(qi) * p.b + bi) * p.ld_dqkv + hi * 3 * D;
+      const long long out_row = (static_cast<long long>(xabs - p.c) * p.b + bi) * p.ld_dqkv + hi * 3 * D;
+      T* drow = static_cast<T*>(p.dqkv) + out_row;
+      uint32_t tsrc;
+      int col0, ncols, slot;
+      float mul;
+      if (MODE == 0) {   // group 0: dV (Acc1) -> v slot; group 1: dK (Acc2) * scale -> k slot
+        tsrc = grp == 0 ? tA1 : tA2;
+        col0 = 0; ncols = D; slot = grp == 0 ? 2 * D : D;
+        mul = grp == 0 ? 1.0f : p.scale;
+      } else {           // dQ (Acc2) * scale -> q slot, each group writes half of the columns
+        tsrc = tA2;
+        col0 = grp * (D / 2); ncols = D / 2; slot = 0;
+        mul = p.scale;
+      }
 #pragma unroll 1
-      for (int ch = 0; ch < D / 32; ++ch) {
+      for (int cc = col0; cc < col0 + ncols; cc += 32) {
         uint32_t raw[32];
         __syncwarp();
-        tmem_ld_32x32(tdQ + lane_base + ch * 32, raw);
+        tmem_ld_32x32(tsrc + lane_base + cc, raw);
         tmem_ld_wait();
-        if (q_ok) {
+        if (x_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 u;
-            u.x = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 0]) * p.scale, __uint_as_float(raw[g * 8 + 1]) * p.scale);
-            u.y = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 2]) * p.scale, __uint_as_float(raw[g * 8 + 3]) * p.scale);
-            u.z = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 4]) * p.scale, __uint_as_float(raw[g * 8 + 5]) * p.scale);
-            u.w = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 6]) * p.scale, __uint_as_float(raw[g * 8 + 7]) * p.scale);
-            *reinterpret_cast<uint4*>(drow + ch * 32 + g * 8) = u;
+            u.x = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 0]) * mul, __uint_as_float(raw[g * 8 + 1]) * mul);
+            u.y = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 2]) * mul, __uint_as_float(raw[g * 8 + 3]) * mul);
+            u.z = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 4]) * mul, __uint_as_float(raw[g * 8 + 5]) * mul);
+            u.w = Elem<T>::pack2(__uint_as_float(raw[g * 8 + 6]) * mul, __uint_as_float(raw[g * 8 + 7]) * mul);
+            __stcg(reinterpret_cast<uint4*>(drow + slot + cc + g * 8), u);
           }
         }
       }
@@ -674,7 +570,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ128,
     while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
   }
   tc_fence_after();
-  if (warp == 4) tmem_dealloc(tmem, kTmemCols);
+  if (warp == 9) tmem_dealloc(tmem, kTmemCols);
 }
 
 // ---------------------------------------------------------------------------- host side
@@ -700,8 +596,10 @@ template <typename K> static bool set_smem(K kern, int bytes) {
 }
 
 template <int D> constexpr int fwd_smem() { return (D / 64) * (128 * 128 + 2 * 64 * 128) + 128 * 128 + 1024 + 256; }
-template <int D> constexpr int dkdv_smem() { return (D / 64) * (2 * 128 * 128 + 4 * 64 * 128) + 2 * 128 * 128 + 1024 + 1024 + 256; }
-template <int D> constexpr int dq_smem() { return (D / 64) * (2 * 128 * 128 + 4 * 64 * 128) + 128 * 128 + 1024 + 256; }
+template <int D> constexpr int bwd_smem() {
+  return (D / 64) * (2 * 128 * 128 + kBwdStages * 2 * 64 * 128) + 2 * 128 * 128 + 1024 +
+         static_cast<int>(sizeof(BwdShared)) + 64;
+}
 
 template <typename T, int D>
 static int attn_fwd_launch(const void* qkv, const AttnParams& p, bool bf16, cudaStream_t s) {
@@ -718,33 +616,33 @@ static int attn_fwd_launch(const void* qkv, const AttnParams& p, bool bf16, cuda
 }
 
 template <typename T, int D>
-static int attn_bwd_launch(const void* qkv, const void* o, const void* d_o, long long ld_do,
-                           float* delta, const AttnParams& p, bool bf16, cudaStream_t s) {
+static int attn_bwd_launch(const void* qkv, const void* o, const void* do_full, long long ld_do,
+                           const AttnParams& p, bool bf16, cudaStream_t s) {
   CUtensorMap tm128, tm64, tmdO64, tmdO128;
-  if (!qkv_tmap(&tm128, qkv, D, p.b, p.h, p.c + p.t, 128, bf16) ||
-      !qkv_tmap(&tm64, qkv, D, p.b, p.h, p.c + p.t, 64, bf16) ||
-      !do_tmap(&tmdO64, d_o, ld_do, D, p.b, p.h, p.t, 64, bf16) ||
-      !do_tmap(&tmdO128, d_o, ld_do, D, p.b, p.h, p.t, 128, bf16))
+  if (!qkv_tmap(&tm128, qkv, D, p.b, p.h, p.q_end, 128, bf16) ||
+      !qkv_tmap(&tm64, qkv, D, p.b, p.h, p.q_end, 64, bf16) ||
+      !do_tmap(&tmdO64, do_full, ld_do, D, p.b, p.h, p.q_end, 64, bf16) ||
+      !do_tmap(&tmdO128, do_full, ld_do, D, p.b, p.h, p.q_end, 128, bf16))
     return kErrDriver;
   {
     const long long warps = static_cast<long long>(p.t) * p.b * p.h;
     const int threads = 256;
     const int blocks = static_cast<int>((warps * 32 + threads - 1) / threads);
-    attn_delta_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(o), p.ld_o,
-                                                    static_cast<const T*>(d_o), ld_do, delta, p.t,
-                                                    p.b, p.h, D);
+    const T* do_slice = static_cast<const T*>(do_full) + static_cast<long long>(p.c) * p.b * ld_do;
+    attn_delta_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(o), p.ld_o, do_slice,
+                                                    ld_do, p.delta, p.lse_stride, p.c, p.t, p.b,
+                                                    p.h, D);
   }
-  auto k1 = attn_bwd_dkdv_kernel<T, D>;
-  auto k2 = attn_bwd_dq_kernel<T, D>;
+  auto k0 = attn_bwd_kernel<T, D, 0>;
+  auto k1 = attn_bwd_kernel<T, D, 1>;
   static bool cfg = false;
   if (!cfg) {
-    if (!set_smem(k1, dkdv_smem<D>()) || !set_smem(k2, dq_smem<D>())) return kErrLaunch;
+    if (!set_smem(k0, bwd_smem<D>()) || !set_smem(k1, bwd_smem<D>())) return kErrLaunch;
     cfg = true;
   }
-  dim3 g1((p.c + p.t + 127) / 128, p.b * p.h);
-  k1<<<g1, kAttnThreads, dkdv_smem<D>(), s>>>(tm128, tm64, tmdO64, p);
-  dim3 g2((p.t + 127) / 128, p.b * p.h);
-  k2<<<g2, kAttnThreads, dq_smem<D>(), s>>>(tm128, tm64, tmdO128, p);
+  dim3 grid((p.t + 127) / 128, p.b * p.h);
+  k0<<<grid, kBwdThreads, bwd_smem<D>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
+  k1<<<grid, kBwdThreads, bwd_smem<D>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
@@ -778,22 +676,28 @@ extern "C" int tp_attn_fwd(int dtype, int D, const void* qkv, int b, int h, int 
               : attn_fwd_launch<__half, 64>(qkv, p, false, s);
 }
 
-// o / d_o: this slice's [t*b][ld] attention output and its gradient; delta: fp32 [b*h*t]
-// workspace; dkv_acc: persistent fp32 [b*h][dkv_rows][2][D] (dkv_rows >= c+t); dqkv: this slice's [t*b][ld_dqkv] output.
-extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int t, int c,
-                           const void* o, long long ld_o, const void* d_o, long long ld_do,
-                           const float* lse2, long long lse_stride, float* delta, float* dkv_acc,
-                           long long dkv_rows, void* dqkv, long long ld_dqkv, int first, int* err, void* stream) {
-  if ((D != 64 && D != 128) || t <= 0 || c < 0 || b <= 0 || h <= 0) return kErrBadArgument;
+// Backward of the slice [c, c+t).  The slices after it must already have been processed:
+//   o        this slice's attention output, [t*b][ld_o]
+//   do_full  full-length gradient of the attention output, [L*b][ld_do]; rows [c*b, q_end*b)
+//            are read (this slice's rows must have been written by the caller)
+//   lse2, delta   fp32 [b*h][lse_stride], indexed by absolute position; delta rows [c, c+t) are
+//            written here, rows [c+t, q_end) were written by the calls for the later slices
+//   dqkv     this slice's [t*b][ld_dqkv] output (same column order as qkv)
+extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int t, int c, int q_end,
+                           const void* o, long long ld_o, const void* do_full, long long ld_do,
+                           const float* lse2, long long lse_stride, float* delta, void* dqkv,
+                           long long ld_dqkv, int* err, void* stream) {
+  if ((D != 64 && D != 128) || t <= 0 || c < 0 || b <= 0 || h <= 0 || q_end < c + t)
+    return kErrBadArgument;
   if (ld_o % 8 || ld_do % 8 || ld_dqkv % 8) return kErrBadArgument;
   AttnParams p = base_params(D, b, h, t, c, err);
   p.o = const_cast<void*>(o); p.ld_o = ld_o;
   p.lse2 = const_cast<float*>(lse2); p.lse_stride = lse_stride;
-  p.delta = delta; p.dkv_acc = dkv_acc; p.dkv_rows = dkv_rows; p.dqkv = dqkv; p.ld_dqkv = ld_dqkv; p.first = first;
+  p.delta = delta; p.q_end = q_end; p.dqkv = dqkv; p.ld_dqkv = ld_dqkv;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == 1;
-  if (D == 128) return bf16 ? attn_bwd_launch<__nv_bfloat16, 128>(qkv, o, d_o, ld_do, delta, p, true, s)
-                            : attn_bwd_launch<__half, 128>(qkv, o, d_o, ld_do, delta, p, false, s);
-  return bf16 ? attn_bwd_launch<__nv_bfloat16, 64>(qkv, o, d_o, ld_do, delta, p, true, s)
-              : attn_bwd_launch<__half, 64>(qkv, o, d_o, ld_do, delta, p, false, s);
+  if (D == 128) return bf16 ? attn_bwd_launch<__nv_bfloat16, 128>(qkv, o, do_full, ld_do, p, true, s)
+                            : attn_bwd_launch<__half, 128>(qkv, o, do_full, ld_do, p, false, s);
+  return bf16 ? attn_bwd_launch<__nv_bfloat16, 64>(qkv, o, do_full, ld_do, p, true, s)
+              : attn_bwd_launch<__half, 64>(qkv, o, do_full, ld_do, p, false, s);
 }

@@ -47,32 +47,59 @@ template <typename T> __device__ __forceinline__ void store8(T* p, const float (
   *reinterpret_cast<uint4*>(p) = u;
 }
 
-// ------------------------------------------------------------------ LayerNorm forward
-// y = (x - mean) * rstd * gamma + beta, one CTA per row; each thread keeps NV vectors of 8.
-template <typename T, int NV>
-__global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
-                                     const T* __restrict__ beta, T* __restrict__ y,
-                                     float* __restrict__ mean_out, float* __restrict__ rstd_out,
-                                     int rows, int H, float eps) {
-  __shared__ float red[33];
-  const long long row = blockIdx.x;
-  const T* xr = x + row * H;
+// ------------------------------------------------------------------ LayerNorm
+// A row is handled by WPR warps; each lane keeps NV vectors of 8 consecutive elements, vector i
+// of lane l of warp w at column ((i * WPR + w) * 32 + l) * 8, so a warp reads 512 contiguous
+// bytes per vector.  A CTA of 8 warps (16 when WPR = 16) holds RPC = max(1, 8 / WPR) rows.
+template <int WPR> struct LnGeom {
+  static constexpr int kWarps = WPR > 8 ? WPR : 8;
+  static constexpr int kRowsPerCta = kWarps / WPR;
+  static constexpr int kThreads = kWarps * 32;
+};
+
+// Sum over the WPR warps of a row group; `red` is [2][kRowsPerCta][WPR] (ping-pong by `slot`).
+template <int WPR>
+__device__ __forceinline__ float group_sum(float v, float* red, int slot, int grp, int wr, int lane) {
+  v = warp_sum(v);
+  if (WPR == 1) return v;
+  float* r = red + (slot * LnGeom<WPR>::kRowsPerCta + grp) * WPR;
+  if (lane == 0) r[wr] = v;
+  __syncthreads();
+  float t = 0.0f;
+#pragma unroll
+  for (int i = 0; i < WPR; ++i) t += r[i];
+  return t;
+}
+
+template <typename T, int NV, int WPR>
+__global__ void __launch_bounds__(LnGeom<WPR>::kThreads)
+layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
+                     const T* __restrict__ beta, T* __restrict__ y, float* __restrict__ mean_out,
+                     float* __restrict__ rstd_out, int rows, int H, float eps) {
+  using G = LnGeom<WPR>;
+  __shared__ float red[2 * G::kRowsPerCta * WPR + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = warp / WPR, wr = warp % WPR;
+  const long long row = static_cast<long long>(blockIdx.x) * G::kRowsPerCta + grp;
+  const bool row_ok = row < rows;
   float v[NV][8];
   float s = 0.0f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int col = (threadIdx.x + i * blockDim.x) * 8;
-    if (col < H) {
-      load8(xr + col, v[i]);
+    const int col = ((i * WPR + wr) * 32 + lane) * 8;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    if (row_ok && col < H) {
+      load8(x + row * H + col, v[i]);
 #pragma unroll
       for (int j = 0; j < 8; ++j) s += v[i][j];
     }
   }
-  const float mean = block_sum(s, red) / H;
+  const float mean = group_sum<WPR>(s, red, 0, grp, wr, lane) / H;
   float q = 0.0f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int col = (threadIdx.x + i * blockDim.x) * 8;
+    const int col = ((i * WPR + wr) * 32 + lane) * 8;
     if (col < H) {
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
@@ -81,14 +108,15 @@ __global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_fwd_kernel(con
       }
     }
   }
-  const float rstd = rsqrtf(block_sum(q, red) / H + eps);
-  if (threadIdx.x == 0) {
+  const float rstd = rsqrtf(group_sum<WPR>(q, red, 1, grp, wr, lane) / H + eps);
+  if (!row_ok) return;
+  if (wr == 0 && lane == 0) {
     mean_out[row] = mean;
     rstd_out[row] = rstd;
   }
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
-    const int col = (threadIdx.x + i * blockDim.x) * 8;
+    const int col = ((i * WPR + wr) * 32 + lane) * 8;
     if (col < H) {
       float g[8], b[8], o[8];
       load8(gamma + col, g);
@@ -100,44 +128,41 @@ __global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_fwd_kernel(con
   }
 }
 
-// ------------------------------------------------------------------ LayerNorm backward
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ dres), g = dy * gamma.
-// Persistent CTAs stride over rows and keep per-column partial sums of dgamma = sum dy*xhat
-// and dbeta = sum dy in registers; partials go to `scratch[gridDim.x][2][H]` and a second
-// kernel folds them into the fp32 gradient accumulators.
-template <typename T, int NV, bool SMEM_PART>
-__global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
-                                     const float* __restrict__ mean, const float* __restrict__ rstd,
-                                     const T* __restrict__ gamma, const T* __restrict__ dres,
-                                     T* __restrict__ dx, float* __restrict__ scratch, int rows,
-                                     int H) {
-  // For wide rows the per-column partial sums live in shared memory (each thread touches only
-  // its own columns, so no synchronisation is needed); otherwise in registers.
-  extern __shared__ float part_smem[];
-  __shared__ float red[33];
-  constexpr int NP = SMEM_PART ? 1 : NV;
-  float pg[NP][8], pb[NP][8];
+// Persistent CTAs stride over rows; every lane keeps partial sums of dgamma = sum dy*xhat and
+// dbeta = sum dy for its own columns.  At the end the row groups of a CTA fold their partials
+// in a fixed order through shared memory and the CTA writes one slot of
+// scratch[gridDim.x][2][H]; a second kernel adds the slots into the fp32 gradients.
+template <typename T, int NV, int WPR>
+__global__ void __launch_bounds__(LnGeom<WPR>::kThreads)
+layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                     const float* __restrict__ mean, const float* __restrict__ rstd,
+                     const T* __restrict__ gamma, const T* __restrict__ dres, T* __restrict__ dx,
+                     float* __restrict__ scratch, int rows, int H) {
+  using G = LnGeom<WPR>;
+  extern __shared__ float part_smem[];  // [2][H]
+  __shared__ float red[2 * 2 * G::kRowsPerCta * WPR + 1];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int grp = warp / WPR, wr = warp % WPR;
+  float pg[NV][8], pb[NV][8];
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int col = (threadIdx.x + i * blockDim.x) * 8;
+  for (int i = 0; i < NV; ++i)
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      if (SMEM_PART) {
-        if (col < H) { part_smem[col + j] = 0.0f; part_smem[H + col + j] = 0.0f; }
-      } else {
-        pg[i % NP][j] = 0.0f;
-        pb[i % NP][j] = 0.0f;
-      }
-    }
-  }
-  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
-    const float mu = mean[row], rs = rstd[row];
+    for (int j = 0; j < 8; ++j) { pg[i][j] = 0.0f; pb[i][j] = 0.0f; }
+  int parity = 0;
+  for (long long base = static_cast<long long>(blockIdx.x) * G::kRowsPerCta; base < rows;
+       base += static_cast<long long>(gridDim.x) * G::kRowsPerCta, parity ^= 1) {
+    const long long row = base + grp;
+    const bool row_ok = row < rows;
+    const float mu = row_ok ? mean[row] : 0.0f, rs = row_ok ? rstd[row] : 0.0f;
     float xh[NV][8], g[NV][8];
     float s1 = 0.0f, s2 = 0.0f;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
-      const int col = (threadIdx.x + i * blockDim.x) * 8;
-      if (col < H) {
+      const int col = ((i * WPR + wr) * 32 + lane) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) { xh[i][j] = 0.0f; g[i][j] = 0.0f; }
+      if (row_ok && col < H) {
         float xv[8], dyv[8], gam[8];
         load8(x + row * H + col, xv);
         load8(dy + row * H + col, dyv);
@@ -148,58 +173,78 @@ __global__ void __launch_bounds__(NV == 1 ? 1024 : 768) layernorm_bwd_kernel(con
           g[i][j] = dyv[j] * gam[j];
           s1 += g[i][j];
           s2 += g[i][j] * xh[i][j];
-          if (SMEM_PART) {
-            part_smem[col + j] += dyv[j] * xh[i][j];
-            part_smem[H + col + j] += dyv[j];
-          } else {
-            pg[i % NP][j] += dyv[j] * xh[i][j];
-            pb[i % NP][j] += dyv[j];
+          pg[i][j] += dyv[j] * xh[i][j];
+          pb[i][j] += dyv[j];
+        }
+      }
+    }
+    const float m1 = group_sum<WPR>(s1, red, 2 * parity, grp, wr, lane) / H;
+    const float m2 = group_sum<WPR>(s2, red, 2 * parity + 1, grp, wr, lane) / H;
+    if (row_ok) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int col = ((i * WPR + wr) * 32 + lane) * 8;
+        if (col < H) {
+          float o[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - m1 - xh[i][j] * m2);
+          if (dres) {
+            float r[8];
+            load8(dres + row * H + col, r);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) o[j] += r[j];
+          }
+          store8(dx + row * H + col, o);
+        }
+      }
+    }
+  }
+  // fold the row groups of this CTA in order, then publish one slot
+#pragma unroll 1
+  for (int gsel = 0; gsel < G::kRowsPerCta; ++gsel) {
+    if (grp == gsel) {
+#pragma unroll
+      for (int i = 0; i < NV; ++i) {
+        const int col = ((i * WPR + wr) * 32 + lane) * 8;
+        if (col < H) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            if (gsel == 0) {
+              part_smem[col + j] = pg[i][j];
+              part_smem[H + col + j] = pb[i][j];
+            } else {
+              part_smem[col + j] += pg[i][j];
+              part_smem[H + col + j] += pb[i][j];
+            }
           }
         }
       }
     }
-    const float m1 = block_sum(s1, red) / H;
-    const float m2 = block_sum(s2, red) / H;
-#pragma unroll
-    for (int i = 0; i < NV; ++i) {
-      const int col = (threadIdx.x + i * blockDim.x) * 8;
-      if (col < H) {
-        float o[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = rs * (g[i][j] - m1 - xh[i][j] * m2);
-        if (dres) {
-          float r[8];
-          load8(dres + row * H + col, r);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) o[j] += r[j];
-        }
-        store8(dx + row * H + col, o);
-      }
-    }
+    __syncthreads();
   }
   float* sg = scratch + static_cast<long long>(blockIdx.x) * 2 * H;
-#pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int col = (threadIdx.x + i * blockDim.x) * 8;
-    if (col < H) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        sg[col + j] = SMEM_PART ? part_smem[col + j] : pg[i % NP][j];
-        sg[H + col + j] = SMEM_PART ? part_smem[H + col + j] : pb[i % NP][j];
-      }
-    }
-  }
+  for (int c = threadIdx.x * 4; c < 2 * H; c += blockDim.x * 4)
+    *reinterpret_cast<float4*>(sg + c) = *reinterpret_cast<const float4*>(part_smem + c);
 }
 
-// dgamma[c] += sum_p scratch[p][0][c]; dbeta[c] += sum_p scratch[p][1][c]
+// dgamma[c] += sum_p scratch[p][0][c]; dbeta[c] += sum_p scratch[p][1][c].
+// blockDim = (32, 8): 32 columns per CTA, 8 lanes over the slots, fixed-order tree in smem.
 __global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int parts, int H,
                                             float* __restrict__ dgamma, float* __restrict__ dbeta) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * H) return;
+  __shared__ float sm[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float s = 0.0f;
-  for (int p = 0; p < parts; ++p) s += scratch[static_cast<long long>(p) * 2 * H + c];
-  if (c < H) dgamma[c] += s;
-  else dbeta[c - H] += s;
+  if (c < 2 * H)
+    for (int p = threadIdx.y; p < parts; p += 8) s += scratch[static_cast<long long>(p) * 2 * H + c];
+  sm[threadIdx.y][threadIdx.x] = s;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < 2 * H) {
+    float t = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) t += sm[i][threadIdx.x];
+    if (c < H) dgamma[c] += t;
+    else dbeta[c - H] += t;
+  }
 }
 
 // ------------------------------------------------------------------ bias gradient
@@ -293,65 +338,88 @@ __global__ void fill_kernel(T* p, long long n, float value) {
 
 using namespace tp;
 
-static inline int ln_threads(int H, int nv) {
-  int t = (H / 8 + nv - 1) / nv;
-  t = (t + 31) / 32 * 32;
-  return t;
+// Geometry: the smallest power-of-two warps-per-row (<= 16) that keeps at most 4 vectors of 8
+// elements per lane.
+static inline bool ln_geometry(int H, int* nv, int* wpr) {
+  if (H % 8 || H <= 0) return false;
+  const int vecs = H / 8;
+  for (int w = 1; w <= 16; w *= 2) {
+    const int n = (vecs + 32 * w - 1) / (32 * w);
+    if (n <= 4) { *nv = n; *wpr = w; return true; }
+  }
+  return false;
 }
+
+#define TP_LN_DISPATCH_WPR(T, NV, CALL)                  \
+  switch (wpr) {                                          \
+    case 1: CALL(T, NV, 1); break;                        \
+    case 2: CALL(T, NV, 2); break;                        \
+    case 4: CALL(T, NV, 4); break;                        \
+    case 8: CALL(T, NV, 8); break;                        \
+    default: CALL(T, NV, 16); break;                      \
+  }
+#define TP_LN_DISPATCH(T, CALL)                           \
+  switch (nv) {                                           \
+    case 1: TP_LN_DISPATCH_WPR(T, 1, CALL) break;         \
+    case 2: TP_LN_DISPATCH_WPR(T, 2, CALL) break;         \
+    case 3: TP_LN_DISPATCH_WPR(T, 3, CALL) break;         \
+    default: TP_LN_DISPATCH_WPR(T, 4, CALL) break;        \
+  }
 
 extern "C" int tp_layernorm_fwd(int dtype, const void* x, const void* gamma, const void* beta,
                                 void* y, float* mean, float* rstd, int rows, int H, float eps,
                                 void* stream) {
   if (rows <= 0) return kOk;
-  if (H % 8 || H > 12288) return kErrBadArgument;
+  int nv, wpr;
+  if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int nv = H > 8192 ? 2 : 1;
-  const int threads = ln_threads(H, nv);
-#define LN_FWD(T, NV)                                                                         \
-  layernorm_fwd_kernel<T, NV><<<rows, threads, 0, s>>>(                                       \
-      static_cast<const T*>(x), static_cast<const T*>(gamma), static_cast<const T*>(beta),    \
-      static_cast<T*>(y), mean, rstd, rows, H, eps)
-  if (dtype == 1) { if (nv == 1) LN_FWD(__nv_bfloat16, 1); else LN_FWD(__nv_bfloat16, 2); }
-  else { if (nv == 1) LN_FWD(__half, 1); else LN_FWD(__half, 2); }
+#define LN_FWD(T, NV, WPR)                                                                       \
+  layernorm_fwd_kernel<T, NV, WPR>                                                               \
+      <<<(rows + LnGeom<WPR>::kRowsPerCta - 1) / LnGeom<WPR>::kRowsPerCta, LnGeom<WPR>::kThreads, \
+         0, s>>>(static_cast<const T*>(x), static_cast<const T*>(gamma),                         \
+                 static_cast<const T*>(beta), static_cast<T*>(y), mean, rstd, rows, H, eps)
+  if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_FWD) }
+  else { TP_LN_DISPATCH(__half, LN_FWD) }
 #undef LN_FWD
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
-// Number of row-partial slots the backward writes; scratch must hold parts * 2 * H floats.
+// Number of CTA slots the backward writes; scratch must hold parts * 2 * H floats.
 extern "C" int tp_layernorm_bwd_parts(int rows) {
-  const int cap = 2 * num_sms();
+  const int cap = num_sms();
   return rows < cap ? rows : cap;
 }
 
 namespace tp {
+template <typename K> static void ln_allow_smem(K kern) {
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
+}
+
 static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const float* mean,
                                 const float* rstd, const void* gamma, const void* dres, void* dx,
                                 float* dgamma, float* dbeta, float* scratch, int rows, int H,
                                 cudaStream_t s) {
   if (rows <= 0) return kOk;
-  if (H % 8 || H > 12288) return kErrBadArgument;
-  const int nv = H > 8192 ? 2 : 1;
-  const int threads = ln_threads(H, nv);
-  const int parts = tp_layernorm_bwd_parts(rows);
-#define LN_BWD(T, NV, SP)                                                                      \
-  layernorm_bwd_kernel<T, NV, SP><<<parts, threads, (SP) ? 2 * H * sizeof(float) : 0, s>>>(    \
-      static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                         \
-      static_cast<const T*>(gamma), static_cast<const T*>(dres), static_cast<T*>(dx), scratch, \
-      rows, H)
-  if (nv == 2) {
-    static bool attr_set = false;
-    if (!attr_set) {
-      cudaFuncSetAttribute(layernorm_bwd_kernel<__half, 2, true>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
-      cudaFuncSetAttribute(layernorm_bwd_kernel<__nv_bfloat16, 2, true>,
-                           cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
-      attr_set = true;
-    }
+  int nv, wpr;
+  if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
+  const int rpc = wpr >= 8 ? 1 : 8 / wpr;
+  int parts = (rows + rpc - 1) / rpc;
+  const int cap = tp_layernorm_bwd_parts(rows);
+  if (parts > cap) parts = cap;
+  const size_t smem = static_cast<size_t>(2) * H * sizeof(float);
+#define LN_BWD(T, NV, WPR)                                                                      \
+  {                                                                                             \
+    auto kern = layernorm_bwd_kernel<T, NV, WPR>;                                               \
+    if (smem > 48 * 1024) ln_allow_smem(kern);                                                  \
+    kern<<<parts, LnGeom<WPR>::kThreads, smem, s>>>(                                            \
+        static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                        \
+        static_cast<const T*>(gamma), static_cast<const T*>(dres), static_cast<T*>(dx), scratch, \
+        rows, H);                                                                               \
   }
-  if (dtype == 1) { if (nv == 1) LN_BWD(__nv_bfloat16, 1, false); else LN_BWD(__nv_bfloat16, 2, true); }
-  else { if (nv == 1) LN_BWD(__half, 1, false); else LN_BWD(__half, 2, true); }
+  if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_BWD) }
+  else { TP_LN_DISPATCH(__half, LN_BWD) }
 #undef LN_BWD
-  layernorm_bwd_reduce_kernel<<<(2 * H + 255) / 256, 256, 0, s>>>(scratch, parts, H, dgamma, dbeta);
+  layernorm_bwd_reduce_kernel<<<(2 * H + 31) / 32, dim3(32, 8), 0, s>>>(scratch, parts, H, dgamma, dbeta);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 }  // namespace tp

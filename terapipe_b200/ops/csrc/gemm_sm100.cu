@@ -199,16 +199,36 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld_wait();
         const int n = n0 + c0;
         if (!row_ok || n >= p.N) continue;
+        // Issue every global load of this 32-column chunk before any dependent math or store,
+        // so the chunk pays one memory latency instead of one per 8-column group.
+        bool gok[4];
+        uint4 bv[4], rv[4], av[4];
+        float4 cv[8];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int ng = n + g * 8;
+          gok[g] = ng + 8 <= p.N;
+          if (!gok[g]) continue;
+          if (p.bias) bv[g] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + ng));
+          if (p.residual)
+            rv[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + ng));
+          if (p.dact)
+            av[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) + row * p.ld_aux + ng));
+          if (OUT_F32 && p.accumulate) {
+            const float4* o = reinterpret_cast<const float4*>(static_cast<const float*>(p.out) + row * p.ldo + ng);
+            cv[2 * g] = __ldcg(o);
+            cv[2 * g + 1] = __ldcg(o + 1);
+          }
+        }
 #pragma unroll
         for (int g = 0; g < 4; ++g) {  // groups of 8 columns
           const int ng = n + g * 8;
-          if (ng + 8 > p.N) break;
+          if (!gok[g]) continue;
           float v[8];
 #pragma unroll
           for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
           if (p.bias) {
-            const uint4 bv = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + ng));
-            const uint32_t bw[4] = {bv.x, bv.y, bv.z, bv.w};
+            const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 f = Elem<T>::unpack2(bw[j]);
@@ -223,7 +243,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
               zv.y = Elem<T>::pack2(v[2], v[3]);
               zv.z = Elem<T>::pack2(v[4], v[5]);
               zv.w = Elem<T>::pack2(v[6], v[7]);
-              *reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + ng) = zv;
+              __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + ng), zv);
             }
 #pragma unroll
             for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j]);
@@ -232,9 +252,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
           }
           if (p.residual) {
-            const uint4 rv = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) +
-                                                             row * p.ldr + ng);
-            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+            const uint32_t rw[4] = {rv[g].x, rv[g].y, rv[g].z, rv[g].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 f = Elem<T>::unpack2(rw[j]);
@@ -243,9 +261,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
           }
           if (p.dact) {
-            const uint4 av = *reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) +
-                                                             row * p.ld_aux + ng);
-            const uint32_t aw[4] = {av.x, av.y, av.z, av.w};
+            const uint32_t aw[4] = {av[g].x, av[g].y, av[g].z, av[g].w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
               const float2 f = Elem<T>::unpack2(aw[j]);
@@ -263,19 +279,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
             float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
             if (p.accumulate) {
-              const float4 c0v = o[0], c1v = o[1];
+              const float4 c0v = cv[2 * g], c1v = cv[2 * g + 1];
               o0.x += c0v.x; o0.y += c0v.y; o0.z += c0v.z; o0.w += c0v.w;
               o1.x += c1v.x; o1.y += c1v.y; o1.z += c1v.z; o1.w += c1v.w;
             }
-            o[0] = o0;
-            o[1] = o1;
+            __stcg(o, o0);
+            __stcg(o + 1, o1);
           } else {
             uint4 ov;
             ov.x = Elem<T>::pack2(v[0], v[1]);
             ov.y = Elem<T>::pack2(v[2], v[3]);
             ov.z = Elem<T>::pack2(v[4], v[5]);
             ov.w = Elem<T>::pack2(v[6], v[7]);
-            *reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.ldo + ng) = ov;
+            __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.ldo + ng), ov);
           }
         }
       }

@@ -148,19 +148,19 @@ def attn_fwd(qkv, b: int, h: int, D: int, t: int, c: int, o, lse2):
     return o
 
 
-def attn_bwd(qkv, b: int, h: int, D: int, t: int, c: int, o, d_o, lse2, delta, dkv_acc, dqkv,
-             first: bool):
+def attn_bwd(qkv, b: int, h: int, D: int, t: int, c: int, q_end: int, o, do_full, lse2, delta,
+             dqkv):
     """Slice-causal attention backward for the slice ``[c, c+t)``.
 
-    Adds this slice's dK/dV for all ``c+t`` visible positions into ``dkv_acc`` (fp32
-    ``[b*h, L, 2*D]``; overwritten instead when ``first``, i.e. for the last slice of the
-    sequence, which is the first one processed) and writes the slice's final
-    ``d(qkv)`` ``[t*b, h*3*D]``.  ``delta`` is an fp32 workspace of ``b*h*t`` elements."""
-    assert delta.numel() >= b * h * t
-    st = cuda_lib().tp_attn_bwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, o.data_ptr(), o.stride(0),
-                                d_o.data_ptr(), d_o.stride(0), lse2.data_ptr(), lse2.stride(0),
-                                delta.data_ptr(), dkv_acc.data_ptr(), dkv_acc.shape[1], dqkv.data_ptr(),
-                                dqkv.stride(0), int(first), status_word(qkv.device).data_ptr(),
-                                _stream())
+    Slices are processed last to first.  ``do_full`` is the full-length gradient of the
+    attention output ``[L*b, h*D]``: rows of the slices after this one (up to position
+    ``q_end``) were written by their own backward, rows ``[c*b, (c+t)*b)`` by the caller just
+    before this call.  ``o`` is this slice's forward output ``[t*b, h*D]``; ``lse2`` and
+    ``delta`` are fp32 ``[b*h, L]`` (``delta`` rows of this slice are written here).
+    Writes the slice's complete ``d(qkv)`` ``[t*b, h*3*D]``."""
+    st = cuda_lib().tp_attn_bwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, q_end, o.data_ptr(),
+                                o.stride(0), do_full.data_ptr(), do_full.stride(0),
+                                lse2.data_ptr(), lse2.stride(0), delta.data_ptr(), dqkv.data_ptr(),
+                                dqkv.stride(0), status_word(qkv.device).data_ptr(), _stream())
     check(st, "tp_attn_bwd")
     return dqkv

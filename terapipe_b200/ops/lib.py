@@ -67,7 +67,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "tp_fused_adam": [I, P, P, P, P, P, L, P, F, F, F, F, F, F, P],
         "tp_fill": [I, P, L, F, P],
         "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
-        "tp_attn_bwd": [I, I, P, I, I, I, I, P, L, P, L, P, L, P, P, L, P, L, I, P, P],
+        "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
     }
     for name, argtypes in sigs.items():
         if hasattr(lib, name):

@@ -8,8 +8,15 @@ What one rank owns
 * Full-length activation buffers ``[L*B, width]`` per layer.  A token slice is a contiguous
   row range, so the "KV cache" is simply the QKV projection buffer: slice *j* writes rows
   ``[c, c+t)`` and attends over rows ``[0, c+t)`` in place.
-* A persistent fp32 ``dK/dV`` accumulator per layer that carries gradients from later
-  slices back to earlier ones while the backward pass walks the slices in reverse.
+* Full-length gradient buffers per layer (``d`` of the layer output, of the post-attention
+  stream, of the FFN pre-activation, of QKV and of the attention output).  They serve two
+  purposes.  (1) The backward pass walks the slices in reverse, so when slice *j* runs, the
+  attention-output gradients of all later slices are still there and ``dK/dV`` of slice
+  *j*'s keys are computed in one pass over those later queries: no accumulator crosses
+  slices.  (2) Weight gradients are not computed per slice but once per layer over all
+  ``L*B`` rows after the last slice (one long-K GEMM per weight instead of one short
+  read-modify-write GEMM per slice); in a pipeline this also takes the weight-gradient work
+  off the inter-stage critical path.
 
 Schedule (same as the reference, test_transformer_terapipe.py:107-175,270-287): for each
 batch slice all token slices forward in order; backward visits batch slices and token
@@ -125,10 +132,11 @@ class StageEngine:
         self.step_count = 0
         self._streams_ready = False
         # launches of this library's own kernels (NCCL and torch kernels are not counted):
-        # per layer and slice 7 forward (2 LN, 4 GEMM, attention) and 19 backward (8 GEMM,
-        # 4 bias column sums, 2x2 LN, 3 attention), plus 2 for the optimizer
+        # per layer and slice 7 forward (2 LN, 4 GEMM, attention) and 11 backward (4 GEMM,
+        # 2x2 LN, 3 attention); per layer 8 for the weight gradients (4 GEMM, 4 bias column
+        # sums); plus 2 for the optimizer
         n_slices = len(self.batch_slices) * len(self.seq_slices)
-        self.launches_per_step = n_slices * self.n_layers * 26 + 2
+        self.launches_per_step = n_slices * self.n_layers * 18 + self.n_layers * 8 + 2
         self.launch_count = 0
 
     # ------------------------------------------------------------------ parameters
@@ -219,24 +227,26 @@ class StageEngine:
         self.stats = [torch.empty(4, rows, dtype=torch.float32, device=dev) for _ in range(self.n_layers)]
         self.lse = [torch.empty(self.B * self.h, self.L, dtype=torch.float32, device=dev)
                     for _ in range(self.n_layers)]
-        self.dkv = [buf(2 * Hl, torch.float32) for _ in range(self.n_layers)]
-        self.dY = buf(H) if not self.is_last else None     # gradients received from the next stage
-        self.dX0 = buf(H) if not self.is_first else None   # gradients sent to the previous stage
+        self.delta = [torch.empty(self.B * self.h, self.L, dtype=torch.float32, device=dev)
+                      for _ in range(self.n_layers)]
+        # gradients, full length (see the module docstring)
+        self.dMid = [buf(H) for _ in range(self.n_layers)]
+        self.dFc = [buf(Fl) for _ in range(self.n_layers)]
+        self.dQKV = [buf(3 * Hl) for _ in range(self.n_layers)]
+        self.dAO = [buf(Hl) for _ in range(self.n_layers)]
+        self.dXo = [buf(H) for _ in range(self.n_layers)]   # d(layer output); the last one is
+        self.dY = self.dXo[-1] if self.n_layers else None    # received from the next stage
+        self.dX0 = buf(H) if not self.is_first else None    # gradients sent to the previous stage
         tmax = max(self.seq_slices) * max(self.batch_slices)
         self.tmax = tmax
-
-        def scratch(width, dtype=dt):
-            return torch.empty(tmax, width, dtype=dtype, device=dev)
-
-        self.dA, self.dB, self.dln = scratch(H), scratch(H), scratch(H)
-        self.dfc, self.dao, self.dqkv = scratch(Fl), scratch(Hl), scratch(3 * Hl)
-        self.delta = torch.empty(max(self.batch_slices) * self.h * max(self.seq_slices),
-                                 dtype=torch.float32, device=dev)
+        self.dA = torch.empty(tmax, H, dtype=dt, device=dev)
+        self.dln = torch.empty(tmax, H, dtype=dt, device=dev)
         self.ln_scratch = torch.empty(F.layernorm_bwd_scratch_floats(tmax, H), dtype=torch.float32,
                                       device=dev)
         numel = self.L * self.B * H
-        self.dy_seed = torch.full((tmax, H), self.loss_scale / numel, dtype=dt, device=dev) \
-            if self.is_last else None
+        if self.is_last and self.n_layers:
+            # loss = mean(output): the seed gradient is the same constant everywhere
+            self.dXo[-1].fill_(self.loss_scale / numel)
         # slice bookkeeping: (batch offset, b, token offset c, t, first row)
         self.slices = []
         boff = 0
@@ -309,67 +319,80 @@ class StageEngine:
                 self._all_reduce_rows(self.X[l + 1], r0, T)
 
     # ------------------------------------------------------------------ backward of one slice
-    def _backward_slice(self, sl, first: bool) -> None:
+    def _backward_slice(self, sl) -> None:
+        """Data gradients of one token slice through every layer of the stage (last layer
+        first).  Weight and bias gradients are left to :meth:`_weight_grads`."""
         boff, b, c, t, r0 = sl
         T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
         lib, dt, s = self.lib, self.dt, self._stream
         g = self.grad
-        dA, dB, dln = self.dA.data_ptr(), self.dB.data_ptr(), self.dln.data_ptr()
-        dfc, dao, dqkv = self.dfc.data_ptr(), self.dao.data_ptr(), self.dqkv.data_ptr()
-        if self.is_last:
-            dcur = self.dy_seed.data_ptr()
-        else:
-            dcur = self.dY.data_ptr() + r0 * H * es
+        dln = self.dln.data_ptr()
         for l in reversed(range(self.n_layers)):
             st = self.stats[l].data_ptr()
             fa = self.fa[l].data_ptr() + r0 * Fl * es
             aux = (self.fz[l].data_ptr() + r0 * Fl * es) if self.fz is not None else fa
             xmid = self.xmid[l].data_ptr() + r0 * H * es
-            ln2 = self.ln2[l].data_ptr() + r0 * H * es
-            ln1 = self.ln1[l].data_ptr() + r0 * H * es
             x = self.X[l].data_ptr() + r0 * H * es
             ao = self.ao[l].data_ptr() + r0 * Hl * es
+            dcur = self.dXo[l].data_ptr() + r0 * H * es
+            dmid = self.dMid[l].data_ptr() + r0 * H * es
+            dfc = self.dFc[l].data_ptr() + r0 * Fl * es
+            dqkv = self.dQKV[l].data_ptr() + r0 * 3 * Hl * es
+            dao = self.dAO[l].data_ptr() + r0 * Hl * es
             # ---- FFN
             self._gemm(dcur, H, self._p(l, "fc2.weight"), Fl, dfc, Fl, T, Fl, H, b_mn=1,
                        dact=_ACT[self.act], aux_in=aux, ld_aux=Fl)
-            self._gemm(dcur, H, fa, Fl, self._p(l, "fc2.weight", g), Fl, H, Fl, T, a_mn=1, b_mn=1,
-                       out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dcur, H, T, H, self._p(l, "fc2.bias", g), s)
             self._gemm(dfc, Fl, self._p(l, "fc1.weight"), H, dln, H, T, H, Fl, b_mn=1)
             if self.tp > 1:
                 self._all_reduce_rows(self.dln, 0, T)
-            self._gemm(dfc, Fl, ln2, H, self._p(l, "fc1.weight", g), H, Fl, H, T, a_mn=1, b_mn=1,
-                       out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dfc, Fl, T, Fl, self._p(l, "fc1.bias", g), s)
             lib.tp_layernorm_bwd(dt, dln, xmid, st + (2 * self.rows + r0) * 4,
-                                 st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur, dB,
+                                 st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur, dmid,
                                  self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g),
                                  self.ln_scratch.data_ptr(), T, H, s)
             # ---- attention
-            self._gemm(dB, H, self._p(l, "attn.out_proj.weight"), Hl, dao, Hl, T, Hl, H, b_mn=1)
-            self._gemm(dB, H, ao, Hl, self._p(l, "attn.out_proj.weight", g), Hl, H, Hl, T, a_mn=1,
-                       b_mn=1, out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dB, H, T, H, self._p(l, "attn.out_proj.bias", g), s)
+            self._gemm(dmid, H, self._p(l, "attn.out_proj.weight"), Hl, dao, Hl, T, Hl, H, b_mn=1)
             qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
+            dao_base = self.dAO[l].data_ptr() + self.L * boff * Hl * es
             lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
-            dkv = self.dkv[l].data_ptr() + self.L * boff * 2 * Hl * 4
-            rc = lib.tp_attn_bwd(dt, self.D, qkv_base, b, self.h, t, c, ao, Hl, dao, Hl, lse, self.L,
-                                 self.delta.data_ptr(), dkv, self.L, dqkv, 3 * Hl, int(first),
-                                 self._status_ptr, s)
+            delta = self.delta[l].data_ptr() + boff * self.h * self.L * 4
+            rc = lib.tp_attn_bwd(dt, self.D, qkv_base, b, self.h, t, c, self.L, ao, Hl, dao_base, Hl,
+                                 lse, self.L, delta, dqkv, 3 * Hl, self._status_ptr, s)
             if rc:
                 F.check(rc, "tp_attn_bwd")
             self._gemm(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, dln, H, T, H, 3 * Hl, b_mn=1)
             if self.tp > 1:
                 self._all_reduce_rows(self.dln, 0, T)
-            self._gemm(dqkv, 3 * Hl, ln1, H, self._p(l, "attn.in_proj.weight", g), H, 3 * Hl, H, T,
-                       a_mn=1, b_mn=1, out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dqkv, 3 * Hl, T, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
-            dnext = dA if (l > 0 or self.is_first) else self.dX0.data_ptr() + r0 * H * es
+            if l > 0:
+                dnext = self.dXo[l - 1].data_ptr() + r0 * H * es
+            elif self.is_first:
+                dnext = self.dA.data_ptr()
+            else:
+                dnext = self.dX0.data_ptr() + r0 * H * es
             lib.tp_layernorm_bwd(dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
-                                 self._p(l, "attn_ln.weight"), dB, dnext,
+                                 self._p(l, "attn_ln.weight"), dmid, dnext,
                                  self._p(l, "attn_ln.weight", g), self._p(l, "attn_ln.bias", g),
                                  self.ln_scratch.data_ptr(), T, H, s)
-            dcur = dnext
+
+    def _weight_grads(self) -> None:
+        """Weight and bias gradients of every layer over all ``L*B`` rows at once:
+        ``dW += dY^T X`` with the token dimension as the (long) GEMM K dimension."""
+        R, H, Hl, Fl = self.rows, self.H, self.Hl, self.Fl
+        lib, dt, s, g = self.lib, self.dt, self._stream, self.grad
+        for l in reversed(range(self.n_layers)):
+            dxo, dmid = self.dXo[l].data_ptr(), self.dMid[l].data_ptr()
+            dfc, dqkv = self.dFc[l].data_ptr(), self.dQKV[l].data_ptr()
+            self._gemm(dxo, H, self.fa[l].data_ptr(), Fl, self._p(l, "fc2.weight", g), Fl, H, Fl, R,
+                       a_mn=1, b_mn=1, out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dxo, H, R, H, self._p(l, "fc2.bias", g), s)
+            self._gemm(dfc, Fl, self.ln2[l].data_ptr(), H, self._p(l, "fc1.weight", g), H, Fl, H, R,
+                       a_mn=1, b_mn=1, out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dfc, Fl, R, Fl, self._p(l, "fc1.bias", g), s)
+            self._gemm(dmid, H, self.ao[l].data_ptr(), Hl, self._p(l, "attn.out_proj.weight", g), Hl,
+                       H, Hl, R, a_mn=1, b_mn=1, out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dmid, H, R, H, self._p(l, "attn.out_proj.bias", g), s)
+            self._gemm(dqkv, 3 * Hl, self.ln1[l].data_ptr(), H, self._p(l, "attn.in_proj.weight", g),
+                       H, 3 * Hl, H, R, a_mn=1, b_mn=1, out_f32=1, accumulate=1)
+            lib.tp_colsum(dt, dqkv, 3 * Hl, R, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
 
     # ------------------------------------------------------------------ one iteration
     def _refresh_handles(self):
@@ -422,10 +445,11 @@ class StageEngine:
                 sl = self.slices[bi][si]
                 if recvs is not None:
                     recvs[(bi, si)].wait()
-                self._backward_slice(sl, first=(si == ns - 1))
+                self._backward_slice(sl)
                 if pipelined and not self.is_first:
                     _, b, _, t, r0 = sl
                     sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank()))
+        self._weight_grads()
         for w in sends:
             w.wait()
 

@@ -47,14 +47,15 @@ def test_attention_slices_match_full_causal(dtype, D, b, h, slices):
 
     g = torch.randn(L * b, h * D, device="cuda", dtype=dtype)
     ref.backward(g.float().view(L, b, h * D))
-    dkv = torch.full((b * h, L, 2 * D), float("nan"), device="cuda")
     dqkv = torch.zeros(L * b, h * 3 * D, device="cuda", dtype=dtype)
-    delta = torch.empty(b * h * max(slices), device="cuda")
+    delta = torch.full((b * h, L), float("nan"), device="cuda")
+    do_full = torch.full((L * b, h * D), float("nan"), device="cuda", dtype=dtype)
     c = L
-    for i, t in reversed(list(enumerate(slices))):
+    for t in reversed(slices):
         c -= t
-        F.attn_bwd(qkv, b, h, D, t, c, o[c * b:(c + t) * b], g[c * b:(c + t) * b], lse2, delta,
-                   dkv, dqkv[c * b:(c + t) * b], first=(i == len(slices) - 1))
+        do_full[c * b:(c + t) * b] = g[c * b:(c + t) * b]     # what the out-proj dgrad would write
+        F.attn_bwd(qkv, b, h, D, t, c, L, o[c * b:(c + t) * b], do_full, lse2, delta,
+                   dqkv[c * b:(c + t) * b])
     F.check_device_status()
     got = dqkv.view(L, b, h, 3, D).float()
     want = qkv_ref.grad.view(L, b, h, 3, D)

@@ -326,8 +326,8 @@ constexpr int kBwdStages = 3;
 struct BwdShared {
   uint64_t bar_x, bar_y[kBwdStages], bar_yfree[kBwdStages], bar_s[2], bar_sfree[2], bar_p[2],
       bar_acc[2], bar_done;
-  float lse[2][2][64];
-  float delta[2][2][64];
+  float lse[kBwdStages][64];    // MODE 0: per streamed block, filled by the producer warp
+  float delta[kBwdStages][64];
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -369,7 +369,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   if (threadIdx.x == 0) {
     mbar_init(&sh->bar_x, 1);
     for (int i = 0; i < kBwdStages; ++i) {
-      mbar_init(&sh->bar_y[i], 1);
+      mbar_init(&sh->bar_y[i], MODE == 0 ? 2 : 1);
       mbar_init(&sh->bar_yfree[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -395,7 +395,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   const uint32_t tA1 = tmem + 256, tA2 = tmem + 256 + D;
 
   if (warp == 8) {
-    if (elect_one()) {
+    // producer warp: lane 0 issues the bulk copies; in MODE 0 all lanes also fetch the streamed
+    // queries' lse/delta into the stage's shared arrays and lane 0 adds the second arrival.
+    const int lane = threadIdx.x & 31;
+    if (lane == 0) {
       mbar_expect_tx(&sh->bar_x, 2 * DH * kXSub);
       for (int hh = 0; hh < DH; ++hh) {
         if (MODE == 0) {
@@ -406,12 +409,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
           tma_load_3d(sX2 + hh * kXSub, &tmDO128, &sh->bar_x, hi * D + hh * 64, bi, x0);
         }
       }
-      for (int i = 0; i < n_iter; ++i) {
-        const int st = i % kBwdStages;
-        if (!mbar_wait(&sh->bar_yfree[st], ((i / kBwdStages) & 1) ^ 1, wctx, kErrWaitAttn)) break;
-        uint8_t* y1 = sY + st * kStageBytes;
-        uint8_t* y2 = y1 + DH * kYSub;
-        const int y0 = ystart + i * 64;
+    }
+    for (int i = 0; i < n_iter; ++i) {
+      const int st = i % kBwdStages;
+      const bool ok = mbar_wait(&sh->bar_yfree[st], ((i / kBwdStages) & 1) ^ 1, wctx, kErrWaitAttn);
+      if (!__all_sync(0xffffffffu, ok)) break;
+      uint8_t* y1 = sY + st * kStageBytes;
+      uint8_t* y2 = y1 + DH * kYSub;
+      const int y0 = ystart + i * 64;
+      if (lane == 0) {
         mbar_expect_tx(&sh->bar_y[st], kStageBytes);
         for (int hh = 0; hh < DH; ++hh) {
           if (MODE == 0) {
@@ -422,6 +428,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
             tma_load_3d(y2 + hh * kYSub, &tmQKV64, &sh->bar_y[st], 2 * D + hh * 64, bh, y0);
           }
         }
+      }
+      if (MODE == 0) {
+        const long long base = static_cast<long long>(bh) * p.lse_stride;
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const int yi = y0 + lane + 32 * k;
+          const bool in = yi < p.q_end;
+          sh->lse[st][lane + 32 * k] = in ? __ldcg(p.lse2 + base + yi) : 0.0f;
+          sh->delta[st][lane + 32 * k] = in ? __ldcg(p.delta + base + yi) : 0.0f;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sh->bar_y[st]);
       }
     }
   } else if (warp == 9) {
@@ -471,54 +489,55 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
     bool ok = true;
     for (int i = grp; i < n_iter; i += 2) {
       const int y0 = ystart + i * 64;
-      const int lb = (i >> 1) & 1;
-      if (MODE == 0) {
-        const int yi = y0 + (r & 63);
-        const bool in = yi < p.q_end;
-        const long long off = static_cast<long long>(bh) * p.lse_stride + yi;
-        if (r < 64) sh->lse[grp][lb][r] = in ? p.lse2[off] : 0.0f;
-        else sh->delta[grp][lb][r - 64] = in ? p.delta[off] : 0.0f;
-        named_bar_sync(1 + grp, 128);  // reached in every iteration, aborted or not
-      }
-      if (ok) ok = mbar_wait(&sh->bar_s[grp], (i >> 1) & 1, wctx, kErrWaitAttn);
-      if (!ok) continue;
+      const int st = i % kBwdStages;
+      ok = mbar_wait(&sh->bar_s[grp], (i >> 1) & 1, wctx, kErrWaitAttn);
+      if (!ok) break;
       tc_fence_after();
       float sv[64], dv[64];
       {
-        uint32_t raw[32];
+        uint32_t r0[32], r1[32], r2[32], r3[32];
         __syncwarp();
+        tmem_ld_32x32(tmem + grp * 64 + lane_base, r0);
+        tmem_ld_32x32(tmem + grp * 64 + lane_base + 32, r1);
+        tmem_ld_32x32(tmem + 128 + grp * 64 + lane_base, r2);
+        tmem_ld_32x32(tmem + 128 + grp * 64 + lane_base + 32, r3);
+        tmem_ld_wait();
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-          tmem_ld_32x32(tmem + grp * 64 + lane_base + half * 32, raw);
-          tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) sv[half * 32 + k] = __uint_as_float(raw[k]);
-          tmem_ld_32x32(tmem + 128 + grp * 64 + lane_base + half * 32, raw);
-          tmem_ld_wait();
-#pragma unroll
-          for (int k = 0; k < 32; ++k) dv[half * 32 + k] = __uint_as_float(raw[k]);
+        for (int k = 0; k < 32; ++k) {
+          sv[k] = __uint_as_float(r0[k]);
+          sv[32 + k] = __uint_as_float(r1[k]);
+          dv[k] = __uint_as_float(r2[k]);
+          dv[32 + k] = __uint_as_float(r3[k]);
         }
       }
       tc_fence_before();
       mbar_arrive(&sh->bar_sfree[grp]);
+      // blocks strictly inside the causal region need no per-element mask
+      const bool full = MODE == 0 ? (y0 >= x0 + 127 && y0 + 64 <= p.q_end) : (y0 + 63 <= x0);
+      if (full) {
 #pragma unroll
-      for (int k = 0; k < 64; ++k) {
-        const int yabs = y0 + k;
-        float pr;
-        if (MODE == 0) {
-          const bool valid = (yabs < p.q_end) && (xabs <= yabs);
-          pr = valid ? exp2f(sv[k] * p.scale2 - sh->lse[grp][lb][k]) : 0.0f;
-          dv[k] = pr * (dv[k] - sh->delta[grp][lb][k]);
-        } else {
-          const bool valid = x_ok && (yabs <= xabs);
-          pr = valid ? exp2f(sv[k] * p.scale2 - lse_r) : 0.0f;
-          dv[k] = pr * (dv[k] - delta_r);
+        for (int k = 0; k < 64; ++k) {
+          const float l2 = MODE == 0 ? sh->lse[st][k] : lse_r;
+          const float dl = MODE == 0 ? sh->delta[st][k] : delta_r;
+          const float pr = exp2f(sv[k] * p.scale2 - l2);
+          dv[k] = pr * (dv[k] - dl);
+          sv[k] = pr;
         }
-        sv[k] = pr;
+      } else {
+#pragma unroll
+        for (int k = 0; k < 64; ++k) {
+          const int yabs = y0 + k;
+          const float l2 = MODE == 0 ? sh->lse[st][k] : lse_r;
+          const float dl = MODE == 0 ? sh->delta[st][k] : delta_r;
+          const bool valid = MODE == 0 ? ((yabs < p.q_end) && (xabs <= yabs)) : (x_ok && (yabs <= xabs));
+          const float pr = valid ? exp2f(sv[k] * p.scale2 - l2) : 0.0f;
+          dv[k] = pr * (dv[k] - dl);
+          sv[k] = pr;
+        }
       }
       // the operand tiles are free once the accumulating MMAs of the previous block are done
       if (i >= 1) ok = mbar_wait(&sh->bar_acc[(i - 1) & 1], ((i - 1) >> 1) & 1, wctx, kErrWaitAttn);
-      if (!ok) continue;
+      if (!ok) break;
       if (MODE == 0) store_row64<T>(sP, r, sv);
       store_row64<T>(sdS, r, dv);
       fence_proxy_async();

@@ -1,0 +1,119 @@
+"""Planner: slice-schedule dynamic program, latency fit, FLOP and memory models."""
+import itertools
+import json
+
+import numpy as np
+import pytest
+
+from terapipe_b200.planner import flop_model, latency_model as lm, memory_model
+
+
+def _synthetic_grid(B=2, L=256, gap=8):
+    n = L // gap + 1
+    b = np.arange(B + 1)[:, None, None]
+    s = (np.arange(n) * gap)[None, :, None]
+    c = (np.arange(n) * gap)[None, None, :]
+    return 0.35e-3 + 1.2e-6 * b * s + 0.4e-9 * b * s * c + 0 * (b + s + c)
+
+
+def _compositions(total):
+    for r in range(1, total + 1):
+        for cuts in itertools.combinations(range(1, total), r - 1):
+            edges = (0,) + cuts + (total,)
+            yield [edges[i + 1] - edges[i] for i in range(r)]
+
+
+def test_native_dp_matches_numpy_and_brute_force():
+    gap = 8
+    grid = _synthetic_grid(B=2, L=48, gap=gap)
+    K = 3
+    cap = float(np.max(grid))
+    total_n, scheme_n = lm.planning(grid, 2, 48, K, cap, gap, use_native=True)
+    total_p, scheme_p = lm.planning(grid, 2, 48, K, cap, gap, use_native=False)
+    assert abs(total_n - total_p) < 1e-12 and scheme_n == scheme_p
+    # brute force over all token compositions and both batch splits, same cap
+    best = np.inf
+    for batch_split in ([2], [1, 1]):
+        per_batch = []
+        for bs in set(batch_split):
+            cand = []
+            for comp in _compositions(48 // gap):
+                ctx, tot, mx = 0, 0.0, 0.0
+                for s in comp:
+                    t = grid[bs, s, ctx]
+                    tot, mx, ctx = tot + t, max(mx, t), ctx + s
+                cand.append((tot, mx))
+            per_batch.append((bs, cand))
+        # the DP minimises the SUM first and reports the max on that optimum
+        tot = sum(min(c)[0] for bs, c in per_batch for _ in range(batch_split.count(bs)))
+        mx = max(min(c)[1] for bs, c in per_batch)
+        best = min(best, tot + (K - 1) * mx)
+    assert total_n <= best + 1e-9
+    assert sum(b for b, _ in scheme_n) == 2
+    for _, tokens in scheme_n:
+        assert sum(tokens) == 48 and all(t % gap == 0 for t in tokens)
+
+
+def test_cap_makes_schedule_infeasible_or_finer():
+    grid = _synthetic_grid(B=1, L=128)
+    total, scheme = lm.planning(grid, 1, 128, 4, 1e-9)
+    assert scheme is None and total == float("inf")
+    coarse = lm.planning(grid, 1, 128, 4, float(grid.max()))[1]
+    fine = lm.planning(grid, 1, 128, 4, float(grid[1, 4, 12]))[1]
+    assert len(fine[0][1]) >= len(coarse[0][1])
+
+
+def _fake_table(B, L, gap=8):
+    table = {}
+    for b in range(1, B + 1):
+        for s in range(gap, L + 1, gap):
+            for c in (0, L // 4, L // 2):
+                t = 0.2e-3 + 1.0e-6 * b * s + 0.5e-9 * b * s * c + 2e-7 * b * c
+                table[f"{b}_{s}_{c}"] = {"forward_mean": t / 3, "backward_mean": 2 * t / 3,
+                                         "update_mean": 1e-4}
+    return table
+
+
+def test_fit_and_search_produce_decreasing_slices():
+    B, L, gap = 2, 256, 8
+    table = lm.parse_json(_fake_table(B, L, gap))
+    comm = {"tensor_sizes": [8, 64, 512, 4096], "mean": [2e-5, 2e-5, 3e-5, 6e-5], "std": [0] * 4}
+    model = lm.fit_latency_tables(table, comm, B, L, layers_per_stage=2, step_gap=gap)
+    assert model.r2 > 0.999
+    assert abs(model.predict(1, 64, 64) - (2 * (0.2e-3 + 1e-6 * 64 + 0.5e-9 * 64 * 64 + 2e-7 * 64)
+                                           + 2 * np.interp(64, comm["tensor_sizes"], comm["mean"]))) < 2e-6
+    scheme, latency = lm.search_schedule(model, B, L, pipelinelen=8, layers_per_node=2)
+    assert scheme is not None and latency < float("inf")
+    for _, tokens in scheme:
+        assert sum(tokens) == L
+        assert all(a >= b for a, b in zip(tokens, tokens[1:])), tokens   # later slices are shorter
+    assert abs(lm.evaluate_split(model, scheme, 8, 2) - latency) < 1e-9
+    entry = lm.scheme_to_dp_result(("m", B, 1, 8, 1, 1, 8), scheme, latency)
+    assert set(entry) == {"model_name", "batch_size", "model_parallel_size", "pipeline_length",
+                          "data_parallel_size", "n_nodes", "gpus_per_node", "latency",
+                          "batch_slices", "input_slices"}
+    json.dumps(entry)
+
+
+def test_flop_model_golden_values():
+    # values printed by the reference's flop_model.py for its published latencies
+    eff = flop_model.efficiency("gpt3-175b", 2, 384, 1.160, peak_tflops=112)
+    assert abs(eff * 112 - 9.73) < 0.02
+    eff = flop_model.efficiency("gpt3-13b", 32, 320, 1.328, peak_tflops=112)
+    assert abs(eff * 112 - 12.04) < 0.02
+    eff = flop_model.efficiency("gpt3-1b", 128, 192, 0.913, peak_tflops=112)
+    assert abs(eff * 112 - 11.75) < 0.02
+    lines = []
+    flop_model.efficiency_stats("gpt3-13b", 32, 320, 1.863, 32, 40, "w/o", printer=lines.append)
+    assert "8.579" in lines[0]
+
+
+def test_memory_model_golden_values():
+    assert abs(memory_model.peak_memory_per_gpu("gpt3-175b", 1, 32) - 11.49) < 0.01
+    assert abs(memory_model.peak_memory_per_gpu("gpt3-175b", 1, 48) - 7.69) < 0.01
+    assert memory_model.peak_memory_per_gpu("gpt3-13b", 1, 3) == float("inf")
+    assert memory_model.peak_memory_per_gpu("gpt3-13b", 1, 0) == float("inf")
+    one = memory_model.engine_memory_per_gpu("gpt3-1b", 8, tp=1, pp=1)
+    eight = memory_model.engine_memory_per_gpu("gpt3-1b", 8, tp=1, pp=8)
+    assert 20 < one < 120 and eight < one / 6
+    assert memory_model.engine_memory_per_gpu("gpt3-44b", 4, tp=4, pp=2) < 180

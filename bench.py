@@ -54,7 +54,8 @@ def parse_args():
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--activation", default=None, choices=[None, "gelu", "relu"])
     ap.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
-    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="never capture the step in a CUDA graph")
+    ap.add_argument("--graph", action="store_true", help="capture even when the stage communicates")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -179,7 +180,8 @@ def run_ours(args):
     trainer = Trainer(args.model, batch_size=args.batch, tp=args.tp, pp=pp,
                       batch_slices=batch_slices, seq_slices=seq_slices,
                       dtype=args.dtype, n_layers=args.n_layers, activation=args.activation or "gelu",
-                      use_graph=not args.no_graph, tp_comm=args.tp_comm)
+                      use_graph=(False if args.no_graph else (True if args.graph else None)),
+                      tp_comm=args.tp_comm)
     cfg = trainer.config
     tokens = cfg.batch_size * cfg.seq_len * trainer.topo.dp
 

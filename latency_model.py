@@ -1,0 +1,10 @@
+"""Latency fit + slice-schedule dynamic program; run as a script to write ``dp_results.json``
+from the tables in ``performance_model_data/``.
+Implemented in :mod:`terapipe_b200.planner.latency_model`."""
+from terapipe_b200.planner.latency_model import *  # noqa: F401,F403
+from terapipe_b200.planner.latency_model import (SCAN_GRID, STEP_GAP, SingleLayerLatency,  # noqa: F401
+                                                 analysis_model, evaluate_split,
+                                                 fit_single_layer_model, main, parse_json, planning)
+
+if __name__ == "__main__":
+    main()

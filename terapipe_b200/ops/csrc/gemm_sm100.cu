@@ -17,6 +17,21 @@
 //
 // One CTA per SM, 192 threads: warp 0 = TMA producer, warp 1 = MMA issuer (owns TMEM),
 // warps 2..5 = epilogue (one TMEM lane quarter each).
+//
+// Fused tensor-parallel all-reduce (template flag AR).  Every rank of a tensor-parallel group
+// runs the same GEMM on its K shard; the partial products must be summed over ranks.  Instead
+// of a separate collective, the kernel finishes the sum itself over NVLink peer memory:
+//   A. each output tile has an owner rank (tile index modulo group size); the epilogue stores
+//      the 16-bit partial tile into the owner's staging buffer and raises a per-(tile, source)
+//      flag there (system-scope release);
+//   B. after its own tiles, every CTA reduces the tiles its rank owns: waits for the flags of
+//      all sources, sums the partials in fp32, adds bias and residual, and stores the result
+//      into the output buffer of EVERY rank (peer stores), then raises a per-tile arrival flag
+//      on every rank;
+//   C. before exiting, the CTAs of a rank wait until all tiles have arrived locally.
+// The transfer of a tile overlaps the math of later tiles.  All waits are bounded; flags carry a
+// call counter ("epoch") so they never need clearing.  Peer buffers are plain device
+// allocations mapped through CUDA IPC; only ordinary loads and stores touch peer memory.
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -40,6 +55,45 @@ struct GemmParams {
   int* err;
 };
 
+constexpr int kMaxTp = 8;
+
+struct ArParams {
+  int tp, rank;
+  int epoch;                     // call index within the step; the kernel adds *epoch_base
+  const int* epoch_base;         // device counter advanced once per step (graph-replay safe)
+  int max_tiles;                 // capacity of the staging / flag arrays, in tiles
+  void* stage[kMaxTp];           // per rank: [tp sources][max_tiles][128][BN] 16-bit partials
+  int* flag_a[kMaxTp];           // per rank: [max_tiles][kMaxTp] partial-arrived flags
+  int* flag_b[kMaxTp];           // per rank: [max_tiles] result-arrived flags
+  void* out[kMaxTp];             // per rank: the output matrix (same offset in every pool)
+};
+
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// Spin until *p >= target; false on abort or after the wait limit.
+__device__ __forceinline__ bool wait_flag(const int* p, int target, const WaitCtx& w, int code) {
+  unsigned long long t0 = 0;
+  unsigned spins = 0;
+  while (ld_acquire_sys(p) < target) {
+    if ((++spins & 0x3F) == 0) {
+      if (*w.abort_smem) return false;
+      const unsigned long long now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      else if (now - t0 > kWaitLimitNs) {
+        report_timeout(w, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
@@ -62,10 +116,10 @@ __device__ __forceinline__ float gelu_grad_f(float z) {
   return cdf + z * pdf;
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p) {
+            const GemmParams p, const ArParams ar) {
   using Cfg = GemmCfg<BN>;
   constexpr int S = Cfg::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -107,6 +161,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_kb = (p.K + kBK - 1) / kBK;
+  const int ar_epoch = AR ? (ar.epoch + (ar.epoch_base ? *ar.epoch_base : 0)) : 0;
 
   if (warp == 0) {
     if (elect_one()) {
@@ -197,6 +252,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         __syncwarp();
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c0, r);
         tmem_ld_wait();
+        if (AR) {
+          // phase A: 16-bit partial of this chunk into the owner's staging tile (peer store)
+          const int owner = tile % ar.tp;
+          T* dst = static_cast<T*>(ar.stage[owner]) +
+                   ((static_cast<long long>(ar.rank) * ar.max_tiles + tile) * kBM + row_in_tile) * BN + c0;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 ov;
+            ov.x = Elem<T>::pack2(__uint_as_float(r[g * 8 + 0]) * p.alpha, __uint_as_float(r[g * 8 + 1]) * p.alpha);
+            ov.y = Elem<T>::pack2(__uint_as_float(r[g * 8 + 2]) * p.alpha, __uint_as_float(r[g * 8 + 3]) * p.alpha);
+            ov.z = Elem<T>::pack2(__uint_as_float(r[g * 8 + 4]) * p.alpha, __uint_as_float(r[g * 8 + 5]) * p.alpha);
+            ov.w = Elem<T>::pack2(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
+            *reinterpret_cast<uint4*>(dst + g * 8) = ov;
+          }
+          continue;
+        }
         const int n = n0 + c0;
         if (!row_ok || n >= p.N) continue;
         // Issue every global load of this 32-column chunk before any dependent math or store,
@@ -298,7 +369,89 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
+      if (AR) {
+        // all 128 epilogue threads have stored their rows: publish the tile to its owner
+        __threadfence_system();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (threadIdx.x == 64)
+          st_release_sys(ar.flag_a[tile % ar.tp] + static_cast<long long>(tile) * kMaxTp + ar.rank, ar_epoch);
+      }
     }
+  }
+
+  if (AR) {
+    __syncthreads();
+    __shared__ int s_ok;
+    // phase B: reduce the tiles this rank owns and push the result to every rank
+    const int n_owned = (p.num_tiles - ar.rank + ar.tp - 1) / ar.tp;
+    for (int j = blockIdx.x; j < n_owned; j += gridDim.x) {
+      const int tile = j * ar.tp + ar.rank;
+      if (threadIdx.x == 0) {
+        bool ok = true;
+        for (int src = 0; src < ar.tp && ok; ++src)
+          ok = wait_flag(ar.flag_a[ar.rank] + static_cast<long long>(tile) * kMaxTp + src, ar_epoch, wctx,
+                         kErrWaitPeer);
+        s_ok = ok ? 1 : 0;
+      }
+      __syncthreads();
+      if (s_ok) {
+        const int m0 = (tile % p.num_m_tiles) * kBM;
+        const int n0 = (tile / p.num_m_tiles) * BN;
+        const T* stage = static_cast<const T*>(ar.stage[ar.rank]);
+        for (int v = threadIdx.x; v < kBM * BN / 8; v += kGemmThreads) {
+          const int rr = v / (BN / 8), cc = (v % (BN / 8)) * 8;
+          const long long row = m0 + rr;
+          const int col = n0 + cc;
+          if (row >= p.M || col + 8 > p.N) continue;
+          float acc8[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+          for (int src = 0; src < ar.tp; ++src) {
+            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(
+                stage + ((static_cast<long long>(src) * ar.max_tiles + tile) * kBM + rr) * BN + cc));
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = Elem<T>::unpack2(w[q]);
+              acc8[2 * q] += f.x;
+              acc8[2 * q + 1] += f.y;
+            }
+          }
+          if (p.bias) {
+            const uint4 u = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + col));
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = Elem<T>::unpack2(w[q]);
+              acc8[2 * q] += f.x;
+              acc8[2 * q + 1] += f.y;
+            }
+          }
+          if (p.residual) {
+            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + col));
+            const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const float2 f = Elem<T>::unpack2(w[q]);
+              acc8[2 * q] += f.x;
+              acc8[2 * q + 1] += f.y;
+            }
+          }
+          uint4 ov;
+          ov.x = Elem<T>::pack2(acc8[0], acc8[1]);
+          ov.y = Elem<T>::pack2(acc8[2], acc8[3]);
+          ov.z = Elem<T>::pack2(acc8[4], acc8[5]);
+          ov.w = Elem<T>::pack2(acc8[6], acc8[7]);
+          for (int dst = 0; dst < ar.tp; ++dst)
+            *reinterpret_cast<uint4*>(static_cast<T*>(ar.out[dst]) + row * p.ldo + col) = ov;
+        }
+      }
+      __threadfence_system();
+      __syncthreads();
+      if (s_ok && threadIdx.x < ar.tp) st_release_sys(ar.flag_b[threadIdx.x] + tile, ar_epoch);
+    }
+    // phase C: every tile of the output must have arrived in this rank's memory
+    for (int tile = blockIdx.x * kGemmThreads + threadIdx.x; tile < p.num_tiles;
+         tile += gridDim.x * kGemmThreads)
+      wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
   }
 
   // teardown: on an aborted run give in-flight bulk copies time to land before the CTA's
@@ -312,11 +465,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, const ArParams* arp = nullptr) {
   using Cfg = GemmCfg<BN>;
-  auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32>;
+  auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR>;
+  ArParams ar;
+  if (arp) ar = *arp;
+  else ar.tp = 0;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -325,7 +481,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     configured = true;
   }
   int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p, ar);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
@@ -396,4 +552,61 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
                          : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, p, s))
   return bf16 ? TP_DISPATCH(__nv_bfloat16) : TP_DISPATCH(__half);
 #undef TP_DISPATCH
+}
+
+// Fused GEMM + tensor-parallel all-reduce (see the file comment).  `out_ptrs[r]` is the address
+// of the output matrix in rank r's memory (peer-mapped), `stage_ptrs` / `flag_*_ptrs` the
+// staging and flag arrays of every rank.  BN is fixed to 128.  Every rank of the group must
+// make the same call with the same epoch = `epoch` + *`epoch_base`; the sum must grow from call
+// to call (epoch = index of the call within a step, *epoch_base advanced per step on the device).
+extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, const void* B,
+                          long long ldb, long long ldo, int M, int N, int K, const void* bias,
+                          const void* residual, long long ldr, int tp, int rank, int epoch,
+                          const int* epoch_base, int max_tiles, void* const* stage_ptrs, int* const* flag_a_ptrs,
+                          int* const* flag_b_ptrs, void* const* out_ptrs, int* err_flag,
+                          void* stream) {
+  using namespace tp;
+  if (M <= 0 || N <= 0 || K <= 0 || tp < 2 || tp > kMaxTp || rank < 0 || rank >= tp)
+    return kErrBadArgument;
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 8)) return kErrBadArgument;
+  constexpr int BN = 128;
+  const bool bf16 = dtype == 1;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_tiles = (M + kBM - 1) / kBM;
+  p.num_tiles = p.num_m_tiles * ((N + BN - 1) / BN);
+  if (p.num_tiles > max_tiles) return kErrTooLarge;
+  CUtensorMap tmA, tmB;
+  if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16)) return kErrDriver;
+  if (!(b_mn ? make_tmap_2d(&tmB, B, N, K, ldb, 64, kBK, bf16)
+             : make_tmap_2d(&tmB, B, K, N, ldb, kBK, BN, bf16)))
+    return kErrDriver;
+  p.out = out_ptrs[rank]; p.ldo = ldo;
+  p.bias = bias; p.residual = residual; p.ldr = ldr;
+  p.aux_out = nullptr; p.aux_in = nullptr; p.ld_aux = 0;
+  p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
+  p.err = err_flag;
+  ArParams ar;
+  ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
+  for (int i = 0; i < kMaxTp; ++i) {
+    ar.stage[i] = i < tp ? stage_ptrs[i] : nullptr;
+    ar.flag_a[i] = i < tp ? flag_a_ptrs[i] : nullptr;
+    ar.flag_b[i] = i < tp ? flag_b_ptrs[i] : nullptr;
+    ar.out[i] = i < tp ? out_ptrs[i] : nullptr;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bf16)
+    return b_mn ? launch_gemm<__nv_bfloat16, BN, false, true, false, true>(tmA, tmB, p, s, &ar)
+                : launch_gemm<__nv_bfloat16, BN, false, false, false, true>(tmA, tmB, p, s, &ar);
+  return b_mn ? launch_gemm<__half, BN, false, true, false, true>(tmA, tmB, p, s, &ar)
+              : launch_gemm<__half, BN, false, false, false, true>(tmA, tmB, p, s, &ar);
+}
+
+namespace tp {
+__global__ void advance_counter_kernel(int* counter, int inc) { *counter += inc; }
+}  // namespace tp
+
+extern "C" int tp_advance_counter(int* counter, int inc, void* stream) {
+  tp::advance_counter_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter, inc);
+  return cudaGetLastError() == cudaSuccess ? tp::kOk : tp::kErrLaunch;
 }

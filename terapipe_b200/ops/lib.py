@@ -66,6 +66,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "tp_adam_tick": [P, F, F, P],
         "tp_fused_adam": [I, P, P, P, P, P, L, P, F, F, F, F, F, F, P],
         "tp_fill": [I, P, L, F, P],
+        "tp_gemm_ar": [I, I, P, L, P, L, L, I, I, I, P, P, L, I, I, I, P, I, P, P, P, P, P, P],
+        "tp_advance_counter": [P, I, P],
         "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
         "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
     }

@@ -127,7 +127,10 @@ class StageEngine:
         self._alloc_activations()
         self.status = F.status_word(dev)
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
-        self.use_graph = (self.pp == 1 and self.tp == 1 and self.dp == 1) if use_graph is None else use_graph
+        # A CUDA graph may hold this library's kernels only: captured NCCL point-to-point or
+        # collective calls deadlocked on replay here, so a stage that calls NCCL runs eagerly.
+        nccl_free = self.pp == 1 and self.dp == 1 and (self.tp == 1 or self.tp_comm == "fused")
+        self.use_graph = nccl_free if use_graph is None else (bool(use_graph) and nccl_free)
         self._graph = None
         self.step_count = 0
         self._streams_ready = False
@@ -138,6 +141,7 @@ class StageEngine:
         n_slices = len(self.batch_slices) * len(self.seq_slices)
         self.launches_per_step = n_slices * self.n_layers * 18 + self.n_layers * 8 + 2
         self.launch_count = 0
+        self._ar_calls_per_step = n_slices * self.n_layers * 4 + 1
 
     # ------------------------------------------------------------------ parameters
     def param(self, layer: int, name: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -216,10 +220,31 @@ class StageEngine:
         def buf(width, dtype=dt):
             return torch.empty(rows, width, dtype=dtype, device=dev)
 
-        self.X = [buf(H) for _ in range(self.n_layers + 1)]
+        tmax = max(self.seq_slices) * max(self.batch_slices)
+        self.tmax = tmax
+        self.ar = None
+        self._pool_off = {}
+        if self.tp_comm == "fused":
+            # matrices that receive all-reduced results live at the same offset of a
+            # peer-mapped pool on every tensor-parallel rank
+            from ..parallel.symm import FusedAllReduceContext
+            n_mats = 2 * self.n_layers
+            pool = n_mats * (rows * H * self.es + 256) + tmax * H * self.es + 4096
+            self.ar = FusedAllReduceContext(mpu.get_model_parallel_group(), tmax, H, pool)
+            self.ar_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._ar_calls = 0
+
+        def sym(name, nrows):
+            if self.ar is None:
+                return torch.empty(nrows, H, dtype=dt, device=dev)
+            t, off = self.ar.alloc((nrows, H), dt)
+            self._pool_off[name] = off
+            return t
+
+        self.X = [buf(H)] + [sym(f"X{l + 1}", rows) for l in range(self.n_layers)]
         self.ln1 = [buf(H) for _ in range(self.n_layers)]
         self.ln2 = [buf(H) for _ in range(self.n_layers)]
-        self.xmid = [buf(H) for _ in range(self.n_layers)]
+        self.xmid = [sym(f"xmid{l}", rows) for l in range(self.n_layers)]
         self.qkv = [buf(3 * Hl) for _ in range(self.n_layers)]
         self.ao = [buf(Hl) for _ in range(self.n_layers)]
         self.fa = [buf(Fl) for _ in range(self.n_layers)]
@@ -237,10 +262,8 @@ class StageEngine:
         self.dXo = [buf(H) for _ in range(self.n_layers)]   # d(layer output); the last one is
         self.dY = self.dXo[-1] if self.n_layers else None    # received from the next stage
         self.dX0 = buf(H) if not self.is_first else None    # gradients sent to the previous stage
-        tmax = max(self.seq_slices) * max(self.batch_slices)
-        self.tmax = tmax
         self.dA = torch.empty(tmax, H, dtype=dt, device=dev)
-        self.dln = torch.empty(tmax, H, dtype=dt, device=dev)
+        self.dln = sym("dln", tmax)
         self.ln_scratch = torch.empty(F.layernorm_bwd_scratch_floats(tmax, H), dtype=torch.float32,
                                       device=dev)
         numel = self.L * self.B * H
@@ -275,6 +298,20 @@ class StageEngine:
     def _all_reduce_rows(self, tensor, r0, T):
         dist.all_reduce(tensor[r0:r0 + T], group=mpu.get_model_parallel_group())
 
+    def _gemm_ar(self, a, lda, b, ldb, out_name, row0, M, N, K, b_mn=0, bias=None, residual=None,
+                 ldr=0):
+        """Fused GEMM + tensor-parallel all-reduce into rows ``[row0, row0+M)`` of the pooled
+        matrix ``out_name`` on every rank; bias and residual are added once, by the tile's owner."""
+        ar = self.ar
+        self._ar_calls += 1
+        off = self._pool_off[out_name] + row0 * N * self.es
+        st = self.lib.tp_gemm_ar(self.dt, b_mn, a, lda, b, ldb, N, M, N, K, bias, residual, ldr,
+                                 ar.tp, ar.rank, self._ar_calls, self.ar_epoch_base.data_ptr(),
+                                 ar.max_tiles, ar.stage_ptrs, ar.flag_a_ptrs, ar.flag_b_ptrs,
+                                 ar.out_ptrs(off), self._status_ptr, self._stream)
+        if st:
+            F.check(st, "tp_gemm_ar")
+
     # ------------------------------------------------------------------ forward of one slice
     def _forward_slice(self, sl) -> None:
         boff, b, c, t, r0 = sl
@@ -298,11 +335,15 @@ class StageEngine:
             if rc:
                 F.check(rc, "tp_attn_fwd")
             xmid = self.xmid[l].data_ptr() + r0 * H * es
-            self._gemm(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl, xmid, H, T, H, Hl,
-                       bias=self._p(l, "attn.out_proj.bias") if tp0 else None,
-                       residual=x if tp0 else None, ldr=H)
-            if self.tp > 1:
-                self._all_reduce_rows(self.xmid[l], r0, T)
+            if self.ar is not None:
+                self._gemm_ar(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl, f"xmid{l}", r0, T, H, Hl,
+                              bias=self._p(l, "attn.out_proj.bias"), residual=x, ldr=H)
+            else:
+                self._gemm(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl, xmid, H, T, H, Hl,
+                           bias=self._p(l, "attn.out_proj.bias") if tp0 else None,
+                           residual=x if tp0 else None, ldr=H)
+                if self.tp > 1:
+                    self._all_reduce_rows(self.xmid[l], r0, T)
             ln2 = self.ln2[l].data_ptr() + r0 * H * es
             lib.tp_layernorm_fwd(dt, xmid, self._p(l, "fc_ln.weight"), self._p(l, "fc_ln.bias"), ln2,
                                  st + (2 * self.rows + r0) * 4, st + (3 * self.rows + r0) * 4, T, H,
@@ -312,11 +353,15 @@ class StageEngine:
             self._gemm(ln2, H, self._p(l, "fc1.weight"), H, fa, Fl, T, Fl, H,
                        bias=self._p(l, "fc1.bias"), act=_ACT[self.act], aux_out=fz, ld_aux=Fl)
             xo = self.X[l + 1].data_ptr() + r0 * H * es
-            self._gemm(fa, Fl, self._p(l, "fc2.weight"), Fl, xo, H, T, H, Fl,
-                       bias=self._p(l, "fc2.bias") if tp0 else None,
-                       residual=xmid if tp0 else None, ldr=H)
-            if self.tp > 1:
-                self._all_reduce_rows(self.X[l + 1], r0, T)
+            if self.ar is not None:
+                self._gemm_ar(fa, Fl, self._p(l, "fc2.weight"), Fl, f"X{l + 1}", r0, T, H, Fl,
+                              bias=self._p(l, "fc2.bias"), residual=xmid, ldr=H)
+            else:
+                self._gemm(fa, Fl, self._p(l, "fc2.weight"), Fl, xo, H, T, H, Fl,
+                           bias=self._p(l, "fc2.bias") if tp0 else None,
+                           residual=xmid if tp0 else None, ldr=H)
+                if self.tp > 1:
+                    self._all_reduce_rows(self.X[l + 1], r0, T)
 
     # ------------------------------------------------------------------ backward of one slice
     def _backward_slice(self, sl) -> None:
@@ -342,9 +387,12 @@ class StageEngine:
             # ---- FFN
             self._gemm(dcur, H, self._p(l, "fc2.weight"), Fl, dfc, Fl, T, Fl, H, b_mn=1,
                        dact=_ACT[self.act], aux_in=aux, ld_aux=Fl)
-            self._gemm(dfc, Fl, self._p(l, "fc1.weight"), H, dln, H, T, H, Fl, b_mn=1)
-            if self.tp > 1:
-                self._all_reduce_rows(self.dln, 0, T)
+            if self.ar is not None:
+                self._gemm_ar(dfc, Fl, self._p(l, "fc1.weight"), H, "dln", 0, T, H, Fl, b_mn=1)
+            else:
+                self._gemm(dfc, Fl, self._p(l, "fc1.weight"), H, dln, H, T, H, Fl, b_mn=1)
+                if self.tp > 1:
+                    self._all_reduce_rows(self.dln, 0, T)
             lib.tp_layernorm_bwd(dt, dln, xmid, st + (2 * self.rows + r0) * 4,
                                  st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur, dmid,
                                  self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g),
@@ -359,9 +407,13 @@ class StageEngine:
                                  lse, self.L, delta, dqkv, 3 * Hl, self._status_ptr, s)
             if rc:
                 F.check(rc, "tp_attn_bwd")
-            self._gemm(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, dln, H, T, H, 3 * Hl, b_mn=1)
-            if self.tp > 1:
-                self._all_reduce_rows(self.dln, 0, T)
+            if self.ar is not None:
+                self._gemm_ar(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, "dln", 0, T, H, 3 * Hl,
+                              b_mn=1)
+            else:
+                self._gemm(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, dln, H, T, H, 3 * Hl, b_mn=1)
+                if self.tp > 1:
+                    self._all_reduce_rows(self.dln, 0, T)
             if l > 0:
                 dnext = self.dXo[l - 1].data_ptr() + r0 * H * es
             elif self.is_first:
@@ -414,10 +466,14 @@ class StageEngine:
         order = [(bi, si) for bi in range(len(self.batch_slices)) for si in range(len(self.seq_slices))]
         if not forward:
             order = order[::-1]
+        # fork the side stream from the current one (required under graph capture) and join it
+        # back: it only carries event nodes, the receives themselves run on NCCL's stream
+        self.recv_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.recv_stream):
             for bi, si in order:
                 _, b, _, t, r0 = self.slices[bi][si]
                 works[(bi, si)] = dist.irecv(buf[r0:r0 + t * b], src)
+        torch.cuda.current_stream().wait_stream(self.recv_stream)
         return works
 
     def _forward_backward(self):
@@ -462,6 +518,12 @@ class StageEngine:
 
     def _iteration(self, update=True):
         self._refresh_handles()
+        if self.ar is not None:
+            # call indices restart at 1 every iteration; the device counter supplies the rest, so
+            # a replayed CUDA graph still produces fresh, growing epochs
+            self.lib.tp_advance_counter(self.ar_epoch_base.data_ptr(), self._ar_calls_per_step,
+                                        self._stream)
+            self._ar_calls = 0
         self._forward_backward()
         if update:
             self._reduce_and_update()

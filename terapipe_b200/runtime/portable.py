@@ -154,7 +154,9 @@ class PortablePipeline:
         return rec
 
     # ---- backward -----------------------------------------------------------------
-    def backward_step(self, rec):
+    def backward_step(self, rec, output_grad=None):
+        """``output_grad``: optional ``[L, B, H]`` gradient of the stage output (last stage only);
+        default is the seed gradient of ``loss = mean(output)`` times the loss scale."""
         cfg = self.config
         numel = cfg.seq_len * cfg.batch_size * cfg.embedding_dim
         n_params = len(self.params)
@@ -167,7 +169,10 @@ class PortablePipeline:
                    for _ in self.layers.layers]
             for si in reversed(range(len(self.seq_slices))):
                 x, y, prefixes, news, c, t, _ = rec[bi, si]
-                if self.is_last:
+                if self.is_last and output_grad is not None:
+                    boff = sum(self.batch_slices[:bi])
+                    dy = output_grad[c:c + t, boff:boff + b].to(y.dtype).contiguous()
+                elif self.is_last:
                     dy = torch.full_like(y, self.loss_scale / numel)
                 else:
                     dy = torch.empty_like(y)

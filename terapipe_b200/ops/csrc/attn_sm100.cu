@@ -326,8 +326,8 @@ constexpr int kBwdStages = 3;
 struct BwdShared {
   uint64_t bar_x, bar_y[kBwdStages], bar_yfree[kBwdStages], bar_s[2], bar_sfree[2], bar_p[2],
       bar_acc[2], bar_done;
-  float lse[kBwdStages][64];    // MODE 0: per streamed block, filled by the producer warp
-  float delta[kBwdStages][64];
+  alignas(16) float lse[kBwdStages][64];    // MODE 0: per streamed block, bulk-copied by the producer
+  alignas(16) float delta[kBwdStages][64];
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -369,7 +369,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   if (threadIdx.x == 0) {
     mbar_init(&sh->bar_x, 1);
     for (int i = 0; i < kBwdStages; ++i) {
-      mbar_init(&sh->bar_y[i], MODE == 0 ? 2 : 1);
+      mbar_init(&sh->bar_y[i], 1);
       mbar_init(&sh->bar_yfree[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
@@ -395,10 +395,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   const uint32_t tA1 = tmem + 256, tA2 = tmem + 256 + D;
 
   if (warp == 8) {
-    // producer warp: lane 0 issues the bulk copies; in MODE 0 all lanes also fetch the streamed
-    // queries' lse/delta into the stage's shared arrays and lane 0 adds the second arrival.
-    const int lane = threadIdx.x & 31;
-    if (lane == 0) {
+    // producer: one thread issues every bulk copy.  In MODE 0 the streamed queries' lse/delta
+    // (64 contiguous floats each) ride on the same barrier as the tiles.
+    if (elect_one()) {
       mbar_expect_tx(&sh->bar_x, 2 * DH * kXSub);
       for (int hh = 0; hh < DH; ++hh) {
         if (MODE == 0) {
@@ -409,16 +408,24 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
           tma_load_3d(sX2 + hh * kXSub, &tmDO128, &sh->bar_x, hi * D + hh * 64, bi, x0);
         }
       }
-    }
-    for (int i = 0; i < n_iter; ++i) {
-      const int st = i % kBwdStages;
-      const bool ok = mbar_wait(&sh->bar_yfree[st], ((i / kBwdStages) & 1) ^ 1, wctx, kErrWaitAttn);
-      if (!__all_sync(0xffffffffu, ok)) break;
-      uint8_t* y1 = sY + st * kStageBytes;
-      uint8_t* y2 = y1 + DH * kYSub;
-      const int y0 = ystart + i * 64;
-      if (lane == 0) {
-        mbar_expect_tx(&sh->bar_y[st], kStageBytes);
+      for (int i = 0; i < n_iter; ++i) {
+        const int st = i % kBwdStages;
+        if (!mbar_wait(&sh->bar_yfree[st], ((i / kBwdStages) & 1) ^ 1, wctx, kErrWaitAttn)) break;
+        uint8_t* y1 = sY + st * kStageBytes;
+        uint8_t* y2 = y1 + DH * kYSub;
+        const int y0 = ystart + i * 64;
+        // a block that runs past q_end takes its lse/delta through guarded plain loads instead
+        const bool bulk_stats = MODE == 0 && y0 + 64 <= p.q_end && (y0 & 3) == 0 &&
+                                (p.lse_stride & 3) == 0;
+        if (MODE == 0 && !bulk_stats) {
+          const long long base = static_cast<long long>(bh) * p.lse_stride;
+          for (int k = 0; k < 64; ++k) {
+            const bool in = y0 + k < p.q_end;
+            sh->lse[st][k] = in ? __ldcg(p.lse2 + base + y0 + k) : 0.0f;
+            sh->delta[st][k] = in ? __ldcg(p.delta + base + y0 + k) : 0.0f;
+          }
+        }
+        mbar_expect_tx(&sh->bar_y[st], kStageBytes + (bulk_stats ? 512 : 0));
         for (int hh = 0; hh < DH; ++hh) {
           if (MODE == 0) {
             tma_load_3d(y1 + hh * kYSub, &tmQKV64, &sh->bar_y[st], hh * 64, bh, y0);
@@ -428,18 +435,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
             tma_load_3d(y2 + hh * kYSub, &tmQKV64, &sh->bar_y[st], 2 * D + hh * 64, bh, y0);
           }
         }
-      }
-      if (MODE == 0) {
-        const long long base = static_cast<long long>(bh) * p.lse_stride;
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const int yi = y0 + lane + 32 * k;
-          const bool in = yi < p.q_end;
-          sh->lse[st][lane + 32 * k] = in ? __ldcg(p.lse2 + base + yi) : 0.0f;
-          sh->delta[st][lane + 32 * k] = in ? __ldcg(p.delta + base + yi) : 0.0f;
+        if (bulk_stats) {
+          const long long off = static_cast<long long>(bh) * p.lse_stride + y0;
+          bulk_load_1d(sh->lse[st], p.lse2 + off, 256, &sh->bar_y[st]);
+          bulk_load_1d(sh->delta[st], p.delta + off, 256, &sh->bar_y[st]);
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sh->bar_y[st]);
       }
     }
   } else if (warp == 9) {

@@ -138,7 +138,7 @@ __global__ void __launch_bounds__(LnGeom<WPR>::kThreads)
 layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                      const float* __restrict__ mean, const float* __restrict__ rstd,
                      const T* __restrict__ gamma, const T* __restrict__ dres, T* __restrict__ dx,
-                     float* __restrict__ scratch, int rows, int H) {
+                     float* __restrict__ scratch, int rows, int H, int accumulate_slots) {
   using G = LnGeom<WPR>;
   extern __shared__ float part_smem[];  // [2][H]
   __shared__ float red[2 * 2 * G::kRowsPerCta * WPR + 1];
@@ -199,7 +199,8 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       }
     }
   }
-  // fold the row groups of this CTA in order, then publish one slot
+  // fold the row groups of this CTA in a fixed order (16-byte accesses: no bank conflicts),
+  // then add the CTA's sums into its slot of the persistent partial buffer
 #pragma unroll 1
   for (int gsel = 0; gsel < G::kRowsPerCta; ++gsel) {
     if (grp == gsel) {
@@ -207,15 +208,19 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       for (int i = 0; i < NV; ++i) {
         const int col = ((i * WPR + wr) * 32 + lane) * 8;
         if (col < H) {
+          float4* sgam = reinterpret_cast<float4*>(part_smem + col);
+          float4* sbet = reinterpret_cast<float4*>(part_smem + H + col);
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            if (gsel == 0) {
-              part_smem[col + j] = pg[i][j];
-              part_smem[H + col + j] = pb[i][j];
-            } else {
-              part_smem[col + j] += pg[i][j];
-              part_smem[H + col + j] += pb[i][j];
+          for (int hlf = 0; hlf < 2; ++hlf) {
+            float4 a = make_float4(pg[i][4 * hlf], pg[i][4 * hlf + 1], pg[i][4 * hlf + 2], pg[i][4 * hlf + 3]);
+            float4 c = make_float4(pb[i][4 * hlf], pb[i][4 * hlf + 1], pb[i][4 * hlf + 2], pb[i][4 * hlf + 3]);
+            if (gsel != 0) {
+              const float4 oa = sgam[hlf], oc = sbet[hlf];
+              a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
+              c.x += oc.x; c.y += oc.y; c.z += oc.z; c.w += oc.w;
             }
+            sgam[hlf] = a;
+            sbet[hlf] = c;
           }
         }
       }
@@ -223,20 +228,39 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
     __syncthreads();
   }
   float* sg = scratch + static_cast<long long>(blockIdx.x) * 2 * H;
-  for (int c = threadIdx.x * 4; c < 2 * H; c += blockDim.x * 4)
-    *reinterpret_cast<float4*>(sg + c) = *reinterpret_cast<const float4*>(part_smem + c);
+  for (int c = threadIdx.x * 4; c < 2 * H; c += blockDim.x * 4) {
+    float4 v = *reinterpret_cast<const float4*>(part_smem + c);
+    if (accumulate_slots) {
+      const float4 o = __ldcg(reinterpret_cast<const float4*>(sg + c));
+      v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+    }
+    __stcg(reinterpret_cast<float4*>(sg + c), v);
+  }
 }
 
-// dgamma[c] += sum_p scratch[p][0][c]; dbeta[c] += sum_p scratch[p][1][c].
-// blockDim = (32, 8): 32 columns per CTA, 8 lanes over the slots, fixed-order tree in smem.
-__global__ void layernorm_bwd_reduce_kernel(const float* __restrict__ scratch, int parts, int H,
-                                            float* __restrict__ dgamma, float* __restrict__ dbeta) {
+// dgamma[c] += sum_p scratch[p][0][c]; dbeta[c] += sum_p scratch[p][1][c]; optionally clears the
+// slots afterwards.  blockDim = (32, 8): 32 columns per CTA, 8 lanes over the slots (4 loads in
+// flight per thread), fixed-order tree in shared memory.
+__global__ void layernorm_bwd_reduce_kernel(float* __restrict__ scratch, int parts, int H,
+                                            float* __restrict__ dgamma, float* __restrict__ dbeta,
+                                            int clear) {
   __shared__ float sm[8][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
-  float s = 0.0f;
-  if (c < 2 * H)
-    for (int p = threadIdx.y; p < parts; p += 8) s += scratch[static_cast<long long>(p) * 2 * H + c];
-  sm[threadIdx.y][threadIdx.x] = s;
+  const long long stride = 2ll * H;
+  float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+  if (c < 2 * H) {
+    int p = threadIdx.y;
+    for (; p + 24 < parts; p += 32) {
+      s0 += __ldcg(scratch + p * stride + c);
+      s1 += __ldcg(scratch + (p + 8) * stride + c);
+      s2 += __ldcg(scratch + (p + 16) * stride + c);
+      s3 += __ldcg(scratch + (p + 24) * stride + c);
+    }
+    for (; p < parts; p += 8) s0 += __ldcg(scratch + p * stride + c);
+    if (clear)
+      for (int q = threadIdx.y; q < parts; q += 8) scratch[q * stride + c] = 0.0f;
+  }
+  sm[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
   __syncthreads();
   if (threadIdx.y == 0 && c < 2 * H) {
     float t = 0.0f;
@@ -395,17 +419,24 @@ template <typename K> static void ln_allow_smem(K kern) {
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
 }
 
-static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const float* mean,
-                                const float* rstd, const void* gamma, const void* dres, void* dx,
-                                float* dgamma, float* dbeta, float* scratch, int rows, int H,
-                                cudaStream_t s) {
-  if (rows <= 0) return kOk;
-  int nv, wpr;
-  if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
+static int ln_parts(int rows, int wpr) {
   const int rpc = wpr >= 8 ? 1 : 8 / wpr;
   int parts = (rows + rpc - 1) / rpc;
   const int cap = tp_layernorm_bwd_parts(rows);
-  if (parts > cap) parts = cap;
+  return parts > cap ? cap : parts;
+}
+
+// mode 0: write the CTA partials into `scratch` and fold them into dgamma/dbeta right away.
+// mode 1: ADD the CTA partials into the persistent slots `scratch` (zero-initialised by the
+//         caller) and leave dgamma/dbeta alone; tp_layernorm_bwd_finish folds them later.
+static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const float* mean,
+                                const float* rstd, const void* gamma, const void* dres, void* dx,
+                                float* dgamma, float* dbeta, float* scratch, int rows, int H,
+                                int mode, cudaStream_t s) {
+  if (rows <= 0) return kOk;
+  int nv, wpr;
+  if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
+  const int parts = ln_parts(rows, wpr);
   const size_t smem = static_cast<size_t>(2) * H * sizeof(float);
 #define LN_BWD(T, NV, WPR)                                                                      \
   {                                                                                             \
@@ -414,12 +445,14 @@ static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const 
     kern<<<parts, LnGeom<WPR>::kThreads, smem, s>>>(                                            \
         static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                        \
         static_cast<const T*>(gamma), static_cast<const T*>(dres), static_cast<T*>(dx), scratch, \
-        rows, H);                                                                               \
+        rows, H, mode);                                                                         \
   }
   if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_BWD) }
   else { TP_LN_DISPATCH(__half, LN_BWD) }
 #undef LN_BWD
-  layernorm_bwd_reduce_kernel<<<(2 * H + 31) / 32, dim3(32, 8), 0, s>>>(scratch, parts, H, dgamma, dbeta);
+  if (mode == 0)
+    layernorm_bwd_reduce_kernel<<<(2 * H + 31) / 32, dim3(32, 8), 0, s>>>(scratch, parts, H, dgamma,
+                                                                          dbeta, 0);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 }  // namespace tp
@@ -429,7 +462,24 @@ extern "C" int tp_layernorm_bwd(int dtype, const void* dy, const void* x, const 
                                 float* dgamma, float* dbeta, float* scratch, int rows, int H,
                                 void* stream) {
   return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, dx, dgamma, dbeta, scratch,
-                              rows, H, static_cast<cudaStream_t>(stream));
+                              rows, H, 0, static_cast<cudaStream_t>(stream));
+}
+
+// Variant that only accumulates into persistent partial slots (tp_layernorm_bwd_parts(rows)
+// slots of 2*H floats, zero before the first call of a backward pass).
+extern "C" int tp_layernorm_bwd_accum(int dtype, const void* dy, const void* x, const float* mean,
+                                      const float* rstd, const void* gamma, const void* dres,
+                                      void* dx, float* slots, int rows, int H, void* stream) {
+  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, dx, nullptr, nullptr, slots,
+                              rows, H, 1, static_cast<cudaStream_t>(stream));
+}
+
+// Fold `parts` slots into dgamma/dbeta (+=) and clear them for the next backward pass.
+extern "C" int tp_layernorm_bwd_finish(float* slots, int parts, int H, float* dgamma, float* dbeta,
+                                       void* stream) {
+  layernorm_bwd_reduce_kernel<<<(2 * H + 31) / 32, dim3(32, 8), 0, static_cast<cudaStream_t>(stream)>>>(
+      slots, parts, H, dgamma, dbeta, 1);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
 extern "C" int tp_colsum(int dtype, const void* dy, long long ld, int rows, int N, float* db,

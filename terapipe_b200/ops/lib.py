@@ -62,6 +62,8 @@ def _declare(lib: ctypes.CDLL) -> None:
         "tp_layernorm_fwd": [I, P, P, P, P, P, P, I, I, F, P],
         "tp_layernorm_bwd_parts": [I],
         "tp_layernorm_bwd": [I, P, P, P, P, P, P, P, P, P, P, I, I, P],
+        "tp_layernorm_bwd_accum": [I, P, P, P, P, P, P, P, P, I, I, P],
+        "tp_layernorm_bwd_finish": [P, I, I, P, P, P],
         "tp_colsum": [I, P, L, I, I, P, P],
         "tp_adam_tick": [P, F, F, P],
         "tp_fused_adam": [I, P, P, P, P, P, L, P, F, F, F, F, F, F, P],

@@ -135,11 +135,11 @@ class StageEngine:
         self.step_count = 0
         self._streams_ready = False
         # launches of this library's own kernels (NCCL and torch kernels are not counted):
-        # per layer and slice 7 forward (2 LN, 4 GEMM, attention) and 11 backward (4 GEMM,
-        # 2x2 LN, 3 attention); per layer 8 for the weight gradients (4 GEMM, 4 bias column
-        # sums); plus 2 for the optimizer
+        # per layer and slice 7 forward (2 LN, 4 GEMM, attention) and 9 backward (4 GEMM,
+        # 2 LN, 3 attention); per layer 10 after the last slice (4 weight-gradient GEMMs, 4 bias
+        # column sums, 2 LayerNorm-gradient reductions); plus 2 for the optimizer
         n_slices = len(self.batch_slices) * len(self.seq_slices)
-        self.launches_per_step = n_slices * self.n_layers * 18 + self.n_layers * 8 + 2
+        self.launches_per_step = n_slices * self.n_layers * 16 + self.n_layers * 10 + 2
         self.launch_count = 0
         self._ar_calls_per_step = n_slices * self.n_layers * 4 + 1
 
@@ -264,8 +264,11 @@ class StageEngine:
         self.dX0 = buf(H) if not self.is_first else None    # gradients sent to the previous stage
         self.dA = torch.empty(tmax, H, dtype=dt, device=dev)
         self.dln = sym("dln", tmax)
-        self.ln_scratch = torch.empty(F.layernorm_bwd_scratch_floats(tmax, H), dtype=torch.float32,
-                                      device=dev)
+        # LayerNorm parameter gradients: every backward launch adds its per-CTA partial sums
+        # into persistent slots; one reduction per layer folds them after the last slice
+        self.ln_parts = self.lib.tp_layernorm_bwd_parts(int(tmax))
+        self.ln_slots = [torch.zeros(2, self.ln_parts, 2 * H, dtype=torch.float32, device=dev)
+                         for _ in range(self.n_layers)]
         numel = self.L * self.B * H
         if self.is_last and self.n_layers:
             # loss = mean(output): the seed gradient is the same constant everywhere
@@ -393,10 +396,10 @@ class StageEngine:
                 self._gemm(dfc, Fl, self._p(l, "fc1.weight"), H, dln, H, T, H, Fl, b_mn=1)
                 if self.tp > 1:
                     self._all_reduce_rows(self.dln, 0, T)
-            lib.tp_layernorm_bwd(dt, dln, xmid, st + (2 * self.rows + r0) * 4,
-                                 st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur, dmid,
-                                 self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g),
-                                 self.ln_scratch.data_ptr(), T, H, s)
+            slots = self.ln_slots[l].data_ptr()
+            lib.tp_layernorm_bwd_accum(dt, dln, xmid, st + (2 * self.rows + r0) * 4,
+                                       st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur,
+                                       dmid, slots + self.ln_parts * 2 * H * 4, T, H, s)
             # ---- attention
             self._gemm(dmid, H, self._p(l, "attn.out_proj.weight"), Hl, dao, Hl, T, Hl, H, b_mn=1)
             qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
@@ -420,10 +423,8 @@ class StageEngine:
                 dnext = self.dA.data_ptr()
             else:
                 dnext = self.dX0.data_ptr() + r0 * H * es
-            lib.tp_layernorm_bwd(dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
-                                 self._p(l, "attn_ln.weight"), dmid, dnext,
-                                 self._p(l, "attn_ln.weight", g), self._p(l, "attn_ln.bias", g),
-                                 self.ln_scratch.data_ptr(), T, H, s)
+            lib.tp_layernorm_bwd_accum(dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
+                                       self._p(l, "attn_ln.weight"), dmid, dnext, slots, T, H, s)
 
     def _weight_grads(self) -> None:
         """Weight and bias gradients of every layer over all ``L*B`` rows at once:
@@ -445,6 +446,11 @@ class StageEngine:
             self._gemm(dqkv, 3 * Hl, self.ln1[l].data_ptr(), H, self._p(l, "attn.in_proj.weight", g),
                        H, 3 * Hl, H, R, a_mn=1, b_mn=1, out_f32=1, accumulate=1)
             lib.tp_colsum(dt, dqkv, 3 * Hl, R, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
+            slots = self.ln_slots[l].data_ptr()
+            lib.tp_layernorm_bwd_finish(slots, self.ln_parts, H, self._p(l, "attn_ln.weight", g),
+                                        self._p(l, "attn_ln.bias", g), s)
+            lib.tp_layernorm_bwd_finish(slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
+                                        self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g), s)
 
     # ------------------------------------------------------------------ one iteration
     def _refresh_handles(self):

@@ -1,0 +1,157 @@
+"""Micro-benchmarks of the sm_100a kernels at the GPT-3 layer shapes (CUDA-event timing).
+
+    python -m terapipe_b200.ops.bench_ops --case gemm  [--hidden 2048] [--tokens 1024]
+    python -m terapipe_b200.ops.bench_ops --case attn  [--ctx 1920] [--slice 128]
+    python -m terapipe_b200.ops.bench_ops --case norm
+    python -m terapipe_b200.ops.bench_ops --case adam
+
+``--once`` runs each kernel a few times without timing (a small, self-terminating workload
+for profiler captures).  Between timed kernels a 256 MB buffer is rewritten to flush the L2
+when ``--flush`` is given; otherwise launches run back to back (warm L2).
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from . import functional as F
+
+
+def _timeit(fn, n=20, warm=3, flush=None):
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if flush is None:
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n * 1e3
+    for _ in range(n):
+        flush.zero_()
+        e0.record()
+        fn()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / n * 1e3
+
+
+def case_gemm(a):
+    dt, dev, H, T = a.dtype, "cuda", a.hidden, a.tokens
+    shapes = {"qkv": (T, 3 * H, H), "out": (T, H, H), "fc1": (T, 4 * H, H), "fc2": (T, H, 4 * H)}
+    for name, (M, N, K) in shapes.items():
+        x = torch.randn(M, K, device=dev, dtype=dt)
+        w = torch.randn(N, K, device=dev, dtype=dt) * 0.02
+        bias = torch.zeros(N, device=dev, dtype=dt)
+        out = torch.empty(M, N, device=dev, dtype=dt)
+        run = lambda: F.gemm(x, w, out, bias=bias)  # noqa: E731
+        if a.once:
+            for _ in range(3):
+                run()
+            continue
+        us = _timeit(run, flush=a.flush_buf)
+        ref = _timeit(lambda: torch.nn.functional.linear(x, w, bias), flush=a.flush_buf)
+        print(f"gemm {name:4s} M{M} N{N} K{K}: {us:7.1f} us {2 * M * N * K / us / 1e6:7.1f} TFLOP/s"
+              f"   (torch/cuBLAS {ref:7.1f} us)")
+        dy = torch.randn(M, N, device=dev, dtype=dt)
+        dx = torch.empty(M, K, device=dev, dtype=dt)
+        us = _timeit(lambda: F.gemm(dy, w, dx, b_mn=True), flush=a.flush_buf)
+        print(f"  dgrad            : {us:7.1f} us {2 * M * N * K / us / 1e6:7.1f} TFLOP/s")
+    if not a.once:
+        R = 16 * T
+        dy = torch.randn(R, 4 * H, device=dev, dtype=dt)
+        x = torch.randn(R, H, device=dev, dtype=dt)
+        dw = torch.zeros(4 * H, H, device=dev)
+        us = _timeit(lambda: F.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True), n=5)
+        print(f"wgrad fc1 over {R} rows: {us:7.1f} us {2 * R * 4 * H * H / us / 1e6:7.1f} TFLOP/s")
+
+
+def case_attn(a):
+    dt, dev, H = a.dtype, "cuda", a.hidden
+    D, b, L, t = 128, a.batch, a.seq, a.slice
+    h = H // D
+    qkv = torch.randn(L, b, h * 3 * D, device=dev, dtype=dt)
+    o = torch.zeros(L * b, h * D, device=dev, dtype=dt)
+    lse = torch.zeros(b * h, L, device=dev)
+    delta = torch.zeros(b * h, L, device=dev)
+    dof = torch.randn(L * b, h * D, device=dev, dtype=dt)
+    dqkv = torch.zeros(t * b, h * 3 * D, device=dev, dtype=dt)
+    for c in ([a.ctx] if a.ctx is not None else [0, L // 2 - t, L - t]):
+        osl = o[c * b:(c + t) * b]
+        fwd = lambda: F.attn_fwd(qkv, b, h, D, t, c, osl, lse)  # noqa: E731
+        bwd = lambda: F.attn_bwd(qkv, b, h, D, t, c, L, osl, dof, lse, delta, dqkv)  # noqa: E731
+        if a.once:
+            for _ in range(2):
+                fwd()
+                bwd()
+            continue
+        fl = 4.0 * b * h * t * (c + t) * D
+        us = _timeit(fwd, flush=a.flush_buf)
+        print(f"attn fwd ctx={c:5d} slice={t}: {us:7.1f} us {fl / us / 1e6:7.1f} TFLOP/s")
+        us = _timeit(bwd, flush=a.flush_buf)
+        print(f"attn bwd ctx={c:5d} (dK/dV over {L - c} queries, dQ over {c + t} keys): {us:7.1f} us")
+
+
+def case_norm(a):
+    dt, dev, H, T = a.dtype, "cuda", a.hidden, a.tokens
+    x = torch.randn(T, H, device=dev, dtype=dt)
+    g = torch.ones(H, device=dev, dtype=dt)
+    bb = torch.zeros(H, device=dev, dtype=dt)
+    y = torch.empty_like(x)
+    mean, rstd = torch.empty(T, device=dev), torch.empty(T, device=dev)
+    dg, db = torch.zeros(H, device=dev), torch.zeros(H, device=dev)
+    sc = torch.empty(F.layernorm_bwd_scratch_floats(T, H), device=dev)
+    dx = torch.empty_like(x)
+    fwd = lambda: F.layernorm_fwd(x, g, bb, y, mean, rstd)  # noqa: E731
+    bwd = lambda: F.layernorm_bwd(y, x, mean, rstd, g, dx, dg, db, sc, dres=x)  # noqa: E731
+    if a.once:
+        for _ in range(3):
+            fwd()
+            bwd()
+        return
+    print(f"layernorm fwd [{T},{H}]: {_timeit(fwd, flush=a.flush_buf):6.1f} us")
+    print(f"layernorm bwd [{T},{H}]: {_timeit(bwd, flush=a.flush_buf):6.1f} us")
+
+
+def case_adam(a):
+    n = a.params // 4 * 4
+    dev = "cuda"
+    p, m, v, g = (torch.zeros(n, device=dev) for _ in range(4))
+    model = torch.zeros(n, device=dev, dtype=a.dtype)
+    st = torch.ones(3, device=dev)
+    run = lambda: F.fused_adam(g, p, m, v, model, st, lr=1e-3)  # noqa: E731
+    if a.once:
+        run()
+        return
+    us = _timeit(run, n=5)
+    print(f"fused adam {n / 1e6:.0f}M params: {us:8.1f} us {n * 34 / us / 1e3:7.0f} GB/s")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--case", required=True, choices=["gemm", "attn", "norm", "adam"])
+    ap.add_argument("--hidden", type=int, default=2048)
+    ap.add_argument("--tokens", type=int, default=1024)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--slice", type=int, default=128)
+    ap.add_argument("--ctx", type=int, default=None)
+    ap.add_argument("--params", type=int, default=302_000_000)
+    ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
+    ap.add_argument("--once", action="store_true")
+    ap.add_argument("--flush", action="store_true")
+    a = ap.parse_args()
+    a.dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
+    a.flush_buf = torch.empty(256 * 1024 * 1024, device="cuda", dtype=torch.uint8) if a.flush else None
+    {"gemm": case_gemm, "attn": case_attn, "norm": case_norm, "adam": case_adam}[a.case](a)
+    torch.cuda.synchronize()
+    F.check_device_status()
+
+
+if __name__ == "__main__":
+    main()

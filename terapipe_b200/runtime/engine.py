@@ -461,6 +461,11 @@ class StageEngine:
         if self._streams_ready:
             return
         self.recv_stream = torch.cuda.Stream()
+        # One 2-rank process group per pipeline link: its own NCCL communicator and stream, so
+        # traffic with the previous stage never queues behind traffic with the next stage (on
+        # a shared communicator the pre-posted receives would hold back every send).
+        self._link_prev = mpu.get_pipeline_parallel_succ_group()
+        self._link_next = mpu.get_pipeline_parallel_pred_group()
         self._streams_ready = True
 
     def _post_recvs(self, forward: bool):
@@ -468,6 +473,7 @@ class StageEngine:
         compute of earlier slices; returns the work handles in consumption order."""
         works = {}
         src = mpu.get_pipeline_prev_rank() if forward else mpu.get_pipeline_next_rank()
+        group = self._link_prev if forward else self._link_next
         buf = self.X[0] if forward else self.dY
         order = [(bi, si) for bi in range(len(self.batch_slices)) for si in range(len(self.seq_slices))]
         if not forward:
@@ -478,7 +484,7 @@ class StageEngine:
         with torch.cuda.stream(self.recv_stream):
             for bi, si in order:
                 _, b, _, t, r0 = self.slices[bi][si]
-                works[(bi, si)] = dist.irecv(buf[r0:r0 + t * b], src)
+                works[(bi, si)] = dist.irecv(buf[r0:r0 + t * b], src, group=group)
         torch.cuda.current_stream().wait_stream(self.recv_stream)
         return works
 
@@ -498,7 +504,7 @@ class StageEngine:
                 if pipelined and not self.is_last:
                     _, b, _, t, r0 = sl
                     sends.append(dist.isend(self.X[self.n_layers][r0:r0 + t * b],
-                                            mpu.get_pipeline_next_rank()))
+                                            mpu.get_pipeline_next_rank(), group=self._link_next))
         if self.is_last:
             self.loss_buf.copy_(self.X[self.n_layers].sum(dtype=torch.float32))
         recvs = self._post_recvs(False) if (pipelined and not self.is_last) else None
@@ -510,7 +516,8 @@ class StageEngine:
                 self._backward_slice(sl)
                 if pipelined and not self.is_first:
                     _, b, _, t, r0 = sl
-                    sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank()))
+                    sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank(),
+                                            group=self._link_prev))
         self._weight_grads()
         for w in sends:
             w.wait()

@@ -533,3 +533,45 @@ extern "C" int tp_fill(int dtype, void* p, long long n, float value, void* strea
   else fill_kernel<__half><<<static_cast<int>(blocks), 256, 0, s>>>(static_cast<__half*>(p), n, value);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+// LayerNorm backward for callers that cannot allocate: the per-CTA partial sums go to a fixed
+// array inside the library image instead of a caller-provided buffer (see terapipe_noalloc.h).
+#include "terapipe_noalloc.h"
+
+namespace tp {
+constexpr int kStaticSlots = 160;
+constexpr int kStaticMaxH = 4096;
+constexpr long long kStaticScratchFloats = static_cast<long long>(kStaticSlots) * 2 * kStaticMaxH;
+// In host code this name is only a handle for cudaGetSymbolAddress; kernels get the address.
+static __device__ __align__(256) float g_ln_static_scratch[kStaticScratchFloats];
+}  // namespace tp
+
+extern "C" long long tp_layernorm_bwd_noalloc_capacity(void) { return tp::kStaticScratchFloats; }
+
+extern "C" int tp_layernorm_bwd_noalloc(int dtype, const void* dy, const void* x, const float* mean,
+                                        const float* rstd, const void* gamma, const void* dres,
+                                        void* dx, float* dgamma, float* dbeta, int rows, int H,
+                                        void* stream) {
+  constexpr int kMaxDevices = 64;
+  static float* scratch_of_device[kMaxDevices] = {nullptr};
+  if (rows <= 0) return kOk;
+  if (H <= 0 || H % 8) return kErrBadArgument;
+  if (H > kStaticMaxH) return kErrTooLarge;
+  const int parts = tp_layernorm_bwd_parts(rows);
+  if (static_cast<long long>(parts) * 2 * H > kStaticScratchFloats) return kErrTooLarge;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kErrDriver;
+  if (!scratch_of_device[dev]) {
+    // once per device, with that device current: resolve the array's device address
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_static_scratch) != cudaSuccess || !p) {
+      cudaGetLastError();
+      return kErrDriver;
+    }
+    scratch_of_device[dev] = p;
+  }
+  // mode 0 writes every slot it later reads, so stale contents of the shared array are harmless
+  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, dx, dgamma, dbeta,
+                              scratch_of_device[dev], rows, H, 0, static_cast<cudaStream_t>(stream));
+}

@@ -54,6 +54,7 @@ def parse_args():
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--activation", default=None, choices=[None, "gelu", "relu"])
     ap.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
+    ap.add_argument("--dp-comm", default="nccl", choices=["nccl", "fused"])
     ap.add_argument("--no-graph", action="store_true", help="never capture the step in a CUDA graph")
     ap.add_argument("--graph", action="store_true", help="capture even when the stage communicates")
     ap.add_argument("--no-e2e", action="store_true")
@@ -181,7 +182,7 @@ def run_ours(args):
                       batch_slices=batch_slices, seq_slices=seq_slices,
                       dtype=args.dtype, n_layers=args.n_layers, activation=args.activation or "gelu",
                       use_graph=(False if args.no_graph else (True if args.graph else None)),
-                      tp_comm=args.tp_comm)
+                      tp_comm=args.tp_comm, dp_comm=args.dp_comm)
     cfg = trainer.config
     tokens = cfg.batch_size * cfg.seq_len * trainer.topo.dp
 
@@ -234,7 +235,7 @@ def run_ours(args):
                        "seq_len": cfg.seq_len, "parallelism": f"pp{pp}xtp{args.tp}xdp{trainer.topo.dp}",
                        "batch_slices": batch_slices, "seq_slices": seq_slices,
                        "activation": cfg.activation, "mixed_precision": "fp32 master + Adam, loss scale 128",
-                       "cuda_graph": bool(trainer.engine.use_graph), "tp_comm": trainer.engine.tp_comm,
+                       "cuda_graph": bool(trainer.engine.use_graph), "tp_comm": trainer.engine.tp_comm, "dp_comm": trainer.engine.dp_comm,
                        "l2": "per-step working set (weights + activations, several GB) far exceeds the 126 MB L2"},
             "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
         }

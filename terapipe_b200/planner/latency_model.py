@@ -86,8 +86,13 @@ def _fit_context_model(rows, targets, holdout=0.25, seed=42):
 def fit_latency_tables(latency_table: Dict[Tuple[int, int, int], dict],
                        comm_table: Optional[dict], batch_size: int, seqlen: int,
                        layers_per_stage: int, step_gap: int = STEP_GAP,
-                       fill_missing: bool = True, verbose: bool = False) -> SingleLayerLatency:
+                       fill_missing: bool = True, verbose: bool = False,
+                       total_batch: Optional[int] = None) -> SingleLayerLatency:
     update_time = float(np.mean([t["update_mean"] for t in latency_table.values()]))
+    wg = [t["wgrad_per_token_mean"] for t in latency_table.values() if "wgrad_per_token_mean" in t]
+    if wg:
+        # per-layer constant of an iteration: optimizer + whole-sequence weight gradients
+        update_time += float(np.median(wg)) * seqlen * (total_batch or batch_size)
     ns = seqlen // step_gap + 1
     t0 = np.full((batch_size + 1, ns), np.inf)
     for (b, s, c), t in latency_table.items():
@@ -136,7 +141,7 @@ def fit_latency_tables(latency_table: Dict[Tuple[int, int, int], dict],
 
 def fit_single_layer_model(model_name, model_parallel_size, layers_per_node,
                            data_dir="performance_model_data", step_gap=STEP_GAP,
-                           batch_size=None, verbose=True):
+                           batch_size=None, verbose=True, total_batch=None):
     """Load ``latency_model.<model>.mp_<mp>.json`` and ``<model>.communication_latency.json``
     from ``data_dir`` and fit the stage model."""
     with open(os.path.join(data_dir, f"latency_model.{model_name}.mp_{model_parallel_size}.json")) as f:
@@ -146,8 +151,9 @@ def fit_single_layer_model(model_name, model_parallel_size, layers_per_node,
     seqlen = MODEL_CONFIGS[model_name][2]
     if batch_size is None:
         batch_size = BATCH_CONFIGS.get(model_name, max(k[0] for k in table))
+    batch_size = min(batch_size, max(k[0] for k in table))
     return fit_latency_tables(table, comm, batch_size, seqlen, layers_per_node, step_gap,
-                              verbose=verbose)
+                              verbose=verbose, total_batch=total_batch)
 
 
 # ------------------------------------------------------------------------- dynamic program
@@ -283,7 +289,7 @@ def analysis_model(model_name, total_batch_size, model_parallel_size, pipelinele
     lm = fit_single_layer_model(model_name, model_parallel_size, layers_per_node, data_dir,
                                 step_gap, batch_size=max(total_batch_size,
                                                          BATCH_CONFIGS.get(model_name, 0)),
-                                verbose=verbose)
+                                verbose=verbose, total_batch=total_batch_size)
     scheme, latency = search_schedule(lm, total_batch_size, seqlen, pipelinelen, layers_per_node)
     if verbose and scheme is not None:
         print(latency, scheme, len(scheme), evaluate_split(lm, scheme, pipelinelen, layers_per_node))
@@ -310,12 +316,17 @@ B200_SETTINGS = [
 ]
 
 
-def main(settings=None, data_dir="performance_model_data", out="dp_results.json"):
+def main(settings=None, data_dir="performance_model_data", out="dp_results.json", step_gap=None):
     settings = settings or B200_SETTINGS
     results = []
     for s in settings:
         try:
-            scheme, latency = analysis_model(*s[:4], data_dir=data_dir)
+            gap = step_gap
+            if gap is None:  # the granularity the table was measured with
+                path = os.path.join(data_dir, f"latency_model.{s[0]}.mp_{s[2]}.json")
+                lens = sorted({int(k.split("_")[1]) for k in json.load(open(path))})
+                gap = min(b - a for a, b in zip(lens, lens[1:])) if len(lens) > 1 else STEP_GAP
+            scheme, latency = analysis_model(*s[:4], data_dir=data_dir, step_gap=gap)
         except FileNotFoundError as e:
             print(f"skip {s[0]}: {e}")
             continue

@@ -83,7 +83,7 @@ class StageEngine:
     def __init__(self, config: TransformerConfig, batch_slices: Sequence[int],
                  seq_slices: Sequence[int], dtype=torch.float16, loss_scale=LOSS_SCALE_FACTOR,
                  lr=1e-10, seed=0, init="device", use_graph: Optional[bool] = None,
-                 tp_comm="nccl", device=None):
+                 tp_comm="nccl", dp_comm="nccl", device=None):
         assert torch.cuda.is_available(), "StageEngine needs a CUDA device (sm_100a)"
         self.cfg = config
         self.batch_slices, self.seq_slices = list(batch_slices), list(seq_slices)
@@ -100,6 +100,7 @@ class StageEngine:
         self.layer_ids = self.topo.layers_of_stage(config.n_layers, self.pp_idx)
         self.n_layers = len(self.layer_ids)
         self.tp_comm = tp_comm if self.tp > 1 else "none"
+        self.dp_comm = dp_comm if self.dp > 1 else "none"
 
         H, Fw = config.embedding_dim, config.ffn_embedding_dim
         heads = config.num_attention_heads
@@ -117,11 +118,26 @@ class StageEngine:
         self.layout = _Layout(self.n_layers, H, Fw, self.tp)
         n = self.layout.total
         dev = self.device
-        self.model = torch.zeros(n, dtype=dtype, device=dev)
+        self.dp_sym = None
+        if self.dp_comm == "fused":
+            # gradients and the 16-bit parameters must be peer-mapped inside the DP group: the
+            # fused reduction reads every replica's gradients and writes every replica's model
+            from ..parallel.symm import SymmetricBuffer
+            model_bytes = (n * 2 + 255) // 256 * 256
+            self.dp_sym = SymmetricBuffer(1024 + model_bytes + n * 4, mpu.get_data_parallel_group())
+            self._dp_off_model, self._dp_off_grad = 1024, 1024 + model_bytes
+            self.model = self.dp_sym.view(self._dp_off_model, (n,), dtype)
+            self.grad = self.dp_sym.view(self._dp_off_grad, (n,), torch.float32)
+            self.dp_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
+            chunk = ((n + self.dp - 1) // self.dp + 3) // 4 * 4
+            self._dp_begin = min(n, self.dp_idx * chunk)
+            self._dp_end = min(n, self._dp_begin + chunk)
+        else:
+            self.model = torch.zeros(n, dtype=dtype, device=dev)
+            self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
         self.master = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
         self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
         self.adam_state = torch.zeros(3, dtype=torch.float32, device=dev)
         self._init_weights(init)
         self._alloc_activations()
@@ -129,9 +145,11 @@ class StageEngine:
         self.loss_buf = torch.zeros(1, dtype=torch.float32, device=dev)
         # A CUDA graph may hold this library's kernels only: captured NCCL point-to-point or
         # collective calls deadlocked on replay here, so a stage that calls NCCL runs eagerly.
-        nccl_free = self.pp == 1 and self.dp == 1 and (self.tp == 1 or self.tp_comm == "fused")
+        nccl_free = (self.pp == 1 and (self.dp == 1 or self.dp_comm == "fused")
+                     and (self.tp == 1 or self.tp_comm == "fused"))
         self.use_graph = nccl_free if use_graph is None else (bool(use_graph) and nccl_free)
         self._graph = None
+        self.timeline = None   # set to a utils.trace.SliceTimeline to record per-slice device times
         self.step_count = 0
         self._streams_ready = False
         # launches of this library's own kernels (NCCL and torch kernels are not counted):
@@ -493,6 +511,8 @@ class StageEngine:
         if pipelined:
             self._setup_streams()
         nb, ns = len(self.batch_slices), len(self.seq_slices)
+        if self.timeline is not None:
+            self.timeline.begin_iteration()
         sends = []
         recvs = self._post_recvs(True) if (pipelined and not self.is_first) else None
         for bi in range(nb):
@@ -500,7 +520,11 @@ class StageEngine:
                 sl = self.slices[bi][si]
                 if recvs is not None:
                     recvs[(bi, si)].wait()
-                self._forward_slice(sl)
+                if self.timeline is not None:
+                    with self.timeline.slice("forward", bi, si):
+                        self._forward_slice(sl)
+                else:
+                    self._forward_slice(sl)
                 if pipelined and not self.is_last:
                     _, b, _, t, r0 = sl
                     sends.append(dist.isend(self.X[self.n_layers][r0:r0 + t * b],
@@ -513,7 +537,11 @@ class StageEngine:
                 sl = self.slices[bi][si]
                 if recvs is not None:
                     recvs[(bi, si)].wait()
-                self._backward_slice(sl)
+                if self.timeline is not None:
+                    with self.timeline.slice("backward", bi, si):
+                        self._backward_slice(sl)
+                else:
+                    self._backward_slice(sl)
                 if pipelined and not self.is_first:
                     _, b, _, t, r0 = sl
                     sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank(),
@@ -523,6 +551,21 @@ class StageEngine:
             w.wait()
 
     def _reduce_and_update(self):
+        if self.dp_sym is not None:
+            # one kernel: peer-load every replica's gradients for the owned chunk, Adam on that
+            # chunk, peer-store the new 16-bit parameters into every replica
+            F.adam_tick(self.adam_state)
+            self.lib.tp_advance_counter(self.dp_epoch_base.data_ptr(), 1, self._stream)
+            sym = self.dp_sym
+            st = self.lib.tp_dp_reduce_adam(
+                self.dt, self.dp, sym.rank, 0, self.dp_epoch_base.data_ptr(),
+                sym.ptr_array(self._dp_off_grad), sym.ptr_array(self._dp_off_model), sym.ptr_array(0),
+                self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
+                self._dp_begin, self._dp_end, self.adam_state.data_ptr(), self.lr, 0.9, 0.999, 1e-8,
+                0.0, 1.0 / (self.loss_scale * self.dp), self._status_ptr, self._stream)
+            if st:
+                F.check(st, "tp_dp_reduce_adam")
+            return
         if self.dp > 1:
             dist.all_reduce(self.grad, group=mpu.get_data_parallel_group())
         F.adam_tick(self.adam_state)
@@ -537,6 +580,10 @@ class StageEngine:
             self.lib.tp_advance_counter(self.ar_epoch_base.data_ptr(), self._ar_calls_per_step,
                                         self._stream)
             self._ar_calls = 0
+        if self.dp_sym is not None and update:
+            # the fused reduction does not clear gradients (peers read them); clear them here,
+            # after the previous reduction's end handshake and before this iteration adds to them
+            self.grad.zero_()
         self._forward_backward()
         if update:
             self._reduce_and_update()

@@ -29,7 +29,7 @@ class Trainer:
                  batch_slices: Optional[Sequence[int]] = None,
                  seq_slices: Optional[Sequence[int]] = None, dtype="fp16",
                  n_layers: Optional[int] = None, activation: str = "gelu", use_graph=None,
-                 tp_comm: str = "nccl", lr: float = 1e-10, seed: int = 0, init: str = "device",
+                 tp_comm: str = "nccl", dp_comm: str = "nccl", lr: float = 1e-10, seed: int = 0, init: str = "device",
                  loss_scale: float = 128.0):
         if dist.is_initialized():
             if not mpu.model_parallel_is_initialized():
@@ -46,7 +46,7 @@ class Trainer:
         self.seed = seed
         self.engine = StageEngine(self.config, batch_slices, seq_slices, dtype=self.dtype,
                                   loss_scale=loss_scale, lr=lr, seed=seed, init=init,
-                                  use_graph=use_graph, tp_comm=tp_comm)
+                                  use_graph=use_graph, tp_comm=tp_comm, dp_comm=dp_comm)
         self._staging = None
 
     @property

@@ -5,7 +5,9 @@ For one layer (tensor parallel over ``--model-parallel-size`` ranks, no pipeline
 slice, times forward, backward and optimizer update on the device for a grid of
 ``(batch, slice_len, context_len)`` and writes
 ``performance_model_data/latency_model.<model>.mp_<mp>.json`` (keys ``"b_s_c"``; fields
-``{py_forward,forward,py_backward,backward,update}_{mean,std}``).  Existing keys are skipped,
+``{py_forward,forward,py_backward,backward,update}_{mean,std}`` plus ``wgrad_per_token_*``:
+the engine computes weight gradients once per iteration over all rows, so their cost is
+reported per token instead of inside ``backward``).  Existing keys are skipped,
 so an interrupted run resumes; the file is flushed every ``--flush-every`` points.  Flags follow
 the reference tool (terapipe_latency_model.py:120-141); ``--step-gap`` / ``--scan-grid`` choose
 a coarser grid than its (8, (16,16,4)).
@@ -44,7 +46,7 @@ class TerapipeLatencyModel:
         if e.ar is not None:
             e.lib.tp_advance_counter(e.ar_epoch_base.data_ptr(), e._ar_calls_per_step, e._stream)
             e._ar_calls = 0
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(4)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
         t0 = time.time()
         ev[0].record()
         e._forward_slice(self.target)
@@ -52,14 +54,17 @@ class TerapipeLatencyModel:
         py_fwd = time.time() - t0
         t0 = time.time()
         e._backward_slice(self.target)
-        e._weight_grads()
         ev[2].record()
         py_bwd = time.time() - t0
-        e._reduce_and_update()
+        # weight gradients run once per iteration over all rows, not per slice: they are timed
+        # apart and reported per token so the planner can add them as a per-layer constant
+        e._weight_grads()
         ev[3].record()
+        e._reduce_and_update()
+        ev[4].record()
         torch.cuda.synchronize()
         return (py_fwd, ev[0].elapsed_time(ev[1]) / 1e3, py_bwd, ev[1].elapsed_time(ev[2]) / 1e3,
-                ev[2].elapsed_time(ev[3]) / 1e3)
+                ev[3].elapsed_time(ev[4]) / 1e3, ev[2].elapsed_time(ev[3]) / 1e3 / e.rows)
 
     def run(self, n_steps=10, warmup_steps=5):
         # the prefix rows must hold valid keys/values: run the context slice once
@@ -69,7 +74,7 @@ class TerapipeLatencyModel:
             e._forward_slice(sl)
         rows = [self.step() for _ in range(n_steps + warmup_steps)][warmup_steps:]
         arr = np.array(rows)
-        names = ("py_forward", "forward", "py_backward", "backward", "update")
+        names = ("py_forward", "forward", "py_backward", "backward", "update", "wgrad_per_token")
         out = {}
         for i, n in enumerate(names):
             out[n + "_mean"] = float(arr[:, i].mean())

@@ -104,6 +104,8 @@ def run(args, dist_env, timed_steps, ClockSampler, slices_from_args) -> None:
             if args.schedule:
                 with open(args.schedule) as f:
                     sched = json.load(f)
+                if isinstance(sched, list):
+                    sched = sched[getattr(args, "schedule_index", 0)]
                 batch_slices, seq_slices = list(sched["batch_slices"]), list(sched["input_slices"])
             else:
                 batch_slices = uniform_slice(args.batch, args.batch_slices)

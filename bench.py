@@ -50,7 +50,9 @@ def parse_args():
     ap.add_argument("--pp", type=int, default=None)
     ap.add_argument("--seq-slices", type=int, default=16)
     ap.add_argument("--batch-slices", type=int, default=1)
-    ap.add_argument("--schedule", default=None, help="JSON file with batch_slices / input_slices lists")
+    ap.add_argument("--schedule", default=None,
+                    help="JSON file with batch_slices / input_slices lists, or a dp_results.json list")
+    ap.add_argument("--schedule-index", type=int, default=0, help="entry of a dp_results.json list")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--activation", default=None, choices=[None, "gelu", "relu"])
     ap.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
@@ -126,6 +128,8 @@ def slices_from_args(args, seq_len):
     if args.schedule:
         with open(args.schedule) as f:
             sched = json.load(f)
+        if isinstance(sched, list):
+            sched = sched[args.schedule_index]
         return list(sched["batch_slices"]), list(sched["input_slices"])
     return uniform_slice(args.batch, args.batch_slices), uniform_slice(seq_len, args.seq_slices)
 

@@ -98,12 +98,17 @@ constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
 
-template <int BN> struct GemmCfg {
-  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 6 : 8);
-  static constexpr int kABytes = kBM * kBK * 2;
+// MT = number of 128-row sub-tiles of the CTA tile (1 or 2).  MT = 2 with BN = 256 gives a
+// 256x256 tile: two MMAs per k-step share one B tile, which halves the shared-memory bytes
+// fetched per FLOP (64 B/clk/SM at full rate instead of 96-128); both accumulators then fill
+// the 512 TMEM columns, so the epilogue of a tile does not overlap the next tile's main loop.
+template <int BN, int MT = 1> struct GemmCfg {
+  static constexpr int kStages = MT == 2 ? 3 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+  static constexpr int kABytes = MT * kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = BN == 64 ? 128 : 2 * BN;  // two accumulators, power of two
+  static constexpr int kAccBuffers = MT == 2 ? 1 : 2;
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -116,12 +121,15 @@ __device__ __forceinline__ float gelu_grad_f(float z) {
   return cdf + z * pdf;
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const GemmParams p, const ArParams ar) {
-  using Cfg = GemmCfg<BN>;
+  using Cfg = GemmCfg<BN, MT>;
   constexpr int S = Cfg::kStages;
+  constexpr int BM = MT * kBM;
+  constexpr int NACC = Cfg::kAccBuffers;
+  static_assert(!(AR && MT != 1), "the fused all-reduce path uses 128-row tiles");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -168,7 +176,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int stage = 0;
       uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
-        const int m0 = (tile % p.num_m_tiles) * kBM;
+        const int m0 = (tile % p.num_m_tiles) * BM;
         const int n0 = (tile / p.num_m_tiles) * BN;
         bool ok = true;
         for (int kb = 0; kb < num_kb && ok; ++kb) {
@@ -181,7 +189,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             tma_load_2d(sA, &tmA, &full[stage], kb * kBK, m0);
           } else {
 #pragma unroll
-            for (int c = 0; c < kBM / 64; ++c)
+            for (int c = 0; c < BM / 64; ++c)
               tma_load_2d(sA + c * (kBK * 128), &tmA, &full[stage], m0 + c * 64, kb * kBK);
           }
           if (!B_MN) {
@@ -204,8 +212,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
-        const int acc = it & 1;
-        const uint32_t acc_phase = (it >> 1) & 1;
+        const int acc = it % NACC;
+        const uint32_t acc_phase = (it / NACC) & 1;
         ok = mbar_wait(&tempty[acc], acc_phase ^ 1, wctx, kErrWaitTmemEmpty);
         if (!ok) break;
         tc_fence_after();
@@ -218,11 +226,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           const uint32_t b_base = a_base + Cfg::kABytes;
 #pragma unroll
           for (int k = 0; k < kBK / 16; ++k) {
-            const uint64_t da = A_MN ? umma_desc_sw128(a_base + k * 2048, kBK * 128, 1024)
-                                     : umma_desc_sw128(a_base + k * 32, 16, 1024);
             const uint64_t db = B_MN ? umma_desc_sw128(b_base + k * 2048, kBK * 128, 1024)
                                      : umma_desc_sw128(b_base + k * 32, 16, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              // sub-tile mt: rows [128 mt, 128 mt + 128) of the A tile (K-major: 128 rows of
+              // 128 B; M-major: two 64-wide chunks of kBK rows each)
+              const uint32_t a_sub = a_base + mt * (A_MN ? 2 * kBK * 128 : kBM * 128);
+              const uint64_t da = A_MN ? umma_desc_sw128(a_sub + k * 2048, kBK * 128, 1024)
+                                       : umma_desc_sw128(a_sub + k * 32, 16, 1024);
+              umma_f16(d_tmem + mt * BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
           }
           umma_commit(&empty[stage]);
           if (++stage == S) { stage = 0; phase ^= 1; }
@@ -237,20 +251,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
-      const int acc = it & 1;
-      const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile % p.num_m_tiles) * kBM;
+      const int acc = it % NACC;
+      const uint32_t acc_phase = (it / NACC) & 1;
+      const int m0 = (tile % p.num_m_tiles) * BM;
       const int n0 = (tile / p.num_m_tiles) * BN;
       ok = mbar_wait(&tfull[acc], acc_phase, wctx, kErrWaitEpilogue);
       if (!ok) break;
       tc_fence_after();
-      const long long row = m0 + row_in_tile;
-      const bool row_ok = row < p.M;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int cm = 0; cm < MT * BN; cm += 32) {
+        const int mt = cm / BN, c0 = cm % BN;
+        const long long row = m0 + mt * kBM + row_in_tile;
+        const bool row_ok = row < p.M;
         uint32_t r[32];
         __syncwarp();
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c0, r);
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cm, r);
         tmem_ld_wait();
         if (AR) {
           // phase A: 16-bit partial of this chunk into the owner's staging tile (peer store)
@@ -465,11 +480,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false, int MT = 1>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                        cudaStream_t stream, const ArParams* arp = nullptr) {
-  using Cfg = GemmCfg<BN>;
-  auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR>;
+  using Cfg = GemmCfg<BN, MT>;
+  auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR, MT>;
   ArParams ar;
   if (arp) ar = *arp;
   else ar.tp = 0;
@@ -485,27 +500,35 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
-template <typename T, int BN>
+template <typename T, int BN, int MT = 1>
 static int dispatch_layout(int a_mn, int b_mn, int out_f32, const CUtensorMap& tmA,
                            const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
-  if (!a_mn && !b_mn && !out_f32) return launch_gemm<T, BN, false, false, false>(tmA, tmB, p, s);
-  if (!a_mn && b_mn && !out_f32) return launch_gemm<T, BN, false, true, false>(tmA, tmB, p, s);
-  if (a_mn && b_mn && out_f32) return launch_gemm<T, BN, true, true, true>(tmA, tmB, p, s);
-  if (!a_mn && !b_mn && out_f32) return launch_gemm<T, BN, false, false, true>(tmA, tmB, p, s);
-  if (a_mn && b_mn && !out_f32) return launch_gemm<T, BN, true, true, false>(tmA, tmB, p, s);
+  if (!a_mn && !b_mn && !out_f32) return launch_gemm<T, BN, false, false, false, false, MT>(tmA, tmB, p, s);
+  if (!a_mn && b_mn && !out_f32) return launch_gemm<T, BN, false, true, false, false, MT>(tmA, tmB, p, s);
+  if (a_mn && b_mn && out_f32) return launch_gemm<T, BN, true, true, true, false, MT>(tmA, tmB, p, s);
+  if (MT == 1) {  // rarely used layouts: only the 128-row tile is instantiated
+    if (!a_mn && !b_mn && out_f32) return launch_gemm<T, BN, false, false, true>(tmA, tmB, p, s);
+    if (a_mn && b_mn && !out_f32) return launch_gemm<T, BN, true, true, false>(tmA, tmB, p, s);
+  }
   return kErrBadArgument;
 }
 
-static int pick_bn(int M, int N, int forced) {
+// Tile choice.  Encoded as BN, or 512 for the 256x256 tile.  Relative time of one tile =
+// (tile FLOPs) / (fraction of the MMA rate the shared-memory feed sustains for that shape);
+// total = waves x that.  Wave quantisation matters because M is only ~1024 rows per slice.
+static int pick_tile(int M, int N, int forced, bool allow_256x256) {
   if (forced == 64 || forced == 128 || forced == 256) return forced;
+  if (forced == 512) return allow_256x256 ? 512 : 256;
   const int sms = num_sms();
-  const int mt = (M + kBM - 1) / kBM;
-  const int cand[3] = {256, 128, 64};
-  const float cost[3] = {2.0f, 1.1f, 0.7f};
+  const int cand[4] = {512, 256, 128, 64};
+  const int bm[4] = {256, 128, 128, 128};
+  const int bn[4] = {256, 256, 128, 64};
+  const float cost[4] = {4.4f, 3.6f, 2.0f, 1.25f};
   int best = 128;
   float best_t = 1e30f;
-  for (int i = 0; i < 3; ++i) {
-    const int tiles = mt * ((N + cand[i] - 1) / cand[i]);
+  for (int i = 0; i < 4; ++i) {
+    if (i == 0 && !allow_256x256) continue;
+    const int tiles = ((M + bm[i] - 1) / bm[i]) * ((N + bn[i] - 1) / bn[i]);
     const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
     if (t < best_t) { best_t = t; best = cand[i]; }
   }
@@ -527,10 +550,15 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
     return kErrBadArgument;
   if (accumulate && !out_f32) return kErrBadArgument;
   const bool bf16 = dtype == 1;
-  const int BN = pick_bn(M, N, force_bn);
+  const bool common_layout = (!a_mn && !out_f32) || (a_mn && b_mn && out_f32);
+  // the 256x256 tile pays off only when the main loop is long enough to amortise its
+  // non-overlapped epilogue (weight gradients over all tokens; not the K = hidden products)
+  const int tile_code = pick_tile(M, N, force_bn, common_layout && (K >= 4096 || force_bn == 512));
+  const int BN = tile_code == 512 ? 256 : tile_code;
+  const int BM = tile_code == 512 ? 256 : kBM;
   CUtensorMap tmA, tmB;
   bool ok;
-  if (!a_mn) ok = make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16);
+  if (!a_mn) ok = make_tmap_2d(&tmA, A, K, M, lda, kBK, BM, bf16);
   else ok = make_tmap_2d(&tmA, A, M, K, lda, 64, kBK, bf16);
   if (!ok) return kErrDriver;
   if (!b_mn) ok = make_tmap_2d(&tmB, B, K, N, ldb, kBK, BN, bf16);
@@ -538,7 +566,7 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   if (!ok) return kErrDriver;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.num_m_tiles = (M + kBM - 1) / kBM;
+  p.num_m_tiles = (M + BM - 1) / BM;
   p.num_tiles = p.num_m_tiles * ((N + BN - 1) / BN);
   p.out = out; p.ldo = ldo;
   p.bias = bias; p.residual = residual; p.ldr = ldr;
@@ -547,7 +575,8 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   p.err = err_flag;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define TP_DISPATCH(T)                                                                   \
-  (BN == 256 ? dispatch_layout<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)              \
+  (tile_code == 512 ? dispatch_layout<T, 256, 2>(a_mn, b_mn, out_f32, tmA, tmB, p, s)    \
+   : BN == 256 ? dispatch_layout<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)            \
              : BN == 128 ? dispatch_layout<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
                          : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, p, s))
   return bf16 ? TP_DISPATCH(__nv_bfloat16) : TP_DISPATCH(__half);

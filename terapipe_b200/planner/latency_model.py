@@ -92,7 +92,9 @@ def fit_latency_tables(latency_table: Dict[Tuple[int, int, int], dict],
     wg = [t["wgrad_per_token_mean"] for t in latency_table.values() if "wgrad_per_token_mean" in t]
     if wg:
         # per-layer constant of an iteration: optimizer + whole-sequence weight gradients
-        update_time += float(np.median(wg)) * seqlen * (total_batch or batch_size)
+        # per-token cost at the largest measured row count (small row counts under-use the GPU)
+        rows = [k[0] * (k[1] + k[2]) for k, t in latency_table.items() if "wgrad_per_token_mean" in t]
+        update_time += float(wg[int(np.argmax(rows))]) * seqlen * (total_batch or batch_size)
     ns = seqlen // step_gap + 1
     t0 = np.full((batch_size + 1, ns), np.inf)
     for (b, s, c), t in latency_table.items():
@@ -193,17 +195,8 @@ def _planning_numpy(grid, B, n, max_latency):
     return g[B], gmax[B], fstep, gstep
 
 
-def planning(latency_grid, total_batch_size, total_seqlen, pipelinelen, max_latency,
-             step_gap=STEP_GAP, use_native=True):
-    """Best schedule whose every slice takes at most ``max_latency``.
-
-    Returns ``(total_time, scheme)`` where ``total_time = (K-1) * max_slice + sum`` and
-    ``scheme = [(batch_slice_size, [token slices, last first]), ...]`` (the same order the
-    reference returns, latency_model.py:137-148), or ``(inf, None)``."""
-    assert total_seqlen % step_gap == 0
-    grid = np.ascontiguousarray(latency_grid, dtype=np.float64)
-    n = total_seqlen // step_gap
-    B = int(total_batch_size)
+def _dp_tables(grid, B, n, max_latency, use_native=True):
+    """(sum, max, f_step, g_step) of the recurrences, from the C++ library when available."""
     lib = None
     if use_native:
         try:
@@ -211,28 +204,68 @@ def planning(latency_grid, total_batch_size, total_seqlen, pipelinelen, max_late
             lib = host_lib()
         except Exception:
             lib = None
-    if lib is not None:
-        fstep = np.zeros((B + 1, n + 1), dtype=np.int64)
-        gstep = np.zeros(B + 1, dtype=np.int64)
-        mx = ctypes.c_double(0.0)
-        total = lib.tp_plan_slices(grid.ctypes.data, grid.shape[0], grid.shape[1], grid.shape[2],
-                                   B, n, float(max_latency), fstep.ctypes.data, gstep.ctypes.data,
-                                   ctypes.byref(mx))
-        mx = mx.value
-    else:
-        total, mx, fstep, gstep = _planning_numpy(grid, B, n, max_latency)
+    if lib is None:
+        return _planning_numpy(grid, B, n, max_latency)
+    fstep = np.zeros((B + 1, n + 1), dtype=np.int64)
+    gstep = np.zeros(B + 1, dtype=np.int64)
+    mx = ctypes.c_double(0.0)
+    total = lib.tp_plan_slices(grid.ctypes.data, grid.shape[0], grid.shape[1], grid.shape[2],
+                               B, n, float(max_latency), fstep.ctypes.data, gstep.ctypes.data,
+                               ctypes.byref(mx))
+    return total, mx.value, fstep, gstep
+
+
+def _token_slices(fstep, bs, n, step_gap):
+    """Backtrack one batch-slice size: token slices, last first, or None if infeasible."""
+    lens, cur = [], n
+    while cur > 0:
+        s = int(fstep[bs, cur])
+        if s <= 0:
+            return None
+        lens.append(s * step_gap)
+        cur -= s
+    return lens
+
+
+def planning(latency_grid, total_batch_size, total_seqlen, pipelinelen, max_latency,
+             step_gap=STEP_GAP, use_native=True, uniform_batch=False):
+    """Best schedule whose every slice takes at most ``max_latency``.
+
+    Returns ``(total_time, scheme)`` where ``total_time = (K-1) * max_slice + sum`` and
+    ``scheme = [(batch_slice_size, [token slices, last first]), ...]`` (the same order the
+    reference returns, latency_model.py:137-148), or ``(inf, None)``.
+
+    ``uniform_batch=True`` only considers equal batch slices (sizes dividing the batch), so that
+    every batch slice uses the same token slicing, which the runtimes require (the reference
+    asserts it after planning, latency_model.py:240)."""
+    assert total_seqlen % step_gap == 0
+    grid = np.ascontiguousarray(latency_grid, dtype=np.float64)
+    n = total_seqlen // step_gap
+    B = int(total_batch_size)
+    total, mx, fstep, gstep = _dp_tables(grid, B, n, max_latency, use_native)
+    if uniform_batch:
+        best = (float("inf"), None)
+        for bs in range(1, B + 1):
+            if B % bs or bs >= grid.shape[0]:
+                continue
+            lens = _token_slices(fstep, bs, n, step_gap)
+            if lens is None:
+                continue
+            ctx, tot, big = 0, 0.0, 0.0
+            for t in reversed(lens):
+                lat = grid[bs, t // step_gap, ctx // step_gap]
+                tot, big, ctx = tot + lat, max(big, lat), ctx + t
+            cand = (B // bs) * tot + (pipelinelen - 1) * big
+            if cand < best[0]:
+                best = (cand, [(bs, list(lens)) for _ in range(B // bs)])
+        return best
     if not np.isfinite(total):
         return float("inf"), None
     scheme: Scheme = []
     cur_b = B
     while cur_b > 0:
         bs = int(gstep[cur_b])
-        lens, cur = [], n
-        while cur > 0:
-            s = int(fstep[bs, cur])
-            lens.append(s * step_gap)
-            cur -= s
-        scheme.append((bs, lens))
+        scheme.append((bs, _token_slices(fstep, bs, n, step_gap)))
         cur_b -= bs
     return (pipelinelen - 1) * mx + total, scheme
 
@@ -252,7 +285,8 @@ def evaluate_split(latency_model: SingleLayerLatency, split_scheme: Scheme, pipe
 
 
 def search_schedule(latency_model: SingleLayerLatency, total_batch_size, seqlen, pipelinelen,
-                    layers_per_node, gap=1e-5, max_candidates: Optional[int] = None, progress=None):
+                    layers_per_node, gap=1e-5, max_candidates: Optional[int] = None, progress=None,
+                    uniform_batch=True):
     """Scan the slice-latency cap over the distinct grid values (ascending) and keep the
     best schedule; stops when ``cap * K`` alone exceeds the best total found."""
     grid = latency_model.latency_grid
@@ -269,7 +303,7 @@ def search_schedule(latency_model: SingleLayerLatency, total_batch_size, seqlen,
             continue
         last = cap
         latency, scheme = planning(grid, total_batch_size, seqlen, pipelinelen, cap,
-                                   latency_model.step_gap)
+                                   latency_model.step_gap, uniform_batch=uniform_batch)
         if scheme is None:
             continue
         latency += layers_per_node * latency_model.update_time

@@ -41,6 +41,13 @@ struct AttnParams {
   int* err;
 };
 
+// One arrival per warp (after the warp's lanes have finished their part): far cheaper than 32
+// contending shared-memory atomics on the same barrier word.
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) mbar_arrive(bar);
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int count) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }
@@ -84,33 +91,40 @@ __device__ __forceinline__ void mma_kn(uint32_t tmem_d, uint32_t a_base, uint32_
 }
 
 struct AttnShared {
-  uint64_t bars[12];
+  uint64_t bars[20];
   uint32_t tmem_slot;
   int abort_flag;
 };
 
 // ============================================================================ forward
+// Software pipeline: K/V tiles sit in a 4-stage ring (the prefix is streamed from HBM, so
+// loads must be issued several blocks ahead), the S accumulator and the P tile are double
+// buffered, and the
+// MMA thread issues S(j+1) = Q K(j+1)^T before it waits for the softmax of block j, so the
+// tensor core computes the next scores while the 128 softmax threads work on the current ones.
 template <typename T, int D>
-__global__ void __launch_bounds__(kAttnThreads, D == 128 ? 2 : 3)
+__global__ void __launch_bounds__(kAttnThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmKV,
                 const AttnParams p) {
   constexpr int DH = D / 64;
   constexpr int kQSub = 128 * 128, kKSub = 64 * 128;
-  constexpr uint32_t kTmemCols = D == 128 ? 256 : 128;
+  constexpr uint32_t kTmemCols = 256;
+  constexpr int KS = 4;  // K/V ring depth
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* sQ = smem;
-  uint8_t* sK = sQ + DH * kQSub;
-  uint8_t* sV = sK + DH * kKSub;
-  uint8_t* sP = sV + DH * kKSub;
-  AttnShared* sh = reinterpret_cast<AttnShared*>(sP + 128 * 128);
+  uint8_t* sK = sQ + DH * kQSub;          // [KS][DH][kKSub]
+  uint8_t* sV = sK + KS * DH * kKSub;     // [KS][DH][kKSub]
+  uint8_t* sP = sV + KS * DH * kKSub;     // [2][128][128B]
+  AttnShared* sh = reinterpret_cast<AttnShared*>(sP + 2 * 128 * 128);
   uint64_t* bar_q = &sh->bars[0];
-  uint64_t* bar_k = &sh->bars[1];
-  uint64_t* bar_v = &sh->bars[2];
-  uint64_t* bar_s = &sh->bars[3];
-  uint64_t* bar_p = &sh->bars[4];
-  uint64_t* bar_pv = &sh->bars[5];
+  uint64_t* bar_k = &sh->bars[1];      // [KS]
+  uint64_t* bar_v = &sh->bars[5];      // [KS]
+  uint64_t* bar_s = &sh->bars[9];      // [2]
+  uint64_t* bar_sfree = &sh->bars[11]; // [2]
+  uint64_t* bar_p = &sh->bars[13];     // [2]
+  uint64_t* bar_pv = &sh->bars[15];    // [2]
 
   const int warp = threadIdx.x >> 5;
   const WaitCtx wctx{&sh->abort_flag, p.err};
@@ -122,11 +136,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   if (threadIdx.x == 0) {
     mbar_init(bar_q, 1);
-    mbar_init(bar_k, 1);
-    mbar_init(bar_v, 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, 128);
-    mbar_init(bar_pv, 1);
+    for (int i = 0; i < KS; ++i) {
+      mbar_init(&bar_k[i], 1);
+      mbar_init(&bar_v[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bar_s[i], 1);
+      mbar_init(&bar_sfree[i], 4);
+      mbar_init(&bar_p[i], 4);
+      mbar_init(&bar_pv[i], 1);
+    }
     sh->abort_flag = 0;
     fence_barrier_init();
   }
@@ -138,46 +157,53 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sh->tmem_slot;
-  const uint32_t tS = tmem, tO = tmem + 64;
+  const uint32_t tO = tmem + 128;   // S[0] at 0, S[1] at 64, O at 128
 
   if (warp == 4) {
     if (elect_one()) {
       constexpr uint32_t idesc_s = umma_idesc_f16(Elem<T>::fmt, 0, 0, 128, 64);
       constexpr uint32_t idesc_pv = umma_idesc_f16(Elem<T>::fmt, 0, 1, 128, D);
+      auto load_kv = [&](int j) {
+        const int st = j % KS;
+        mbar_expect_tx(&bar_k[st], DH * kKSub);
+        for (int hh = 0; hh < DH; ++hh)
+          tma_load_3d(sK + (st * DH + hh) * kKSub, &tmKV, &bar_k[st], D + hh * 64, bh, j * 64);
+        mbar_expect_tx(&bar_v[st], DH * kKSub);
+        for (int hh = 0; hh < DH; ++hh)
+          tma_load_3d(sV + (st * DH + hh) * kKSub, &tmKV, &bar_v[st], 2 * D + hh * 64, bh, j * 64);
+      };
+      auto issue_s = [&](int j) -> bool {
+        const int ks = j % KS, sb = j & 1;
+        if (!mbar_wait(&bar_k[ks], (j / KS) & 1, wctx, kErrWaitAttn)) return false;
+        if (!mbar_wait(&bar_sfree[sb], ((j >> 1) & 1) ^ 1, wctx, kErrWaitAttn)) return false;
+        tc_fence_after();
+        mma_kk<DH>(tmem + sb * 64, smem_u32(sQ), kQSub, smem_u32(sK + ks * DH * kKSub), kKSub, idesc_s);
+        umma_commit(&bar_s[sb]);
+        return true;
+      };
       mbar_expect_tx(bar_q, DH * kQSub);
       for (int hh = 0; hh < DH; ++hh)
         tma_load_3d(sQ + hh * kQSub, &tmQ, bar_q, hh * 64, bh, p.c + q0);
-      mbar_expect_tx(bar_k, DH * kKSub);
-      for (int hh = 0; hh < DH; ++hh) tma_load_3d(sK + hh * kKSub, &tmKV, bar_k, D + hh * 64, bh, 0);
-      mbar_expect_tx(bar_v, DH * kKSub);
-      for (int hh = 0; hh < DH; ++hh)
-        tma_load_3d(sV + hh * kKSub, &tmKV, bar_v, 2 * D + hh * 64, bh, 0);
+      for (int j = 0; j < KS && j < nkb; ++j) load_kv(j);
       bool ok = mbar_wait(bar_q, 0, wctx, kErrWaitAttn);
+      if (ok) ok = issue_s(0);
       for (int j = 0; j < nkb && ok; ++j) {
-        const uint32_t ph = j & 1;
-        ok = mbar_wait(bar_k, ph, wctx, kErrWaitAttn);
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (j + 1 < nkb) ok = issue_s(j + 1);
+        if (!ok) break;
+        ok = mbar_wait(&bar_p[st], ph, wctx, kErrWaitAttn) &&
+             mbar_wait(&bar_v[j % KS], (j / KS) & 1, wctx, kErrWaitAttn);
         if (!ok) break;
         tc_fence_after();
-        mma_kk<DH>(tS, smem_u32(sQ), kQSub, smem_u32(sK), kKSub, idesc_s);
-        umma_commit(bar_s);
-        ok = mbar_wait(bar_s, ph, wctx, kErrWaitAttn);
-        if (!ok) break;
-        if (j + 1 < nkb) {
-          mbar_expect_tx(bar_k, DH * kKSub);
-          for (int hh = 0; hh < DH; ++hh)
-            tma_load_3d(sK + hh * kKSub, &tmKV, bar_k, D + hh * 64, bh, (j + 1) * 64);
-        }
-        ok = mbar_wait(bar_p, ph, wctx, kErrWaitAttn) && mbar_wait(bar_v, ph, wctx, kErrWaitAttn);
-        if (!ok) break;
-        tc_fence_after();
-        mma_kn(tO, smem_u32(sP), smem_u32(sV), kKSub, idesc_pv, j > 0);
-        umma_commit(bar_pv);
-        ok = mbar_wait(bar_pv, ph, wctx, kErrWaitAttn);
-        if (!ok) break;
-        if (j + 1 < nkb) {
-          mbar_expect_tx(bar_v, DH * kKSub);
-          for (int hh = 0; hh < DH; ++hh)
-            tma_load_3d(sV + hh * kKSub, &tmKV, bar_v, 2 * D + hh * 64, bh, (j + 1) * 64);
+        mma_kn(tO, smem_u32(sP + st * 128 * 128), smem_u32(sV + (j % KS) * DH * kKSub), kKSub, idesc_pv, j > 0);
+        umma_commit(&bar_pv[st]);
+        if (j >= 1 && j - 1 + KS < nkb) {
+          // ring stage (j-1) % KS is reusable once PV(j-1) has finished reading V(j-1); waiting
+          // for the PREVIOUS block keeps this thread off the critical path of the current one
+          ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, wctx, kErrWaitAttn);
+          if (!ok) break;
+          load_kv(j - 1 + KS);
         }
       }
     }
@@ -189,28 +215,39 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int j = 0; j < nkb; ++j) {
-      ok = mbar_wait(bar_s, j & 1, wctx, kErrWaitAttn);
+      const int st = j & 1;
+      ok = mbar_wait(&bar_s[st], (j >> 1) & 1, wctx, kErrWaitAttn);
       if (!ok) break;
       tc_fence_after();
       float s[64];
       {
-        uint32_t raw[32];
+        uint32_t r0[32], r1[32];
         __syncwarp();
-        tmem_ld_32x32(tS + lane_base, raw);
+        tmem_ld_32x32(tmem + st * 64 + lane_base, r0);
+        tmem_ld_32x32(tmem + st * 64 + lane_base + 32, r1);
         tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(raw[i]);
-        tmem_ld_32x32(tS + lane_base + 32, raw);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) s[32 + i] = __uint_as_float(raw[i]);
+        for (int i = 0; i < 32; ++i) {
+          s[i] = __uint_as_float(r0[i]);
+          s[32 + i] = __uint_as_float(r1[i]);
+        }
       }
+      tc_fence_before();
+      warp_arrive(&bar_sfree[st]);
       float mx = -INFINITY;
       const int kbase = j * 64;
+      if (kbase + 63 <= p.c + q0) {   // every key of the block is visible to every row
 #pragma unroll
-      for (int i = 0; i < 64; ++i) {
-        s[i] = (kbase + i <= qpos) ? s[i] * p.scale2 : -INFINITY;
-        mx = fmaxf(mx, s[i]);
+        for (int i = 0; i < 64; ++i) {
+          s[i] *= p.scale2;
+          mx = fmaxf(mx, s[i]);
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          s[i] = (kbase + i <= qpos) ? s[i] * p.scale2 : -INFINITY;
+          mx = fmaxf(mx, s[i]);
+        }
       }
       bool need = false;
       float alpha = 1.0f;
@@ -223,6 +260,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         l *= alpha;
       }
       if (__any_sync(0xffffffffu, need)) {
+        // O may only be touched once PV(j-1) has been accumulated
+        ok = mbar_wait(&bar_pv[(j - 1) & 1], ((j - 1) >> 1) & 1, wctx, kErrWaitAttn);
+        if (!ok) break;
+        tc_fence_after();
 #pragma unroll 1
         for (int ch = 0; ch < D / 32; ++ch) {
           uint32_t raw[32];
@@ -241,12 +282,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         sum += s[i];
       }
       l += sum;
-      store_row64<T>(sP, r, s);
+      store_row64<T>(sP + st * 128 * 128, r, s);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(bar_p);
+      warp_arrive(&bar_p[st]);
     }
-    if (ok) ok = mbar_wait(bar_pv, (nkb - 1) & 1, wctx, kErrWaitAttn);
+    if (ok) ok = mbar_wait(&bar_pv[(nkb - 1) & 1], ((nkb - 1) >> 1) & 1, wctx, kErrWaitAttn);
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.0f / l;
@@ -374,8 +415,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh->bar_s[i], 1);
-      mbar_init(&sh->bar_sfree[i], 128);
-      mbar_init(&sh->bar_p[i], 128);
+      mbar_init(&sh->bar_sfree[i], 4);
+      mbar_init(&sh->bar_p[i], 4);
     }
     mbar_init(&sh->bar_acc[0], 1);
     mbar_init(&sh->bar_acc[1], 1);
@@ -511,7 +552,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
         }
       }
       tc_fence_before();
-      mbar_arrive(&sh->bar_sfree[grp]);
+      warp_arrive(&sh->bar_sfree[grp]);
       // blocks strictly inside the causal region need no per-element mask
       const bool full = MODE == 0 ? (y0 >= x0 + 127 && y0 + 64 <= p.q_end) : (y0 + 63 <= x0);
       if (full) {
@@ -542,7 +583,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
       store_row64<T>(sdS, r, dv);
       fence_proxy_async();
       tc_fence_before();
-      mbar_arrive(&sh->bar_p[grp]);
+      warp_arrive(&sh->bar_p[grp]);
     }
     if (ok && n_iter > 0) ok = mbar_wait(&sh->bar_done, 0, wctx, kErrWaitAttn);
     if (ok && n_iter > 0) {
@@ -614,7 +655,7 @@ template <typename K> static bool set_smem(K kern, int bytes) {
   return cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
 }
 
-template <int D> constexpr int fwd_smem() { return (D / 64) * (128 * 128 + 2 * 64 * 128) + 128 * 128 + 1024 + 256; }
+template <int D> constexpr int fwd_smem() { return (D / 64) * (128 * 128 + 8 * 64 * 128) + 2 * 128 * 128 + 1024 + 512; }
 template <int D> constexpr int bwd_smem() {
   return (D / 64) * (2 * 128 * 128 + kBwdStages * 2 * 64 * 128) + 2 * 128 * 128 + 1024 +
          static_cast<int>(sizeof(BwdShared)) + 64;

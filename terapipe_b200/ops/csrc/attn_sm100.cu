@@ -362,13 +362,16 @@ __global__ void attn_delta_kernel(const T* __restrict__ o, long long ld_o, const
 // 10 warps: two worker groups of 4 warps alternate over the streamed blocks (each owns one
 // S/dP buffer), warp 8 elects the TMA thread, warp 9 the MMA thread.
 constexpr int kBwdThreads = 320;
-constexpr int kBwdStages = 3;
+constexpr int kBwdMaxStages = 4;
+// Ring depth of the streamed tiles: the dQ mode needs no P tile and spends that shared memory
+// on a fourth stage (the streamed K/V come from HBM, so loads must run well ahead).
+template <int MODE> struct BwdStages { static constexpr int value = MODE == 1 ? 4 : 3; };
 
 struct BwdShared {
-  uint64_t bar_x, bar_y[kBwdStages], bar_yfree[kBwdStages], bar_s[2], bar_sfree[2], bar_p[2],
+  uint64_t bar_x, bar_y[kBwdMaxStages], bar_yfree[kBwdMaxStages], bar_s[2], bar_sfree[2], bar_p[2],
       bar_acc[2], bar_done;
-  alignas(16) float lse[kBwdStages][64];    // MODE 0: per streamed block, bulk-copied by the producer
-  alignas(16) float delta[kBwdStages][64];
+  alignas(16) float lse[kBwdMaxStages][64];    // MODE 0: per streamed block, bulk-copied by the producer
+  alignas(16) float delta[kBwdMaxStages][64];
   uint32_t tmem_slot;
   int abort_flag;
 };
@@ -382,6 +385,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   constexpr int DH = D / 64;
   constexpr int kXSub = 128 * 128, kYSub = 64 * 128;
   constexpr int kStageBytes = 2 * DH * kYSub;
+  constexpr int kBwdStages = BwdStages<MODE>::value;
   constexpr uint32_t kTmemCols = 512;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -389,8 +393,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   uint8_t* sX1 = smem;
   uint8_t* sX2 = sX1 + DH * kXSub;
   uint8_t* sY = sX2 + DH * kXSub;                 // [stages][Y1 | Y2][DH][kYSub]
-  uint8_t* sP = sY + kBwdStages * kStageBytes;    // [128][128B]
-  uint8_t* sdS = sP + 128 * 128;
+  uint8_t* sP = sY + kBwdStages * kStageBytes;    // [128][128B], MODE 0 only
+  uint8_t* sdS = MODE == 0 ? sP + 128 * 128 : sP;
   BwdShared* sh = reinterpret_cast<BwdShared*>(sdS + 128 * 128);
 
   const int warp = threadIdx.x >> 5;
@@ -656,8 +660,9 @@ template <typename K> static bool set_smem(K kern, int bytes) {
 }
 
 template <int D> constexpr int fwd_smem() { return (D / 64) * (128 * 128 + 8 * 64 * 128) + 2 * 128 * 128 + 1024 + 512; }
-template <int D> constexpr int bwd_smem() {
-  return (D / 64) * (2 * 128 * 128 + kBwdStages * 2 * 64 * 128) + 2 * 128 * 128 + 1024 +
+template <int D, int MODE> constexpr int bwd_smem() {
+  return (D / 64) * (2 * 128 * 128 + BwdStages<MODE>::value * 2 * 64 * 128) +
+         (MODE == 0 ? 2 : 1) * 128 * 128 + 1024 +
          static_cast<int>(sizeof(BwdShared)) + 64;
 }
 
@@ -697,12 +702,12 @@ static int attn_bwd_launch(const void* qkv, const void* o, const void* do_full, 
   auto k1 = attn_bwd_kernel<T, D, 1>;
   static bool cfg = false;
   if (!cfg) {
-    if (!set_smem(k0, bwd_smem<D>()) || !set_smem(k1, bwd_smem<D>())) return kErrLaunch;
+    if (!set_smem(k0, bwd_smem<D, 0>()) || !set_smem(k1, bwd_smem<D, 1>())) return kErrLaunch;
     cfg = true;
   }
   dim3 grid((p.t + 127) / 128, p.b * p.h);
-  k0<<<grid, kBwdThreads, bwd_smem<D>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
-  k1<<<grid, kBwdThreads, bwd_smem<D>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
+  k0<<<grid, kBwdThreads, bwd_smem<D, 0>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
+  k1<<<grid, kBwdThreads, bwd_smem<D, 1>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 

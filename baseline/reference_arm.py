@@ -57,6 +57,25 @@ def _autograd_grad_returns_list(torch) -> None:
     torch.autograd.grad = grad
 
 
+def _cat_out_across_devices(torch) -> None:
+    """With tensor parallelism the reference builds the full master weight on the CPU and does
+    ``torch.cat(chunks, dim, out=weight)`` with ``weight`` on the GPU (mpu/layers.py:65-79);
+    current torch refuses an ``out`` on another device.  In this process only, perform the
+    concatenation where the chunks live and copy the result into ``out``."""
+    original = torch.cat
+    if getattr(original, "_cross_device_out", False):
+        return
+
+    def cat(tensors, dim=0, *, out=None):
+        if out is not None and len(tensors) and tensors[0].device != out.device:
+            out.copy_(original(list(tensors), dim))
+            return out
+        return original(tensors, dim) if out is None else original(tensors, dim, out=out)
+
+    cat._cross_device_out = True
+    torch.cat = cat
+
+
 def _unavailable(why: str) -> None:
     print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
 
@@ -90,6 +109,7 @@ def run(args, dist_env, timed_steps, ClockSampler, slices_from_args) -> None:
             import test_transformer_terapipe as ref
             ref.np = _NumpyCompat(ref.np)
             _autograd_grad_returns_list(torch)
+            _cat_out_across_devices(torch)
             from transformer_models import MODEL_CONFIGS, TransformerConfig
             assert os.path.dirname(os.path.abspath(ref.__file__)) == REF
             pp = args.pp if args.pp is not None else world // args.tp

@@ -102,14 +102,16 @@ constexpr int kGemmThreads = 192;
 // 256x256 tile: two MMAs per k-step share one B tile, which halves the shared-memory bytes
 // fetched per FLOP (64 B/clk/SM at full rate instead of 96-128); both accumulators then fill
 // the 512 TMEM columns, so the epilogue of a tile does not overlap the next tile's main loop.
-template <int BN, int MT = 1> struct GemmCfg {
-  static constexpr int kStages = MT == 2 ? 3 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8));
+template <int BN, int MT = 1, bool AR = false> struct GemmCfg {
+  // the fused all-reduce variant gives one stage up for a [128][BN] 16-bit staging tile
+  static constexpr int kStages = (MT == 2 ? 3 : (BN == 256 ? 4 : (BN == 128 ? 6 : 8))) - (AR ? 1 : 0);
+  static constexpr int kArStageBytes = AR ? kBM * BN * 2 : 0;
   static constexpr int kABytes = MT * kBM * kBK * 2;
   static constexpr int kBBytes = BN * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = BN == 64 ? 128 : 2 * BN;  // two accumulators, power of two
   static constexpr int kAccBuffers = MT == 2 ? 1 : 2;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kArStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ float gelu_f(float z) {
@@ -125,7 +127,7 @@ template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = fals
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
             const GemmParams p, const ArParams ar) {
-  using Cfg = GemmCfg<BN, MT>;
+  using Cfg = GemmCfg<BN, MT, AR>;
   constexpr int S = Cfg::kStages;
   constexpr int BM = MT * kBM;
   constexpr int NACC = Cfg::kAccBuffers;
@@ -133,7 +135,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint8_t* ar_tile = smem + S * Cfg::kStageBytes;  // AR only: row-major [128][BN] partial tile
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kArStageBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + S;
   uint64_t* tfull = bars + 2 * S;
@@ -268,10 +271,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cm, r);
         tmem_ld_wait();
         if (AR) {
-          // phase A: 16-bit partial of this chunk into the owner's staging tile (peer store)
-          const int owner = tile % ar.tp;
-          T* dst = static_cast<T*>(ar.stage[owner]) +
-                   ((static_cast<long long>(ar.rank) * ar.max_tiles + tile) * kBM + row_in_tile) * BN + c0;
+          // phase A, step 1: 16-bit partial of this chunk into the CTA's staging tile (row-major)
+          T* dst = reinterpret_cast<T*>(ar_tile) + row_in_tile * BN + c0;
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 ov;
@@ -385,8 +386,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       __syncwarp();
       if (lane == 0) mbar_arrive(&tempty[acc]);
       if (AR) {
-        // all 128 epilogue threads have stored their rows: publish the tile to its owner
-        __threadfence_system();
+        // phase A, step 2: the staging tile is one contiguous block in the owner's memory, so
+        // the 128 epilogue threads copy it with fully coalesced 16-byte stores (512 contiguous
+        // bytes per warp instruction over NVLink), then one thread publishes the tile.  The
+        // release store is cumulative over the writes ordered before it by the barrier.
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        {
+          const int owner = tile % ar.tp;
+          uint4* dst = reinterpret_cast<uint4*>(
+              static_cast<T*>(ar.stage[owner]) +
+              (static_cast<long long>(ar.rank) * ar.max_tiles + tile) * kBM * BN);
+          const uint4* src = reinterpret_cast<const uint4*>(ar_tile);
+          const int e = threadIdx.x - 64;
+#pragma unroll
+          for (int k = 0; k < kBM * BN * 2 / 16 / 128; ++k) dst[e + k * 128] = src[e + k * 128];
+        }
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (threadIdx.x == 64)
           st_release_sys(ar.flag_a[tile % ar.tp] + static_cast<long long>(tile) * kMaxTp + ar.rank, ar_epoch);
@@ -459,7 +473,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             *reinterpret_cast<uint4*>(static_cast<T*>(ar.out[dst]) + row * p.ldo + col) = ov;
         }
       }
-      __threadfence_system();
       __syncthreads();
       if (s_ok && threadIdx.x < ar.tp) st_release_sys(ar.flag_b[threadIdx.x] + tile, ar_epoch);
     }
@@ -483,7 +496,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false, int MT = 1>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                        cudaStream_t stream, const ArParams* arp = nullptr) {
-  using Cfg = GemmCfg<BN, MT>;
+  using Cfg = GemmCfg<BN, MT, AR>;
   auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR, MT>;
   ArParams ar;
   if (arp) ar = *arp;

@@ -15,6 +15,8 @@ from torch import nn
 
 from terapipe_b200 import parallel as mpu
 from terapipe_b200.models import MODEL_CONFIGS, TransformerConfig, slice_state_dict  # noqa: F401
+from terapipe_b200.parallel.p2p import (PipelineRecvOperator, PipelineSendOperator,  # noqa: F401
+                                        pipeline_recv, pipeline_send)
 from terapipe_b200.runtime import cli, verify
 from terapipe_b200.runtime.portable import PortablePipeline, TransformerLayers  # noqa: F401
 from terapipe_b200.runtime.runner import NCCLTransformerRunner, init_distributed

@@ -152,6 +152,32 @@ class TransformerConfig:
     def compute_pseudo_loss(pred_y, y):
         return torch.mean((pred_y - y) ** 2)
 
+    # ---- legacy layer factories (single process; transformer_models.py:113-174) --------
+    def _make_layer(self, device):
+        from .layers import TransformerLayer
+        return TransformerLayer(self.embedding_dim, self.ffn_embedding_dim,
+                                self.num_attention_heads, device=device,
+                                activation=self.activation)
+
+    def create_layers_and_inputs(self):
+        layers = [self._make_layer("cpu") for _ in range(self.n_layers)]
+        return layers, torch.randn(self.seq_len, self.batch_size, self.embedding_dim)
+
+    def create_layers_gpu(self, device=None):
+        dev = self._device(device)
+        return [self._make_layer(dev) for _ in range(self.n_layers // self.n_devices)]
+
+    def create_layers_and_inputs_on_gpu(self):
+        if self.n_layers % self.n_devices:
+            raise AssertionError("layers must divide evenly over the devices")
+        per_dev = self.n_layers // self.n_devices
+        cuda = torch.cuda.is_available()
+        devs = [f"cuda:{self.placement_orders[i // per_dev]}" if cuda else "cpu"
+                for i in range(self.n_layers)]
+        layers = [self._make_layer(d) for d in devs]
+        x = torch.randn(self.seq_len, self.batch_size, self.embedding_dim, device=devs[0])
+        return layers, x
+
     def n_params_per_layer(self) -> int:
         h, f = self.embedding_dim, self.ffn_embedding_dim
         return 4 * h + (3 * h * h + 3 * h) + (h * h + h) + (f * h + f) + (h * f + h)

@@ -38,3 +38,43 @@ def recv_backward(buf: torch.Tensor) -> torch.Tensor:
     if nxt is not None:
         dist.recv(buf, nxt)
     return buf
+
+
+class PipelineSendOperator(torch.autograd.Function):
+    """Differentiable send to the next stage: forward sends ``x``, backward receives the
+    gradient of ``x`` from there (the role of terapipe.py:98-124 in the reference)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        send_forward(x.detach())
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, grad):
+        if _init.get_pipeline_next_rank() is None:
+            return grad
+        buf = torch.empty_like(grad)
+        recv_backward(buf)
+        return buf
+
+
+class PipelineRecvOperator(torch.autograd.Function):
+    """Differentiable receive from the previous stage: forward fills ``x`` with the received
+    slice, backward sends the gradient back (terapipe.py:127-151)."""
+
+    @staticmethod
+    def forward(ctx, x):
+        if _init.get_pipeline_prev_rank() is None:
+            return x.view_as(x)
+        buf = torch.empty_like(x)
+        recv_forward(buf)
+        return buf
+
+    @staticmethod
+    def backward(ctx, grad):
+        send_backward(grad)
+        return grad
+
+
+pipeline_send = PipelineSendOperator.apply
+pipeline_recv = PipelineRecvOperator.apply

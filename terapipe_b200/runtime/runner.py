@@ -153,3 +153,8 @@ class NCCLTransformerRunner:
             worst = max(worst, rel)
         assert worst < rtol, f"sliced and unsliced gradients differ: relative error {worst}"
         return worst
+
+
+# The reference splits the runner into a base class (model, schedule, optimizer) and a subclass
+# that adds step/run/verify; here one class does both and the base name is kept as an alias.
+NCCLTransformer = NCCLTransformerRunner

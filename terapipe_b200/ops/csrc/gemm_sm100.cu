@@ -123,6 +123,108 @@ __device__ __forceinline__ float gelu_grad_f(float z) {
   return cdf + z * pdf;
 }
 
+// Fused epilogue of one 32-column chunk of one output row: r holds the fp32 accumulators of
+// columns [n, n + 32) of row `row`.  The caller has checked row < M and n < N.
+template <typename T, bool OUT_F32>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&r)[32],
+                                               long long row, int n) {
+    // Issue every global load of this 32-column chunk before any dependent math or store,
+    // so the chunk pays one memory latency instead of one per 8-column group.
+    bool gok[4];
+    uint4 bv[4], rv[4], av[4];
+    float4 cv[8];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const int ng = n + g * 8;
+      gok[g] = ng + 8 <= p.N;
+      if (!gok[g]) continue;
+      if (p.bias) bv[g] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + ng));
+      if (p.residual)
+        rv[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + ng));
+      if (p.dact)
+        av[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) + row * p.ld_aux + ng));
+      if (OUT_F32 && p.accumulate) {
+        const float4* o = reinterpret_cast<const float4*>(static_cast<const float*>(p.out) + row * p.ldo + ng);
+        cv[2 * g] = __ldcg(o);
+        cv[2 * g + 1] = __ldcg(o + 1);
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {  // groups of 8 columns
+      const int ng = n + g * 8;
+      if (!gok[g]) continue;
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
+      if (p.bias) {
+        const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Elem<T>::unpack2(bw[j]);
+          v[2 * j] += f.x;
+          v[2 * j + 1] += f.y;
+        }
+      }
+      if (p.act == 2) {
+        if (p.aux_out) {
+          uint4 zv;
+          zv.x = Elem<T>::pack2(v[0], v[1]);
+          zv.y = Elem<T>::pack2(v[2], v[3]);
+          zv.z = Elem<T>::pack2(v[4], v[5]);
+          zv.w = Elem<T>::pack2(v[6], v[7]);
+          __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + ng), zv);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j]);
+      } else if (p.act == 1) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
+      }
+      if (p.residual) {
+        const uint32_t rw[4] = {rv[g].x, rv[g].y, rv[g].z, rv[g].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Elem<T>::unpack2(rw[j]);
+          v[2 * j] += f.x;
+          v[2 * j + 1] += f.y;
+        }
+      }
+      if (p.dact) {
+        const uint32_t aw[4] = {av[g].x, av[g].y, av[g].z, av[g].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Elem<T>::unpack2(aw[j]);
+          if (p.dact == 1) {
+            v[2 * j] = f.x > 0.0f ? v[2 * j] : 0.0f;
+            v[2 * j + 1] = f.y > 0.0f ? v[2 * j + 1] : 0.0f;
+          } else {
+            v[2 * j] *= gelu_grad_f(f.x);
+            v[2 * j + 1] *= gelu_grad_f(f.y);
+          }
+        }
+      }
+      if (OUT_F32) {
+        float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + row * p.ldo + ng);
+        float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
+        float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
+        if (p.accumulate) {
+          const float4 c0v = cv[2 * g], c1v = cv[2 * g + 1];
+          o0.x += c0v.x; o0.y += c0v.y; o0.z += c0v.z; o0.w += c0v.w;
+          o1.x += c1v.x; o1.y += c1v.y; o1.z += c1v.z; o1.w += c1v.w;
+        }
+        __stcg(o, o0);
+        __stcg(o + 1, o1);
+      } else {
+        uint4 ov;
+        ov.x = Elem<T>::pack2(v[0], v[1]);
+        ov.y = Elem<T>::pack2(v[2], v[3]);
+        ov.z = Elem<T>::pack2(v[4], v[5]);
+        ov.w = Elem<T>::pack2(v[6], v[7]);
+        __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.ldo + ng), ov);
+      }
+    }
+}
+
 template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -286,101 +388,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         const int n = n0 + c0;
         if (!row_ok || n >= p.N) continue;
-        // Issue every global load of this 32-column chunk before any dependent math or store,
-        // so the chunk pays one memory latency instead of one per 8-column group.
-        bool gok[4];
-        uint4 bv[4], rv[4], av[4];
-        float4 cv[8];
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          const int ng = n + g * 8;
-          gok[g] = ng + 8 <= p.N;
-          if (!gok[g]) continue;
-          if (p.bias) bv[g] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + ng));
-          if (p.residual)
-            rv[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + ng));
-          if (p.dact)
-            av[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) + row * p.ld_aux + ng));
-          if (OUT_F32 && p.accumulate) {
-            const float4* o = reinterpret_cast<const float4*>(static_cast<const float*>(p.out) + row * p.ldo + ng);
-            cv[2 * g] = __ldcg(o);
-            cv[2 * g + 1] = __ldcg(o + 1);
-          }
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {  // groups of 8 columns
-          const int ng = n + g * 8;
-          if (!gok[g]) continue;
-          float v[8];
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
-          if (p.bias) {
-            const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = Elem<T>::unpack2(bw[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
-            }
-          }
-          if (p.act == 2) {
-            if (p.aux_out) {
-              uint4 zv;
-              zv.x = Elem<T>::pack2(v[0], v[1]);
-              zv.y = Elem<T>::pack2(v[2], v[3]);
-              zv.z = Elem<T>::pack2(v[4], v[5]);
-              zv.w = Elem<T>::pack2(v[6], v[7]);
-              __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + ng), zv);
-            }
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j]);
-          } else if (p.act == 1) {
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
-          }
-          if (p.residual) {
-            const uint32_t rw[4] = {rv[g].x, rv[g].y, rv[g].z, rv[g].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = Elem<T>::unpack2(rw[j]);
-              v[2 * j] += f.x;
-              v[2 * j + 1] += f.y;
-            }
-          }
-          if (p.dact) {
-            const uint32_t aw[4] = {av[g].x, av[g].y, av[g].z, av[g].w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const float2 f = Elem<T>::unpack2(aw[j]);
-              if (p.dact == 1) {
-                v[2 * j] = f.x > 0.0f ? v[2 * j] : 0.0f;
-                v[2 * j + 1] = f.y > 0.0f ? v[2 * j + 1] : 0.0f;
-              } else {
-                v[2 * j] *= gelu_grad_f(f.x);
-                v[2 * j + 1] *= gelu_grad_f(f.y);
-              }
-            }
-          }
-          if (OUT_F32) {
-            float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + row * p.ldo + ng);
-            float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
-            float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
-            if (p.accumulate) {
-              const float4 c0v = cv[2 * g], c1v = cv[2 * g + 1];
-              o0.x += c0v.x; o0.y += c0v.y; o0.z += c0v.z; o0.w += c0v.w;
-              o1.x += c1v.x; o1.y += c1v.y; o1.z += c1v.z; o1.w += c1v.w;
-            }
-            __stcg(o, o0);
-            __stcg(o + 1, o1);
-          } else {
-            uint4 ov;
-            ov.x = Elem<T>::pack2(v[0], v[1]);
-            ov.y = Elem<T>::pack2(v[2], v[3]);
-            ov.z = Elem<T>::pack2(v[4], v[5]);
-            ov.w = Elem<T>::pack2(v[6], v[7]);
-            __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.ldo + ng), ov);
-          }
-        }
+        epilogue_chunk<T, OUT_F32>(p, r, row, n);
       }
       tc_fence_before();
       __syncwarp();
@@ -523,6 +531,240 @@ static int dispatch_layout(int a_mn, int b_mn, int out_f32, const CUtensorMap& t
     if (!a_mn && !b_mn && out_f32) return launch_gemm<T, BN, false, false, true>(tmA, tmB, p, s);
     if (a_mn && b_mn && !out_f32) return launch_gemm<T, BN, true, true, false>(tmA, tmB, p, s);
   }
+  return kErrBadArgument;
+}
+
+// ---------------------------------------------------------------------------------------------
+// CTA-pair variant (tcgen05 cta_group::2).  A cluster of two CTAs, one per SM of a TPC, owns a
+// 256 x BN output tile: CTA r of the pair loads rows [128 r, 128 r + 128) of the A tile and
+// rows [BN/2 r, BN/2 r + BN/2) of the B tile into its own shared memory and keeps 128 lanes x
+// BN columns of the fp32 accumulator in its own TMEM; the leader CTA (rank 0) issues one MMA
+// per k16 step for both.  Per SM and k16 step the tensor core then reads 4 KB of A and only
+// BN/2 rows of B (4 KB for BN = 256) while TMA writes the same amount: 64 + 64 B/clk, inside the
+// 128 B/clk a shared memory delivers, where a lone CTA with a 128 x 256 tile needs 96 + 96.
+// Unlike the 256 x 256 single-CTA tile the accumulator is still double buffered (2 x BN columns
+// per CTA), so the epilogue of a tile overlaps the main loop of the next one.
+//
+// Synchronisation across the pair:
+//   full[s]   lives in the leader; both CTAs' TMA loads count their bytes on it;
+//   empty[s]  one per CTA, both signalled by one tcgen05.commit of the leader;
+//   tfull[a]  one per CTA (epilogue warps of each CTA wait on their own), same commit form;
+//   tempty[a] lives in the leader, 8 arrivals: the 4 epilogue warps of each CTA.
+template <int BN> struct PairCfg {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = (BN / 2) * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages = BN == 256 ? 6 : 8;
+  static constexpr int kTmemCols = 2 * BN;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                 const GemmParams p) {
+  using Cfg = PairCfg<BN>;
+  constexpr int S = Cfg::kStages;
+  constexpr int HB = BN / 2;  // B rows held by one CTA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint64_t* full = bars;
+  uint64_t* empty = bars + S;
+  uint64_t* tfull = bars + 2 * S;
+  uint64_t* tempty = bars + 2 * S + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t cta = cluster_ctarank();   // 0 = leader
+  const int pair = blockIdx.x >> 1;
+  const int npairs = gridDim.x >> 1;
+  const WaitCtx wctx{abort_flag, p.err};
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) {
+      mbar_init(&full[i], 1);
+      mbar_init(&empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&tfull[i], 1);
+      mbar_init(&tempty[i], 8);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    prefetch_tmap(&tmA);
+    prefetch_tmap(&tmB);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const int num_kb = (p.K + kBK - 1) / kBK;
+
+  if (warp == 0) {
+    if (elect_one()) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < p.num_tiles && ok; tile += npairs) {
+        const int m0 = (tile % p.num_m_tiles) * (2 * kBM) + static_cast<int>(cta) * kBM;
+        const int n0 = (tile / p.num_m_tiles) * BN + static_cast<int>(cta) * HB;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&empty[stage], phase ^ 1, wctx, kErrWaitProducer);
+          if (!ok) break;
+          uint8_t* sA = smem + stage * Cfg::kStageBytes;
+          uint8_t* sB = sA + Cfg::kABytes;
+          if (cta == 0) mbar_expect_tx(&full[stage], 2 * Cfg::kStageBytes);
+          const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);
+          if (!A_MN) {
+            tma_load_2d_pair(sA, &tmA, bar, kb * kBK, m0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < kBM / 64; ++c)
+              tma_load_2d_pair(sA + c * (kBK * 128), &tmA, bar, m0 + c * 64, kb * kBK);
+          }
+          if (!B_MN) {
+            tma_load_2d_pair(sB, &tmB, bar, kb * kBK, n0);
+          } else {
+#pragma unroll
+            for (int c = 0; c < HB / 64; ++c)
+              tma_load_2d_pair(sB + c * (kBK * 128), &tmB, bar, n0 + c * 64, kb * kBK);
+          }
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (cta == 0 && elect_one()) {
+      constexpr uint32_t idesc = umma_idesc_f16(Elem<T>::fmt, A_MN ? 1 : 0, B_MN ? 1 : 0, 2 * kBM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        ok = mbar_wait(&tempty[acc], acc_phase ^ 1, wctx, kErrWaitTmemEmpty);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          ok = mbar_wait(&full[stage], phase, wctx, kErrWaitMma);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t a_base = smem_u32(smem + stage * Cfg::kStageBytes);
+          const uint32_t b_base = a_base + Cfg::kABytes;
+#pragma unroll
+          for (int k = 0; k < kBK / 16; ++k) {
+            const uint64_t da = A_MN ? umma_desc_sw128(a_base + k * 2048, kBK * 128, 1024)
+                                     : umma_desc_sw128(a_base + k * 32, 16, 1024);
+            const uint64_t db = B_MN ? umma_desc_sw128(b_base + k * 2048, kBK * 128, 1024)
+                                     : umma_desc_sw128(b_base + k * 32, 16, 1024);
+            umma_f16_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit_pair(&empty[stage], 3);
+          if (++stage == S) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit_pair(&tfull[acc], 3);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
+    const int row_in_tile = quarter * 32 + lane;
+    int it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      const int m0 = (tile % p.num_m_tiles) * (2 * kBM) + static_cast<int>(cta) * kBM;
+      const int n0 = (tile / p.num_m_tiles) * BN;
+      ok = mbar_wait(&tfull[acc], acc_phase, wctx, kErrWaitEpilogue);
+      if (!ok) break;
+      tc_fence_after();
+      const long long row = m0 + row_in_tile;
+      const bool row_ok = row < p.M;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        __syncwarp();
+        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c0, r);
+        tmem_ld_wait();
+        const int n = n0 + c0;
+        if (!row_ok || n >= p.N) continue;
+        epilogue_chunk<T, OUT_F32>(p, r, row, n);
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+    }
+  }
+
+  // teardown: nobody leaves (or frees TMEM) while the peer may still read this CTA's shared
+  // memory or signal its barriers.  On an aborted run give in-flight copies time to land first.
+  __syncthreads();
+  if (*abort_flag) {
+    const unsigned long long t0 = globaltimer_ns();
+    while (globaltimer_ns() - t0 < 200000ull) __nanosleep(1000);
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+}
+
+static int max_pairs() {
+  static int cached[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) return num_sms() / 2;
+  if (cached[dev] == 0) cached[dev] = num_sms() / 2;
+  return cached[dev];
+}
+
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
+                            cudaStream_t stream) {
+  using Cfg = PairCfg<BN>;
+  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
+        cudaSuccess)
+      return kErrLaunch;
+    configured = true;
+  }
+  const int pairs = p.num_tiles < max_pairs() ? p.num_tiles : max_pairs();
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(2 * pairs, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? kOk : kErrLaunch;
+}
+
+template <typename T, int BN>
+static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorMap& tmA,
+                                const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
+  if (!a_mn && !b_mn && !out_f32) return launch_gemm_pair<T, BN, false, false, false>(tmA, tmB, p, s);
+  if (!a_mn && b_mn && !out_f32) return launch_gemm_pair<T, BN, false, true, false>(tmA, tmB, p, s);
+  if (a_mn && b_mn && out_f32) return launch_gemm_pair<T, BN, true, true, true>(tmA, tmB, p, s);
   return kErrBadArgument;
 }
 

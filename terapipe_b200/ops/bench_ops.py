@@ -41,34 +41,94 @@ def _timeit(fn, n=20, warm=3, flush=None):
     return total / n * 1e3
 
 
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / (b.float().norm() + 1e-12)).item()
+
+
 def case_gemm(a):
+    """Layer GEMMs of one token slice.  ``--tile`` takes a comma list of tile codes to force
+    (0 = automatic choice, 64/128/256 = one CTA with a 128 x BN tile, 512 = one CTA 256 x 256,
+    1128/1256 = CTA pair with a 256 x 128 / 256 x 256 tile); every forced run is also checked
+    against torch."""
     dt, dev, H, T = a.dtype, "cuda", a.hidden, a.tokens
+    tiles = [int(t) for t in a.tile.split(",")]
     shapes = {"qkv": (T, 3 * H, H), "out": (T, H, H), "fc1": (T, 4 * H, H), "fc2": (T, H, 4 * H)}
     for name, (M, N, K) in shapes.items():
         x = torch.randn(M, K, device=dev, dtype=dt)
         w = torch.randn(N, K, device=dev, dtype=dt) * 0.02
         bias = torch.zeros(N, device=dev, dtype=dt)
         out = torch.empty(M, N, device=dev, dtype=dt)
-        run = lambda: F.gemm(x, w, out, bias=bias)  # noqa: E731
-        if a.once:
-            for _ in range(3):
-                run()
-            continue
-        us = _timeit(run, flush=a.flush_buf)
-        ref = _timeit(lambda: torch.nn.functional.linear(x, w, bias), flush=a.flush_buf)
-        print(f"gemm {name:4s} M{M} N{N} K{K}: {us:7.1f} us {2 * M * N * K / us / 1e6:7.1f} TFLOP/s"
-              f"   (torch/cuBLAS {ref:7.1f} us)")
         dy = torch.randn(M, N, device=dev, dtype=dt)
         dx = torch.empty(M, K, device=dev, dtype=dt)
-        us = _timeit(lambda: F.gemm(dy, w, dx, b_mn=True), flush=a.flush_buf)
-        print(f"  dgrad            : {us:7.1f} us {2 * M * N * K / us / 1e6:7.1f} TFLOP/s")
+        if a.once:
+            for _ in range(3):
+                F.gemm(x, w, out, bias=bias, force_bn=tiles[0])
+            continue
+        ref = _timeit(lambda: torch.nn.functional.linear(x, w, bias), flush=a.flush_buf)
+        y_ref = torch.nn.functional.linear(x, w, bias)
+        dx_ref = dy @ w
+        for tile in tiles:
+            out.fill_(float("nan"))
+            us = _timeit(lambda: F.gemm(x, w, out, bias=bias, force_bn=tile), flush=a.flush_buf)
+            err = _rel(out, y_ref)
+            print(f"gemm {name:4s} M{M} N{N} K{K} tile {tile:4d}: {us:7.1f} us "
+                  f"{2 * M * N * K / us / 1e6:7.1f} TFLOP/s  rel.err {err:.1e}   (torch/cuBLAS {ref:7.1f} us)")
+            dx.fill_(float("nan"))
+            us = _timeit(lambda: F.gemm(dy, w, dx, b_mn=True, force_bn=tile), flush=a.flush_buf)
+            err = _rel(dx, dx_ref)
+            print(f"  dgrad                     tile {tile:4d}: {us:7.1f} us "
+                  f"{2 * M * N * K / us / 1e6:7.1f} TFLOP/s  rel.err {err:.1e}")
+        F.check_device_status()
     if not a.once:
         R = 16 * T
         dy = torch.randn(R, 4 * H, device=dev, dtype=dt)
         x = torch.randn(R, H, device=dev, dtype=dt)
         dw = torch.zeros(4 * H, H, device=dev)
-        us = _timeit(lambda: F.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True), n=5)
-        print(f"wgrad fc1 over {R} rows: {us:7.1f} us {2 * R * 4 * H * H / us / 1e6:7.1f} TFLOP/s")
+        for tile in tiles:
+            us = _timeit(lambda: F.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True, force_bn=tile), n=5)
+            dw.zero_()
+            F.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True, force_bn=tile)
+            err = _rel(dw, dy.float().t() @ x.float())
+            print(f"wgrad fc1 over {R} rows tile {tile:4d}: {us:7.1f} us "
+                  f"{2 * R * 4 * H * H / us / 1e6:7.1f} TFLOP/s  rel.err {err:.1e}")
+        F.check_device_status()
+
+
+def case_gemm_trace(a):
+    """Where the cycles of the CTA-pair GEMM go: per-phase medians over CTAs."""
+    dt, dev, H, T = torch.float16, "cuda", a.hidden, a.tokens
+    shapes = {"qkv": (T, 3 * H, H), "out": (T, H, H), "fc1": (T, 4 * H, H), "fc2": (T, H, 4 * H)}
+    for name, (M, N, K) in shapes.items():
+        x = torch.randn(M, K, device=dev, dtype=dt)
+        w = torch.randn(N, K, device=dev, dtype=dt) * 0.02
+        out = torch.empty(M, N, device=dev, dtype=dt)
+        for bn in (128, 256):
+            for _ in range(3):
+                tr = F.gemm_pair_trace(x, w, out, bn)
+            if a.flush_buf is not None:
+                a.flush_buf.zero_()
+                tr = F.gemm_pair_trace(x, w, out, bn)
+            torch.cuda.synchronize()
+            tr = tr.cpu().double()
+            lead = tr[0::2]
+            t0 = tr[:, 0:1]
+            rel = tr - t0
+            med = lambda v: float(v.median())  # noqa: E731
+            mx = lambda v: float(v.max())  # noqa: E731
+            tiles = lead[:, 8]
+            ideal = (K // 16) * (bn // 2)      # MMA cycles of one tile at the full rate
+            print(f"trace {name} M{M} N{N} K{K} pair tile 256x{bn}: CTAs {tr.shape[0]}, tiles/pair "
+                  f"{int(tiles.min())}-{int(tiles.max())}, MMA cycles per tile at full rate {ideal}")
+            print(f"  set-up done            median {med(rel[:, 1]):8.0f}  max {mx(rel[:, 1]):8.0f}")
+            print(f"  first operands arrived median {med(lead[:, 4] - lead[:, 0]):8.0f}  max {mx(lead[:, 4] - lead[:, 0]):8.0f}")
+            print(f"  last MMA issued        median {med(lead[:, 7] - lead[:, 0]):8.0f}  max {mx(lead[:, 7] - lead[:, 0]):8.0f}")
+            print(f"    of which waiting for operands {med(lead[:, 5]):8.0f} (max {mx(lead[:, 5]):8.0f}), "
+                  f"for a free accumulator {med(lead[:, 6]):8.0f} (max {mx(lead[:, 6]):8.0f})")
+            print(f"  producer waited for ring slots  median {med(tr[:, 2]):8.0f}; last load issued at {med(rel[:, 3]):8.0f}")
+            print(f"  last accumulator ready median {med(rel[:, 10]):8.0f}  max {mx(rel[:, 10]):8.0f}")
+            print(f"  last store issued      median {med(rel[:, 12]):8.0f}  max {mx(rel[:, 12]):8.0f}")
+            print(f"  kernel exit            median {med(rel[:, 13]):8.0f}  max {mx(rel[:, 13]):8.0f}")
+        F.check_device_status()
 
 
 def case_attn(a):
@@ -134,7 +194,7 @@ def case_adam(a):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--case", required=True, choices=["gemm", "attn", "norm", "adam"])
+    ap.add_argument("--case", required=True, choices=["gemm", "gemm-trace", "attn", "norm", "adam"])
     ap.add_argument("--hidden", type=int, default=2048)
     ap.add_argument("--tokens", type=int, default=1024)
     ap.add_argument("--batch", type=int, default=8)
@@ -143,12 +203,13 @@ def main():
     ap.add_argument("--ctx", type=int, default=None)
     ap.add_argument("--params", type=int, default=302_000_000)
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
+    ap.add_argument("--tile", default="0", help="gemm: comma list of tile codes to force")
     ap.add_argument("--once", action="store_true")
     ap.add_argument("--flush", action="store_true")
     a = ap.parse_args()
     a.dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
     a.flush_buf = torch.empty(256 * 1024 * 1024, device="cuda", dtype=torch.uint8) if a.flush else None
-    {"gemm": case_gemm, "attn": case_attn, "norm": case_norm, "adam": case_adam}[a.case](a)
+    {"gemm": case_gemm, "gemm-trace": case_gemm_trace, "attn": case_attn, "norm": case_norm, "adam": case_adam}[a.case](a)
     torch.cuda.synchronize()
     F.check_device_status()
 

@@ -53,6 +53,7 @@ struct GemmParams {
   int dact;        // 0 none, 1 relu' (aux_in = activation output), 2 gelu' (aux_in = pre-activation)
   int accumulate;  // fp32 output only
   int* err;
+  long long* trace;  // optional per-CTA phase stamps (trace builds of the kernel only)
 };
 
 constexpr int kMaxTp = 8;
@@ -559,7 +560,11 @@ template <int BN> struct PairCfg {
   static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+// TRACE = true additionally records, per CTA, SM-clock stamps of the pipeline phases into
+// p.trace[blockIdx.x * kTraceSlots ...] (see the slot list at tp_gemm_trace).
+constexpr int kTraceSlots = 16;
+
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const GemmParams p) {
@@ -580,6 +585,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();   // 0 = leader
+  long long* tr = TRACE ? p.trace + static_cast<long long>(blockIdx.x) * kTraceSlots : nullptr;
+  if (TRACE && threadIdx.x == 0) tr[0] = clock64();
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
   const WaitCtx wctx{abort_flag, p.err};
@@ -609,18 +616,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const int num_kb = (p.K + kBK - 1) / kBK;
+  if (TRACE && threadIdx.x == 0) tr[1] = clock64();
 
   if (warp == 0) {
     if (elect_one()) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      long long stall = 0;
       for (int tile = pair; tile < p.num_tiles && ok; tile += npairs) {
         const int m0 = (tile % p.num_m_tiles) * (2 * kBM) + static_cast<int>(cta) * kBM;
         const int n0 = (tile / p.num_m_tiles) * BN + static_cast<int>(cta) * HB;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long t_w = TRACE ? clock64() : 0;
           ok = mbar_wait(&empty[stage], phase ^ 1, wctx, kErrWaitProducer);
           if (!ok) break;
+          if (TRACE) stall += clock64() - t_w;
           uint8_t* sA = smem + stage * Cfg::kStageBytes;
           uint8_t* sB = sA + Cfg::kABytes;
           if (cta == 0) mbar_expect_tx(&full[stage], 2 * Cfg::kStageBytes);
@@ -642,6 +653,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (++stage == S) { stage = 0; phase ^= 1; }
         }
       }
+      if (TRACE) { tr[2] = stall; tr[3] = clock64(); }
     }
   } else if (warp == 1) {
     if (cta == 0 && elect_one()) {
@@ -650,16 +662,25 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
+      long long stall_full = 0, stall_acc = 0;
       for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
+        const long long t_a = TRACE ? clock64() : 0;
         ok = mbar_wait(&tempty[acc], acc_phase ^ 1, wctx, kErrWaitTmemEmpty);
         if (!ok) break;
+        if (TRACE) stall_acc += clock64() - t_a;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
+          const long long t_w = TRACE ? clock64() : 0;
           ok = mbar_wait(&full[stage], phase, wctx, kErrWaitMma);
           if (!ok) break;
+          if (TRACE) {
+            const long long now = clock64();
+            if (it == 0 && kb == 0) tr[4] = now;
+            else stall_full += now - t_w;
+          }
           tc_fence_after();
           const uint32_t a_base = smem_u32(smem + stage * Cfg::kStageBytes);
           const uint32_t b_base = a_base + Cfg::kABytes;
@@ -677,19 +698,28 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (!ok) break;
         umma_commit_pair(&tfull[acc], 3);
       }
+      if (TRACE) { tr[5] = stall_full; tr[6] = stall_acc; tr[7] = clock64(); tr[8] = it; }
     }
   } else {
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
     int it = 0;
     bool ok = true;
+    long long stall_epi = 0;
     for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       const int m0 = (tile % p.num_m_tiles) * (2 * kBM) + static_cast<int>(cta) * kBM;
       const int n0 = (tile / p.num_m_tiles) * BN;
+      const long long t_e = TRACE ? clock64() : 0;
       ok = mbar_wait(&tfull[acc], acc_phase, wctx, kErrWaitEpilogue);
       if (!ok) break;
+      if (TRACE && threadIdx.x == 64) {
+        const long long now = clock64();
+        stall_epi += now - t_e;
+        if (it == 0) tr[9] = now;
+        tr[10] = now;  // accumulator of the last tile became ready
+      }
       tc_fence_after();
       const long long row = m0 + row_in_tile;
       const bool row_ok = row < p.M;
@@ -707,6 +737,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
     }
+    if (TRACE && threadIdx.x == 64) { tr[11] = stall_epi; tr[12] = clock64(); }
   }
 
   // teardown: nobody leaves (or frees TMEM) while the peer may still read this CTA's shared
@@ -720,6 +751,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   cluster_sync_all();
   tc_fence_after();
   if (warp == 1) tmem_dealloc_pair(tmem_base, Cfg::kTmemCols);
+  if (TRACE && threadIdx.x == 0) tr[13] = clock64();
 }
 
 static int max_pairs() {
@@ -731,11 +763,11 @@ static int max_pairs() {
   return cached[dev];
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
                             cudaStream_t stream) {
   using Cfg = PairCfg<BN>;
-  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32>;
+  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32, TRACE>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -768,23 +800,31 @@ static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorM
   return kErrBadArgument;
 }
 
-// Tile choice.  Encoded as BN, or 512 for the 256x256 tile.  Relative time of one tile =
-// (tile FLOPs) / (fraction of the MMA rate the shared-memory feed sustains for that shape);
-// total = waves x that.  Wave quantisation matters because M is only ~1024 rows per slice.
-static int pick_tile(int M, int N, int forced, bool allow_256x256) {
+// Tile choice.  Codes: 64 / 128 / 256 = one CTA, 128 x BN tile; 512 = one CTA, 256 x 256;
+// 1128 / 1256 = CTA pair, 256 x 128 / 256 x 256.  Relative time of one tile =
+// (tile FLOPs per SM) / (fraction of the MMA rate the shared-memory feed sustains for that
+// shape); total = waves x that.  Wave quantisation matters because M is only ~1024 rows per
+// token slice.
+static bool g_pair_default = true;
+
+static int pick_tile(int M, int N, int forced, bool allow_256x256, bool allow_pair) {
   if (forced == 64 || forced == 128 || forced == 256) return forced;
   if (forced == 512) return allow_256x256 ? 512 : 256;
+  if (forced == 1128 || forced == 1256) return allow_pair ? forced : forced - 1000;
   const int sms = num_sms();
-  const int cand[4] = {512, 256, 128, 64};
-  const int bm[4] = {256, 128, 128, 128};
-  const int bn[4] = {256, 256, 128, 64};
-  const float cost[4] = {4.4f, 3.6f, 2.0f, 1.25f};
+  constexpr int kCand = 6;
+  const int cand[kCand] = {1256, 1128, 512, 256, 128, 64};
+  const int bm[kCand] = {256, 256, 256, 128, 128, 128};
+  const int bn[kCand] = {256, 128, 256, 256, 128, 64};
+  const int slots[kCand] = {sms / 2, sms / 2, sms, sms, sms, sms};
+  const float cost[kCand] = {2.3f, 1.7f, 4.4f, 3.6f, 2.0f, 1.25f};
   int best = 128;
   float best_t = 1e30f;
-  for (int i = 0; i < 4; ++i) {
-    if (i == 0 && !allow_256x256) continue;
+  for (int i = 0; i < kCand; ++i) {
+    if (cand[i] == 512 && !allow_256x256) continue;
+    if (cand[i] > 1000 && !(allow_pair && g_pair_default)) continue;
     const int tiles = ((M + bm[i] - 1) / bm[i]) * ((N + bn[i] - 1) / bn[i]);
-    const float t = static_cast<float>((tiles + sms - 1) / sms) * cost[i];
+    const float t = static_cast<float>((tiles + slots[i] - 1) / slots[i]) * cost[i];
     if (t < best_t) { best_t = t; best = cand[i]; }
   }
   return best;
@@ -808,15 +848,19 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   const bool common_layout = (!a_mn && !out_f32) || (a_mn && b_mn && out_f32);
   // the 256x256 tile pays off only when the main loop is long enough to amortise its
   // non-overlapped epilogue (weight gradients over all tokens; not the K = hidden products)
-  const int tile_code = pick_tile(M, N, force_bn, common_layout && (K >= 4096 || force_bn == 512));
-  const int BN = tile_code == 512 ? 256 : tile_code;
-  const int BM = tile_code == 512 ? 256 : kBM;
+  const int tile_code = pick_tile(M, N, force_bn, common_layout && (K >= 4096 || force_bn == 512),
+                                  common_layout);
+  const bool pair = tile_code > 1000;
+  const int BN = pair ? tile_code - 1000 : (tile_code == 512 ? 256 : tile_code);
+  const int BM = (pair || tile_code == 512) ? 256 : kBM;   // rows of one output tile
+  const int box_m = pair ? kBM : BM;                       // rows of A one CTA loads
+  const int box_n = pair ? BN / 2 : BN;                    // rows of B one CTA loads
   CUtensorMap tmA, tmB;
   bool ok;
-  if (!a_mn) ok = make_tmap_2d(&tmA, A, K, M, lda, kBK, BM, bf16);
+  if (!a_mn) ok = make_tmap_2d(&tmA, A, K, M, lda, kBK, box_m, bf16);
   else ok = make_tmap_2d(&tmA, A, M, K, lda, 64, kBK, bf16);
   if (!ok) return kErrDriver;
-  if (!b_mn) ok = make_tmap_2d(&tmB, B, K, N, ldb, kBK, BN, bf16);
+  if (!b_mn) ok = make_tmap_2d(&tmB, B, K, N, ldb, kBK, box_n, bf16);
   else ok = make_tmap_2d(&tmB, B, N, K, ldb, 64, kBK, bf16);
   if (!ok) return kErrDriver;
   GemmParams p;
@@ -828,12 +872,15 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   p.aux_out = aux_out; p.aux_in = aux_in; p.ld_aux = ld_aux;
   p.alpha = alpha; p.act = act; p.dact = dact; p.accumulate = accumulate;
   p.err = err_flag;
+  p.trace = nullptr;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define TP_DISPATCH(T)                                                                   \
-  (tile_code == 512 ? dispatch_layout<T, 256, 2>(a_mn, b_mn, out_f32, tmA, tmB, p, s)    \
+  (pair ? (BN == 256 ? dispatch_layout_pair<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
+                     : dispatch_layout_pair<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)) \
+   : tile_code == 512 ? dispatch_layout<T, 256, 2>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
    : BN == 256 ? dispatch_layout<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)            \
-             : BN == 128 ? dispatch_layout<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
-                         : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, p, s))
+   : BN == 128 ? dispatch_layout<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)            \
+               : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, p, s))
   return bf16 ? TP_DISPATCH(__nv_bfloat16) : TP_DISPATCH(__half);
 #undef TP_DISPATCH
 }
@@ -870,6 +917,7 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.aux_out = nullptr; p.aux_in = nullptr; p.ld_aux = 0;
   p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
   p.err = err_flag;
+  p.trace = nullptr;
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
   for (int i = 0; i < kMaxTp; ++i) {
@@ -889,6 +937,42 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
 namespace tp {
 __global__ void advance_counter_kernel(int* counter, int inc) { *counter += inc; }
 }  // namespace tp
+
+// Phase trace of the CTA-pair kernel (fp16, out = A[M][K] * B[N][K]^T, no epilogue operands).
+// `trace` receives 16 int64 slots per CTA (2 * min(tiles, SMs / 2) CTAs), SM clock cycles:
+//   0 kernel entry, 1 set-up done (barriers, TMEM, cluster sync), 2 producer: cycles spent
+//   waiting for free ring slots, 3 producer: last load issued, 4 MMA thread: first operands
+//   arrived, 5 MMA thread: cycles waiting for operands (after the first), 6 MMA thread: cycles
+//   waiting for a free accumulator, 7 MMA thread: last MMA issued, 8 tiles done, 9 epilogue:
+//   first accumulator ready, 10 epilogue: last accumulator ready, 11 epilogue: cycles waiting
+//   for accumulators, 12 epilogue: last store issued, 13 kernel exit.  Slots 4-8 are written by
+//   the leader CTA of each pair only.
+extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B, long long ldb,
+                             void* out, long long ldo, int M, int N, int K, long long* trace,
+                             int* err_flag, void* stream) {
+  using namespace tp;
+  if (M <= 0 || N <= 0 || K <= 0 || (bn != 128 && bn != 256) || !trace) return kErrBadArgument;
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 8)) return kErrBadArgument;
+  CUtensorMap tmA, tmB;
+  if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, false)) return kErrDriver;
+  if (!make_tmap_2d(&tmB, B, K, N, ldb, kBK, bn / 2, false)) return kErrDriver;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  p.num_tiles = p.num_m_tiles * ((N + bn - 1) / bn);
+  p.out = out; p.ldo = ldo;
+  p.bias = nullptr; p.residual = nullptr; p.ldr = 0;
+  p.aux_out = nullptr; p.aux_in = nullptr; p.ld_aux = 0;
+  p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
+  p.err = err_flag;
+  p.trace = trace;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  return bn == 256 ? launch_gemm_pair<__half, 256, false, false, false, true>(tmA, tmB, p, s)
+                   : launch_gemm_pair<__half, 128, false, false, false, true>(tmA, tmB, p, s);
+}
+
+// Process-wide switch for the automatic tile choice: 0 keeps every GEMM on single-CTA tiles.
+extern "C" void tp_gemm_set_pair_default(int enabled) { tp::g_pair_default = enabled != 0; }
 
 extern "C" int tp_advance_counter(int* counter, int inc, void* stream) {
   tp::advance_counter_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(counter, inc);

@@ -79,6 +79,27 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn=False, b_m
     return out
 
 
+GEMM_TRACE_SLOTS = 16
+
+
+def gemm_pair_trace(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 256) -> torch.Tensor:
+    """Run the CTA-pair GEMM (fp16, ``out = a @ b.T``) in its tracing build and return the
+    per-CTA phase stamps, an int64 tensor ``[n_ctas, 16]`` of SM clock cycles (slot meanings
+    are listed at ``tp_gemm_trace`` in ``csrc/gemm_sm100.cu``)."""
+    M, N = out.shape
+    K = a.shape[1]
+    assert a.dtype == torch.float16 and b.dtype == torch.float16 and out.dtype == torch.float16
+    tiles = ((M + 255) // 256) * ((N + bn - 1) // bn)
+    sms = torch.cuda.get_device_properties(a.device).multi_processor_count
+    n_ctas = 2 * min(tiles, sms // 2)
+    trace = torch.zeros(n_ctas, GEMM_TRACE_SLOTS, dtype=torch.int64, device=a.device)
+    st = cuda_lib().tp_gemm_trace(int(bn), a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
+                                  out.data_ptr(), out.stride(0), M, N, K, trace.data_ptr(),
+                                  status_word(a.device).data_ptr(), _stream())
+    check(st, "tp_gemm_trace")
+    return trace
+
+
 def layernorm_fwd(x, gamma, beta, y, mean, rstd, eps=1e-5):
     rows, H = x.shape
     st = cuda_lib().tp_layernorm_fwd(_dt(x), x.data_ptr(), gamma.data_ptr(), beta.data_ptr(),

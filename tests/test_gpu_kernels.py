@@ -12,14 +12,14 @@ def _rel(a, b):
 @pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
 @pytest.mark.parametrize("M,N,K", [(1024, 768, 256), (1000, 1024, 512), (128, 256, 64),
                                    (72, 2048, 2048), (1024, 6144, 2048)])
-@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512])
+@pytest.mark.parametrize("bn", [0, 64, 128, 256, 512, 1128, 1256])
 def test_gemm_forward_layout(dtype, M, N, K, bn):
     from terapipe_b200.ops import functional as F
     torch.manual_seed(0)
     a = torch.randn(M, K, device="cuda", dtype=dtype)
     w = torch.randn(N, K, device="cuda", dtype=dtype) * 0.05
     bias = torch.randn(N, device="cuda", dtype=dtype)
-    out = torch.empty(M, N, device="cuda", dtype=dtype)
+    out = torch.full((M, N), float("nan"), device="cuda", dtype=dtype)  # a skipped store must show
     F.gemm(a, w, out, bias=bias, force_bn=bn)
     ref = a.float() @ w.float().t() + bias.float()
     F.check_device_status()
@@ -34,7 +34,8 @@ def test_gemm_dgrad_layout(dtype):
     dy = torch.randn(M, Nout, device="cuda", dtype=dtype)
     w = torch.randn(Nout, Kin, device="cuda", dtype=dtype) * 0.05
     dx = torch.empty(M, Kin, device="cuda", dtype=dtype)
-    for bn in (64, 128, 256, 512):
+    for bn in (64, 128, 256, 512, 1128, 1256):
+        dx.fill_(float("nan"))
         F.gemm(dy, w, dx, b_mn=True, force_bn=bn)
         assert _rel(dx, dy.float() @ w.float()) < 1e-2
     F.check_device_status()
@@ -47,7 +48,7 @@ def test_gemm_wgrad_layout_accumulates(dtype):
     T, Nout, Kin = 328, 384, 512
     dy = torch.randn(T, Nout, device="cuda", dtype=dtype)
     x = torch.randn(T, Kin, device="cuda", dtype=dtype)
-    for bn in (64, 128, 256, 512):
+    for bn in (64, 128, 256, 512, 1128, 1256):
         dw = torch.ones(Nout, Kin, device="cuda", dtype=torch.float32)
         F.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True, force_bn=bn)
         F.gemm(dy, x, dw, a_mn=True, b_mn=True, accumulate=True, force_bn=bn)

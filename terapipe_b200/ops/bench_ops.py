@@ -25,6 +25,7 @@ def _timeit(fn, n=20, warm=3, flush=None):
     total = 0.0
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if flush is None:
+        torch.cuda._sleep(3_000_000)  # lets the host run ahead so launch overhead is not timed
         e0.record()
         for _ in range(n):
             fn()
@@ -103,6 +104,21 @@ def case_gemm_trace(a):
         w = torch.randn(N, K, device=dev, dtype=dt) * 0.02
         out = torch.empty(M, N, device=dev, dtype=dt)
         for bn in (128, 256):
+            for variant in (7, 8):  # TMEM load latency probes
+                for _ in range(3):
+                    tr = F.gemm_pair_trace(x, w, out, bn, variant)
+                torch.cuda.synchronize()
+                tr = tr.cpu().double()
+                print(f"  [TMEM probe {variant}] {name} 256x{bn}: first chunk load+wait {float(tr[:, 16].median()):6.0f} "
+                      f"read {float(tr[:, 17].median()):6.0f}; later chunks (sum) load+wait {float(tr[:, 18].median()):6.0f} "
+                      f"read {float(tr[:, 19].median()):6.0f}; tiles {float(tr[0::2, 8].median()):.0f}")
+            for variant in (1, 2, 3, 4, 5, 6):  # truncated epilogues, see GemmParams::variant
+                for _ in range(3):
+                    tr = F.gemm_pair_trace(x, w, out, bn, variant)
+                torch.cuda.synchronize()
+                tr = tr.cpu().double()
+                print(f"  [epilogue variant {variant}] {name} 256x{bn}: accumulator ready -> epilogue done "
+                      f"{float((tr[:, 12] - tr[:, 10]).median()):7.0f}, -> exit {float((tr[:, 13] - tr[:, 10]).median()):7.0f}")
             for _ in range(3):
                 tr = F.gemm_pair_trace(x, w, out, bn)
             if a.flush_buf is not None:
@@ -128,6 +144,11 @@ def case_gemm_trace(a):
             print(f"  last accumulator ready median {med(rel[:, 10]):8.0f}  max {mx(rel[:, 10]):8.0f}")
             print(f"  last store issued      median {med(rel[:, 12]):8.0f}  max {mx(rel[:, 12]):8.0f}")
             print(f"  kernel exit            median {med(rel[:, 13]):8.0f}  max {mx(rel[:, 13]):8.0f}")
+            print(f"  epilogue warp: TMEM loads {med(tr[:, 14]):8.0f}, math + stores {med(tr[:, 15]):8.0f}, "
+                  f"waiting for accumulators {med(tr[:, 11]):8.0f}")
+            print(f"    math + stores = buffer wait {med(tr[:, 16]):8.0f} + math/smem {med(tr[:, 17]):8.0f} "
+                  f"+ fence/issue {med(tr[:, 18]):8.0f}; first TMEM load of each tile: wait returns after "
+                  f"{med(tr[:, 19]):6.0f}, register readable after {med(tr[:, 20]):6.0f} more")
         F.check_device_status()
 
 

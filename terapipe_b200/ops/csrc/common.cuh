@@ -71,6 +71,31 @@ inline bool make_tmap_2d(CUtensorMap* out, const void* base, uint64_t inner, uin
   return make_tmap_16b(out, base, 2, dims, strides, box, bf16);
 }
 
+// Tensor map of a row-major [rows][cols] output matrix for the epilogue's staged stores: boxes
+// of 32 x 32 elements whose shared-memory rows are 64 bytes (16-bit elements, 64-byte swizzle)
+// or 128 bytes (fp32, 128-byte swizzle).
+inline bool make_tmap_out(CUtensorMap* out, const void* base, uint64_t cols, uint64_t rows,
+                          uint64_t ld_elems, bool f32, bool bf16) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {cols, rows};
+  const cuuint64_t strides[1] = {ld_elems * (f32 ? 4u : 2u)};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                     : (bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16);
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  f32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    fprintf(stderr, "terapipe_b200: cuTensorMapEncodeTiled (output map) failed (%d) dims=%llu,%llu ld=%llu base=%p\n",
+            (int)r, (unsigned long long)cols, (unsigned long long)rows, (unsigned long long)ld_elems, base);
+    return false;
+  }
+  return true;
+}
+
 inline int num_sms() {
   static int n = 0;
   if (!n) {

@@ -54,6 +54,8 @@ struct GemmParams {
   int accumulate;  // fp32 output only
   int* err;
   long long* trace;  // optional per-CTA phase stamps (trace builds of the kernel only)
+  int variant;       // trace builds only: 1 = epilogue reads TMEM and drops the values, 2 = stops
+                     // after the shared-memory writes, 3 = stops after the proxy fence
 };
 
 constexpr int kMaxTp = 8;
@@ -98,6 +100,10 @@ __device__ __forceinline__ bool wait_flag(const int* p, int target, const WaitCt
 constexpr int kBM = 128;
 constexpr int kBK = 64;
 constexpr int kGemmThreads = 192;
+// staged output path of the epilogue (see EpiStage): two 32-row x 128-byte buffers per warp
+constexpr int kEpiBufBytes = 4096;                      // 32 rows x 128 B
+constexpr int kEpiBytesPerWarp = 2 * kEpiBufBytes;
+constexpr int kEpiBytes = 4 * kEpiBytesPerWarp;         // four epilogue warps
 
 // MT = number of 128-row sub-tiles of the CTA tile (1 or 2).  MT = 2 with BN = 256 gives a
 // 256x256 tile: two MMAs per k-step share one B tile, which halves the shared-memory bytes
@@ -112,124 +118,289 @@ template <int BN, int MT = 1, bool AR = false> struct GemmCfg {
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = BN == 64 ? 128 : 2 * BN;  // two accumulators, power of two
   static constexpr int kAccBuffers = MT == 2 ? 1 : 2;
-  static constexpr int kSmemBytes = kStages * kStageBytes + kArStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiStageBytes = AR ? 0 : kEpiBytes;  // staged output path (not used with AR)
+  static constexpr int kSmemBytes =
+      kStages * kStageBytes + kArStageBytes + kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
-__device__ __forceinline__ float gelu_f(float z) {
+// Not inlined on purpose: the epilogue applies them to 32 values per chunk, and 32 inlined erff
+// expansions (twice, with the derivative) make the chunk code so large that the instruction
+// fetch of the rarely executed epilogue dominates its run time.
+__device__ __noinline__ float gelu_f(float z) {
   return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));
 }
-__device__ __forceinline__ float gelu_grad_f(float z) {
+__device__ __noinline__ float gelu_grad_f(float z) {
   const float cdf = 0.5f * (1.0f + erff(z * 0.70710678118654752f));
   const float pdf = 0.3989422804014327f * __expf(-0.5f * z * z);
   return cdf + z * pdf;
 }
 
-// Fused epilogue of one 32-column chunk of one output row: r holds the fp32 accumulators of
-// columns [n, n + 32) of row `row`.  The caller has checked row < M and n < N.
-template <typename T, bool OUT_F32>
-__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const uint32_t (&r)[32],
-                                               long long row, int n) {
-    // Issue every global load of this 32-column chunk before any dependent math or store,
-    // so the chunk pays one memory latency instead of one per 8-column group.
-    bool gok[4];
-    uint4 bv[4], rv[4], av[4];
-    float4 cv[8];
+// Staged output path of one epilogue warp.  A TMEM load hands every thread one ROW of the tile,
+// so direct global stores would touch 32 different lines per instruction.  Instead the warp
+// writes its 32 x 32 chunk into a private, swizzled shared-memory buffer (conflict free) and one
+// lane stores the chunk with a single TMA tile store - or a TMA add-reduction when an fp32 output
+// accumulates, which also removes the read of the old value.  The warp's buffers rotate, and
+// the TMEM load of the next chunk is in flight while a chunk is processed.
+
+// SM clock read that memory operations cannot be moved across (trace builds only)
+__device__ __forceinline__ long long clock_ordered() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+  return t;
+}
+
+struct EpiStage {
+  uint8_t* buf;  // this warp's two buffers (1024-byte aligned)
+  int issued;    // chunks stored so far by this warp
+};
+
+__device__ __forceinline__ void epi_drain(int lane) {
+  if (lane == 0) bulk_wait<0>();
+  __syncwarp();
+}
+
+// Fused epilogue of one 32-column chunk: r holds the fp32 accumulators of columns [n, n + 32)
+// of row `row` (thread = row).  row0 is the first row of the warp's 32-row group (row0 < M);
+// the caller has checked n < N.  t_next: TMEM address of the next chunk to load into r, or 0.  Rows >= M and columns >= N are clipped by the tile store.
+template <typename T, bool OUT_F32, bool TRACE = false>
+__device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtensorMap* tmO,
+                                               EpiStage& es, uint32_t (&r)[32], long long row,
+                                               bool row_ok, int n, int row0, int lane,
+                                               uint32_t t_next, long long* cyc = nullptr) {
+  const long long t_0 = TRACE ? clock_ordered() : 0;
+  if (TRACE && p.variant == 1) {
+    asm volatile("" ::"r"(r[0]), "r"(r[31]) : "memory");
+    return;
+  }
+  // Issue every global load of this 32-column chunk before any dependent math or store,
+  // so the chunk pays one memory latency instead of one per 8-column group.
+  bool gok[4];
+  uint4 bv[4], rv[4], av[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) gok[g] = n + g * 8 + 8 <= p.N;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  if (p.bias) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      bv[g] = gok[g] ? __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + n + g * 8)) : zero4;
+  }
+  if (p.residual) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      rv[g] = (gok[g] && row_ok)
+                  ? __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + n + g * 8))
+                  : zero4;
+  }
+  if (p.dact) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      av[g] = (gok[g] && row_ok)
+                  ? __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) + row * p.ld_aux + n + g * 8))
+                  : zero4;
+  }
+  // A tile store reads its source a good thousand cycles after it was issued, so the buffers
+  // rotate: four 2 KB buffers for 16-bit output, two 4 KB buffers for fp32.  The buffer about
+  // to be overwritten was the source of the store issued kBufs chunks ago.
+  constexpr int kBufs = OUT_F32 ? 2 : 4;
+  uint8_t* sb = es.buf + (es.issued % kBufs) * (kEpiBytesPerWarp / kBufs);
+  if (es.issued >= kBufs) {
+    if (lane == 0) bulk_wait_read<kBufs - 1>();
+    __syncwarp();
+  }
+  const long long t_1 = TRACE ? clock_ordered() : 0;
+  // trace builds: a zero the compiler cannot see through ties the math below to the clock read
+  const uint32_t tz = TRACE ? static_cast<uint32_t>(static_cast<unsigned long long>(t_1) >> 63) : 0u;
+  // One pass per fused operation over all 32 values: one uniform branch per pass and 32
+  // independent instructions inside it (a lone warp per scheduler needs the ILP).
+  float v[32];
+#pragma unroll
+  for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j] + tz);
+  // r is free again: start the TMEM load of the next chunk (t_next = 0: there is none).  The
+  // empty asm keeps the copies above ahead of the load that overwrites their source.
+  asm volatile("" ::: "memory");
+  if (t_next) tmem_ld_32x32(t_next, r);
+  if (TRACE && p.variant >= 4 && p.variant <= 6) {
+    // attribution probes: 4 = conversions only, 5 = shared-memory stores only, 6 = both through
+    // explicit st.shared instructions
+    if (p.variant == 4) {
+      uint32_t x = 0;
+#pragma unroll
+      for (int j = 0; j < 16; ++j) x ^= Elem<T>::pack2(v[2 * j], v[2 * j + 1]);
+      if (x == 0x12345u) cyc[4] += 1;
+    } else if (p.variant == 5) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g)
+        *reinterpret_cast<float4*>(sb + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) =
+            make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
+    } else {
+      const uint32_t base = smem_u32(sb) + lane * 64;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint32_t a0 = Elem<T>::pack2(v[g * 8 + 0], v[g * 8 + 1]), a1 = Elem<T>::pack2(v[g * 8 + 2], v[g * 8 + 3]);
+        const uint32_t a2 = Elem<T>::pack2(v[g * 8 + 4], v[g * 8 + 5]), a3 = Elem<T>::pack2(v[g * 8 + 6], v[g * 8 + 7]);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + ((g ^ ((lane >> 1) & 3)) << 4)),
+                     "r"(a0), "r"(a1), "r"(a2), "r"(a3)
+                     : "memory");
+      }
+    }
+    return;
+  }
+  if (p.alpha != 1.0f) {
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+  }
+  if (p.bias) {
 #pragma unroll
     for (int g = 0; g < 4; ++g) {
-      const int ng = n + g * 8;
-      gok[g] = ng + 8 <= p.N;
-      if (!gok[g]) continue;
-      if (p.bias) bv[g] = __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + ng));
-      if (p.residual)
-        rv[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row * p.ldr + ng));
-      if (p.dact)
-        av[g] = __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) + row * p.ld_aux + ng));
-      if (OUT_F32 && p.accumulate) {
-        const float4* o = reinterpret_cast<const float4*>(static_cast<const float*>(p.out) + row * p.ldo + ng);
-        cv[2 * g] = __ldcg(o);
-        cv[2 * g + 1] = __ldcg(o + 1);
+      const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Elem<T>::unpack2(bw[j]);
+        v[g * 8 + 2 * j] += f.x;
+        v[g * 8 + 2 * j + 1] += f.y;
+      }
+    }
+  }
+  if (p.act == 2) {
+    if (p.aux_out && row_ok) {
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        if (!gok[g]) continue;
+        uint4 zv;
+        zv.x = Elem<T>::pack2(v[g * 8 + 0], v[g * 8 + 1]);
+        zv.y = Elem<T>::pack2(v[g * 8 + 2], v[g * 8 + 3]);
+        zv.z = Elem<T>::pack2(v[g * 8 + 4], v[g * 8 + 5]);
+        zv.w = Elem<T>::pack2(v[g * 8 + 6], v[g * 8 + 7]);
+        __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + n + g * 8), zv);
       }
     }
 #pragma unroll
-    for (int g = 0; g < 4; ++g) {  // groups of 8 columns
-      const int ng = n + g * 8;
-      if (!gok[g]) continue;
-      float v[8];
+    for (int j = 0; j < 32; ++j) v[j] = gelu_f(v[j]);
+  } else if (p.act == 1) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = __uint_as_float(r[g * 8 + j]) * p.alpha;
-      if (p.bias) {
-        const uint32_t bw[4] = {bv[g].x, bv[g].y, bv[g].z, bv[g].w};
+    for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.0f);
+  }
+  if (p.residual) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = Elem<T>::unpack2(bw[j]);
-          v[2 * j] += f.x;
-          v[2 * j + 1] += f.y;
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t rw[4] = {rv[g].x, rv[g].y, rv[g].z, rv[g].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Elem<T>::unpack2(rw[j]);
+        v[g * 8 + 2 * j] += f.x;
+        v[g * 8 + 2 * j + 1] += f.y;
+      }
+    }
+  }
+  if (p.dact) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t aw[4] = {av[g].x, av[g].y, av[g].z, av[g].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = Elem<T>::unpack2(aw[j]);
+        if (p.dact == 1) {
+          v[g * 8 + 2 * j] = f.x > 0.0f ? v[g * 8 + 2 * j] : 0.0f;
+          v[g * 8 + 2 * j + 1] = f.y > 0.0f ? v[g * 8 + 2 * j + 1] : 0.0f;
+        } else {
+          v[g * 8 + 2 * j] *= gelu_grad_f(f.x);
+          v[g * 8 + 2 * j + 1] *= gelu_grad_f(f.y);
         }
       }
-      if (p.act == 2) {
-        if (p.aux_out) {
-          uint4 zv;
-          zv.x = Elem<T>::pack2(v[0], v[1]);
-          zv.y = Elem<T>::pack2(v[2], v[3]);
-          zv.z = Elem<T>::pack2(v[4], v[5]);
-          zv.w = Elem<T>::pack2(v[6], v[7]);
-          __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.aux_out) + row * p.ld_aux + ng), zv);
-        }
+    }
+  }
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = gelu_f(v[j]);
-      } else if (p.act == 1) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = fmaxf(v[j], 0.0f);
-      }
-      if (p.residual) {
-        const uint32_t rw[4] = {rv[g].x, rv[g].y, rv[g].z, rv[g].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = Elem<T>::unpack2(rw[j]);
-          v[2 * j] += f.x;
-          v[2 * j + 1] += f.y;
-        }
-      }
-      if (p.dact) {
-        const uint32_t aw[4] = {av[g].x, av[g].y, av[g].z, av[g].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 f = Elem<T>::unpack2(aw[j]);
-          if (p.dact == 1) {
-            v[2 * j] = f.x > 0.0f ? v[2 * j] : 0.0f;
-            v[2 * j + 1] = f.y > 0.0f ? v[2 * j + 1] : 0.0f;
-          } else {
-            v[2 * j] *= gelu_grad_f(f.x);
-            v[2 * j + 1] *= gelu_grad_f(f.y);
-          }
-        }
-      }
-      if (OUT_F32) {
-        float4* o = reinterpret_cast<float4*>(static_cast<float*>(p.out) + row * p.ldo + ng);
-        float4 o0 = make_float4(v[0], v[1], v[2], v[3]);
-        float4 o1 = make_float4(v[4], v[5], v[6], v[7]);
-        if (p.accumulate) {
-          const float4 c0v = cv[2 * g], c1v = cv[2 * g + 1];
-          o0.x += c0v.x; o0.y += c0v.y; o0.z += c0v.z; o0.w += c0v.w;
-          o1.x += c1v.x; o1.y += c1v.y; o1.z += c1v.z; o1.w += c1v.w;
-        }
-        __stcg(o, o0);
-        __stcg(o + 1, o1);
+  for (int g = 0; g < 4; ++g) {
+    if (OUT_F32) {
+      // 128-byte rows, 128-byte swizzle: 16-byte chunk index ^= row & 7
+      uint8_t* rowp = sb + lane * 128;
+      *reinterpret_cast<float4*>(rowp + (((2 * g) ^ (lane & 7)) << 4)) =
+          make_float4(v[g * 8 + 0], v[g * 8 + 1], v[g * 8 + 2], v[g * 8 + 3]);
+      *reinterpret_cast<float4*>(rowp + (((2 * g + 1) ^ (lane & 7)) << 4)) =
+          make_float4(v[g * 8 + 4], v[g * 8 + 5], v[g * 8 + 6], v[g * 8 + 7]);
+    } else {
+      // 64-byte rows, 64-byte swizzle: 16-byte chunk index ^= (row >> 1) & 3
+      uint4 ov;
+      ov.x = Elem<T>::pack2(v[g * 8 + 0], v[g * 8 + 1]);
+      ov.y = Elem<T>::pack2(v[g * 8 + 2], v[g * 8 + 3]);
+      ov.z = Elem<T>::pack2(v[g * 8 + 4], v[g * 8 + 5]);
+      ov.w = Elem<T>::pack2(v[g * 8 + 6], v[g * 8 + 7]);
+      *reinterpret_cast<uint4*>(sb + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = ov;
+    }
+  }
+  const long long t_2 = TRACE ? clock_ordered() : 0;
+  if (TRACE && p.variant == 2) return;
+  fence_proxy_async();
+  __syncwarp();
+  if (TRACE && p.variant == 3) return;
+  if (lane == 0) {
+    if (OUT_F32 && p.accumulate) tma_reduce_add_2d(tmO, sb, n, row0);
+    else tma_store_2d(tmO, sb, n, row0);
+    bulk_commit();
+  }
+  ++es.issued;
+  if (TRACE) {
+    cyc[0] += t_1 - t_0;        // loads issued, staging buffer free
+    cyc[1] += t_2 - t_1;        // math and shared-memory writes
+    cyc[2] += clock_ordered() - t_2;  // proxy fence, tile store issued
+  }
+}
+
+// Epilogue of one warp's 32 rows over `nc` 32-column chunks of an accumulator at TMEM address
+// `t_acc` (lane quarter already applied); the warp takes chunks c_first, c_first + c_step, ...
+// The chunk code exists once (it is large); the TMEM
+// load of chunk c + 1 is issued from inside it as soon as chunk c's values have been copied out
+// of the load registers.
+template <typename T, bool OUT_F32, bool TRACE = false>
+__device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtensorMap* tmO,
+                                              EpiStage& es, uint32_t t_acc, int nc, int row0, int n0,
+                                              int lane, int c_first = 0, int c_step = 1,
+                                              long long* cyc = nullptr) {
+  const long long row = row0 + lane;
+  const bool row_ok = row < p.M;
+  uint32_t r[32];
+  __syncwarp();
+  if (TRACE && p.variant >= 7) {
+    // latency probe: load one chunk (7: one 32-column load, 8: two 16-column loads), wait, read
+    // every register; cycles of load + wait and of the reads, first chunk and later chunks apart
+#pragma unroll 1
+    for (int c = c_first; c < nc; c += c_step) {
+      const long long t0 = clock_ordered();
+      if (p.variant == 7) {
+        tmem_ld_32x32(t_acc + c * 32, r);
       } else {
-        uint4 ov;
-        ov.x = Elem<T>::pack2(v[0], v[1]);
-        ov.y = Elem<T>::pack2(v[2], v[3]);
-        ov.z = Elem<T>::pack2(v[4], v[5]);
-        ov.w = Elem<T>::pack2(v[6], v[7]);
-        __stcg(reinterpret_cast<uint4*>(static_cast<T*>(p.out) + row * p.ldo + ng), ov);
+        uint32_t lo[16], hi[16];
+        tmem_ld_32x16(t_acc + c * 32, lo);
+        tmem_ld_32x16(t_acc + c * 32 + 16, hi);
+#pragma unroll
+        for (int j = 0; j < 16; ++j) { r[j] = lo[j]; r[j + 16] = hi[j]; }
       }
+      tmem_ld_wait();
+      const long long t1 = clock_ordered();
+      uint32_t x = 0, y;
+#pragma unroll
+      for (int j = 0; j < 32; ++j) x ^= r[j];
+      asm volatile("mov.b32 %0, %1;" : "=r"(y) : "r"(x) : "memory");
+      const long long t2 = clock_ordered();
+      cyc[c == c_first ? 0 : 2] += t1 - t0;
+      cyc[c == c_first ? 1 : 3] += t2 - t1 + (y == 0x12345u ? 1 : 0);
     }
+    return;
+  }
+  if (c_first >= nc) return;
+  tmem_ld_32x32(t_acc + c_first * 32, r);
+#pragma unroll 1
+  for (int c = c_first; c < nc; c += c_step) {
+    tmem_ld_wait();
+    epilogue_chunk<T, OUT_F32, TRACE>(p, tmO, es, r, row, row_ok, n0 + c * 32, row0, lane,
+                                      c + c_step < nc ? t_acc + (c + c_step) * 32 : 0u, cyc);
+  }
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false, int MT = 1>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-            const GemmParams p, const ArParams ar) {
+            const __grid_constant__ CUtensorMap tmO, const GemmParams p, const ArParams ar) {
   using Cfg = GemmCfg<BN, MT, AR>;
   constexpr int S = Cfg::kStages;
   constexpr int BM = MT * kBM;
@@ -239,7 +410,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* ar_tile = smem + S * Cfg::kStageBytes;  // AR only: row-major [128][BN] partial tile
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes + Cfg::kArStageBytes);
+  uint8_t* epi_smem = smem + S * Cfg::kStageBytes + Cfg::kArStageBytes;  // non-AR: output staging
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::kEpiStageBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + S;
   uint64_t* tfull = bars + 2 * S;
@@ -264,6 +436,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    if (!AR) prefetch_tmap(&tmO);
   }
   if (warp == 1) {
     tmem_alloc(tmem_slot, Cfg::kTmemCols);
@@ -354,6 +527,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   } else {
     const int quarter = warp & 3;  // TMEM lane quarter this warp may access
     const int row_in_tile = quarter * 32 + lane;
+    EpiStage es{epi_smem + quarter * kEpiBytesPerWarp, 0};
     int it = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < p.num_tiles && ok; tile += gridDim.x, ++it) {
@@ -364,16 +538,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
       ok = mbar_wait(&tfull[acc], acc_phase, wctx, kErrWaitEpilogue);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+      if (AR) {
 #pragma unroll 1
-      for (int cm = 0; cm < MT * BN; cm += 32) {
-        const int mt = cm / BN, c0 = cm % BN;
-        const long long row = m0 + mt * kBM + row_in_tile;
-        const bool row_ok = row < p.M;
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + cm, r);
-        tmem_ld_wait();
-        if (AR) {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(t_acc + c0, r);
+          tmem_ld_wait();
           // phase A, step 1: 16-bit partial of this chunk into the CTA's staging tile (row-major)
           T* dst = reinterpret_cast<T*>(ar_tile) + row_in_tile * BN + c0;
 #pragma unroll
@@ -385,11 +557,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             ov.w = Elem<T>::pack2(__uint_as_float(r[g * 8 + 6]) * p.alpha, __uint_as_float(r[g * 8 + 7]) * p.alpha);
             *reinterpret_cast<uint4*>(dst + g * 8) = ov;
           }
-          continue;
         }
-        const int n = n0 + c0;
-        if (!row_ok || n >= p.N) continue;
-        epilogue_chunk<T, OUT_F32>(p, r, row, n);
+      } else {
+        // columns of this tile inside the matrix, in 32-column chunks (warp-uniform)
+        const int nc = (min(BN, p.N - n0) + 31) / 32;
+#pragma unroll 1
+        for (int mt = 0; mt < MT; ++mt) {
+          const int row0 = m0 + mt * kBM + quarter * 32;
+          if (row0 >= p.M) continue;  // warp-uniform: nothing to store
+          epilogue_rows<T, OUT_F32>(p, &tmO, es, t_acc + mt * BN, nc, row0, n0, lane);
+        }
       }
       tc_fence_before();
       __syncwarp();
@@ -415,6 +592,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           st_release_sys(ar.flag_a[tile % ar.tp] + static_cast<long long>(tile) * kMaxTp + ar.rank, ar_epoch);
       }
     }
+    if (!AR) epi_drain(lane);  // the staging buffers must outlive the stores that read them
   }
 
   if (AR) {
@@ -503,8 +681,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool AR = false, int MT = 1>
-static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                       cudaStream_t stream, const ArParams* arp = nullptr) {
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO,
+                       const GemmParams& p, cudaStream_t stream, const ArParams* arp = nullptr) {
   using Cfg = GemmCfg<BN, MT, AR>;
   auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR, MT>;
   ArParams ar;
@@ -518,19 +696,20 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const Gem
     configured = true;
   }
   int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, p, ar);
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, tmO, p, ar);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
 template <typename T, int BN, int MT = 1>
 static int dispatch_layout(int a_mn, int b_mn, int out_f32, const CUtensorMap& tmA,
-                           const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
-  if (!a_mn && !b_mn && !out_f32) return launch_gemm<T, BN, false, false, false, false, MT>(tmA, tmB, p, s);
-  if (!a_mn && b_mn && !out_f32) return launch_gemm<T, BN, false, true, false, false, MT>(tmA, tmB, p, s);
-  if (a_mn && b_mn && out_f32) return launch_gemm<T, BN, true, true, true, false, MT>(tmA, tmB, p, s);
+                           const CUtensorMap& tmB, const CUtensorMap& tmO, const GemmParams& p,
+                           cudaStream_t s) {
+  if (!a_mn && !b_mn && !out_f32) return launch_gemm<T, BN, false, false, false, false, MT>(tmA, tmB, tmO, p, s);
+  if (!a_mn && b_mn && !out_f32) return launch_gemm<T, BN, false, true, false, false, MT>(tmA, tmB, tmO, p, s);
+  if (a_mn && b_mn && out_f32) return launch_gemm<T, BN, true, true, true, false, MT>(tmA, tmB, tmO, p, s);
   if (MT == 1) {  // rarely used layouts: only the 128-row tile is instantiated
-    if (!a_mn && !b_mn && out_f32) return launch_gemm<T, BN, false, false, true>(tmA, tmB, p, s);
-    if (a_mn && b_mn && !out_f32) return launch_gemm<T, BN, true, true, false>(tmA, tmB, p, s);
+    if (!a_mn && !b_mn && out_f32) return launch_gemm<T, BN, false, false, true>(tmA, tmB, tmO, p, s);
+    if (a_mn && b_mn && !out_f32) return launch_gemm<T, BN, true, true, false>(tmA, tmB, tmO, p, s);
   }
   return kErrBadArgument;
 }
@@ -550,31 +729,40 @@ static int dispatch_layout(int a_mn, int b_mn, int out_f32, const CUtensorMap& t
 //   full[s]   lives in the leader; both CTAs' TMA loads count their bytes on it;
 //   empty[s]  one per CTA, both signalled by one tcgen05.commit of the leader;
 //   tfull[a]  one per CTA (epilogue warps of each CTA wait on their own), same commit form;
-//   tempty[a] lives in the leader, 8 arrivals: the 4 epilogue warps of each CTA.
+//   tempty[a] lives in the leader, 16 arrivals: the 8 epilogue warps of each CTA.
+// Ten warps: 0 = TMA producer, 1 = MMA issuer, 2..9 = epilogue.  A lone warp per scheduler
+// runs the long straight-line epilogue code at only one instruction per 4-5 cycles (it is bound
+// by instruction fetch, not by TMEM or shared memory), so two warps share each TMEM lane quarter
+// and take alternate 32-column chunks; that halves the exposed epilogue of a CTA's last tile.
+constexpr int kPairThreads = 320;
+constexpr int kPairEpiWarps = 8;
+
 template <int BN> struct PairCfg {
   static constexpr int kABytes = kBM * kBK * 2;
   static constexpr int kBBytes = (BN / 2) * kBK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kStages = BN == 256 ? 6 : 8;
+  static constexpr int kStages = BN == 256 ? 5 : 6;
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+  static constexpr int kEpiStageBytes = kPairEpiWarps * kEpiBytesPerWarp;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kEpiStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 // TRACE = true additionally records, per CTA, SM-clock stamps of the pipeline phases into
 // p.trace[blockIdx.x * kTraceSlots ...] (see the slot list at tp_gemm_trace).
-constexpr int kTraceSlots = 16;
+constexpr int kTraceSlots = 24;
 
 template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
   using Cfg = PairCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int HB = BN / 2;  // B rows held by one CTA
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + S * Cfg::kStageBytes);
+  uint8_t* epi_smem = smem + S * Cfg::kStageBytes;  // output staging of the epilogue warps
+  uint64_t* bars = reinterpret_cast<uint64_t*>(epi_smem + Cfg::kEpiStageBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + S;
   uint64_t* tfull = bars + 2 * S;
@@ -598,23 +786,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&tfull[i], 1);
-      mbar_init(&tempty[i], 8);
+      mbar_init(&tempty[i], 2 * kPairEpiWarps);
     }
     *abort_flag = 0;
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
+    prefetch_tmap(&tmO);
   }
-  __syncthreads();
-  if (warp == 1) {
-    tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
-    tmem_relinquish_pair();
-  }
-  tc_fence_before();
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
+  // The producer warp starts loading at once; the other five warps meet again after the TMEM
+  // allocation (named barrier 1, 288 threads).
+  uint32_t tmem_base = 0;
+  if (warp >= 1) {
+    if (warp == 1) {
+      tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
+      tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 1, 288;" ::: "memory");
+    tc_fence_after();
+    tmem_base = *tmem_slot;
+  }
   const int num_kb = (p.K + kBK - 1) / kBK;
   if (TRACE && threadIdx.x == 0) tr[1] = clock64();
 
@@ -701,11 +895,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (TRACE) { tr[5] = stall_full; tr[6] = stall_acc; tr[7] = clock64(); tr[8] = it; }
     }
   } else {
-    const int quarter = warp & 3;  // TMEM lane quarter this warp may access
-    const int row_in_tile = quarter * 32 + lane;
+    const int quarter = warp & 3;      // TMEM lane quarter this warp may access
+    const int half = (warp - 2) >> 2;  // which of the two warps of that quarter
+    EpiStage es{epi_smem + (warp - 2) * kEpiBytesPerWarp, 0};
     int it = 0;
     bool ok = true;
-    long long stall_epi = 0;
+    long long stall_epi = 0, cyc_ld = 0, cyc_rest = 0;
+    long long cyc3[5] = {0, 0, 0, 0, 0};
     for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -721,23 +917,22 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         tr[10] = now;  // accumulator of the last tile became ready
       }
       tc_fence_after();
-      const long long row = m0 + row_in_tile;
-      const bool row_ok = row < p.M;
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        __syncwarp();
-        tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN + c0, r);
-        tmem_ld_wait();
-        const int n = n0 + c0;
-        if (!row_ok || n >= p.N) continue;
-        epilogue_chunk<T, OUT_F32>(p, r, row, n);
+      const int row0 = m0 + quarter * 32;
+      if (row0 < p.M) {
+        const int nc = (min(BN, p.N - n0) + 31) / 32;
+        const long long t_l = TRACE ? clock64() : 0;
+        epilogue_rows<T, OUT_F32, TRACE>(
+            p, &tmO, es, tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN, nc, row0,
+            n0, lane, half, 2, cyc3);
+        if (TRACE) cyc_rest += clock64() - t_l;
       }
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
     }
-    if (TRACE && threadIdx.x == 64) { tr[11] = stall_epi; tr[12] = clock64(); }
+    if (TRACE && threadIdx.x == 64) { tr[11] = stall_epi; tr[12] = clock64(); tr[14] = cyc_ld; tr[15] = cyc_rest;
+      tr[16] = cyc3[0]; tr[17] = cyc3[1]; tr[18] = cyc3[2]; tr[19] = cyc3[3]; tr[20] = cyc3[4]; }
+    epi_drain(lane);  // the staging buffers must outlive the stores that read them
   }
 
   // teardown: nobody leaves (or frees TMEM) while the peer may still read this CTA's shared
@@ -764,8 +959,8 @@ static int max_pairs() {
 }
 
 template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false>
-static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const GemmParams& p,
-                            cudaStream_t stream) {
+static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO,
+                            const GemmParams& p, cudaStream_t stream) {
   using Cfg = PairCfg<BN>;
   auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32, TRACE>;
   static bool configured = false;
@@ -778,7 +973,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   const int pairs = p.num_tiles < max_pairs() ? p.num_tiles : max_pairs();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.blockDim = dim3(kPairThreads, 1, 1);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -788,15 +983,16 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, p) == cudaSuccess ? kOk : kErrLaunch;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p) == cudaSuccess ? kOk : kErrLaunch;
 }
 
 template <typename T, int BN>
 static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorMap& tmA,
-                                const CUtensorMap& tmB, const GemmParams& p, cudaStream_t s) {
-  if (!a_mn && !b_mn && !out_f32) return launch_gemm_pair<T, BN, false, false, false>(tmA, tmB, p, s);
-  if (!a_mn && b_mn && !out_f32) return launch_gemm_pair<T, BN, false, true, false>(tmA, tmB, p, s);
-  if (a_mn && b_mn && out_f32) return launch_gemm_pair<T, BN, true, true, true>(tmA, tmB, p, s);
+                                const CUtensorMap& tmB, const CUtensorMap& tmO, const GemmParams& p,
+                                cudaStream_t s) {
+  if (!a_mn && !b_mn && !out_f32) return launch_gemm_pair<T, BN, false, false, false>(tmA, tmB, tmO, p, s);
+  if (!a_mn && b_mn && !out_f32) return launch_gemm_pair<T, BN, false, true, false>(tmA, tmB, tmO, p, s);
+  if (a_mn && b_mn && out_f32) return launch_gemm_pair<T, BN, true, true, true>(tmA, tmB, tmO, p, s);
   return kErrBadArgument;
 }
 
@@ -807,25 +1003,35 @@ static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorM
 // token slice.
 static bool g_pair_default = true;
 
-static int pick_tile(int M, int N, int forced, bool allow_256x256, bool allow_pair) {
+// Measured model of one launch, in kilo-cycles: waves x (main loop of one tile, proportional to
+// K, + epilogue where it does not overlap the next tile) + exposed epilogue of the last tile.
+// `loop` is per 2048 of K: the CTA-pair tiles run at 80-98 % of the MMA rate, the one-CTA tiles
+// at 50-67 % (L2 -> shared-memory feed of one SM).
+struct TileCand {
+  int code, bm, bn;
+  bool pair;
+  float loop, epi_each, tail;
+};
+static const TileCand kTileCands[6] = {
+    {1256, 256, 256, true, 16.7f, 0.0f, 8.5f}, {1128, 256, 128, true, 10.0f, 0.0f, 5.5f},
+    {512, 256, 256, false, 36.0f, 18.0f, 0.0f}, {256, 128, 256, false, 24.7f, 0.0f, 10.0f},
+    {128, 128, 128, false, 16.4f, 0.0f, 5.4f}, {64, 128, 64, false, 9.5f, 0.0f, 3.0f}};
+
+static int pick_tile(int M, int N, int K, int forced, bool allow_256x256, bool allow_pair) {
   if (forced == 64 || forced == 128 || forced == 256) return forced;
   if (forced == 512) return allow_256x256 ? 512 : 256;
   if (forced == 1128 || forced == 1256) return allow_pair ? forced : forced - 1000;
   const int sms = num_sms();
-  constexpr int kCand = 6;
-  const int cand[kCand] = {1256, 1128, 512, 256, 128, 64};
-  const int bm[kCand] = {256, 256, 256, 128, 128, 128};
-  const int bn[kCand] = {256, 128, 256, 256, 128, 64};
-  const int slots[kCand] = {sms / 2, sms / 2, sms, sms, sms, sms};
-  const float cost[kCand] = {2.3f, 1.7f, 4.4f, 3.6f, 2.0f, 1.25f};
   int best = 128;
   float best_t = 1e30f;
-  for (int i = 0; i < kCand; ++i) {
-    if (cand[i] == 512 && !allow_256x256) continue;
-    if (cand[i] > 1000 && !(allow_pair && g_pair_default)) continue;
-    const int tiles = ((M + bm[i] - 1) / bm[i]) * ((N + bn[i] - 1) / bn[i]);
-    const float t = static_cast<float>((tiles + slots[i] - 1) / slots[i]) * cost[i];
-    if (t < best_t) { best_t = t; best = cand[i]; }
+  for (const TileCand& c : kTileCands) {
+    if (c.code == 512 && !allow_256x256) continue;
+    if (c.pair && !(allow_pair && g_pair_default)) continue;
+    const int tiles = ((M + c.bm - 1) / c.bm) * ((N + c.bn - 1) / c.bn);
+    const int slots = c.pair ? sms / 2 : sms;
+    const float waves = static_cast<float>((tiles + slots - 1) / slots);
+    const float t = waves * (c.loop * static_cast<float>(K) / 2048.0f + c.epi_each) + c.tail;
+    if (t < best_t) { best_t = t; best = c.code; }
   }
   return best;
 }
@@ -846,10 +1052,9 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   if (accumulate && !out_f32) return kErrBadArgument;
   const bool bf16 = dtype == 1;
   const bool common_layout = (!a_mn && !out_f32) || (a_mn && b_mn && out_f32);
-  // the 256x256 tile pays off only when the main loop is long enough to amortise its
-  // non-overlapped epilogue (weight gradients over all tokens; not the K = hidden products)
-  const int tile_code = pick_tile(M, N, force_bn, common_layout && (K >= 4096 || force_bn == 512),
-                                  common_layout);
+  // only the three layouts of a Linear layer's forward / dgrad / wgrad products have the
+  // 256-row tiles instantiated
+  const int tile_code = pick_tile(M, N, K, force_bn, common_layout, common_layout);
   const bool pair = tile_code > 1000;
   const int BN = pair ? tile_code - 1000 : (tile_code == 512 ? 256 : tile_code);
   const int BM = (pair || tile_code == 512) ? 256 : kBM;   // rows of one output tile
@@ -863,6 +1068,8 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   if (!b_mn) ok = make_tmap_2d(&tmB, B, K, N, ldb, kBK, box_n, bf16);
   else ok = make_tmap_2d(&tmB, B, N, K, ldb, 64, kBK, bf16);
   if (!ok) return kErrDriver;
+  CUtensorMap tmO;
+  if (!make_tmap_out(&tmO, out, N, M, ldo, out_f32 != 0, bf16)) return kErrDriver;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.num_m_tiles = (M + BM - 1) / BM;
@@ -873,14 +1080,15 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   p.alpha = alpha; p.act = act; p.dact = dact; p.accumulate = accumulate;
   p.err = err_flag;
   p.trace = nullptr;
+  p.variant = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define TP_DISPATCH(T)                                                                   \
-  (pair ? (BN == 256 ? dispatch_layout_pair<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
-                     : dispatch_layout_pair<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)) \
-   : tile_code == 512 ? dispatch_layout<T, 256, 2>(a_mn, b_mn, out_f32, tmA, tmB, p, s)  \
-   : BN == 256 ? dispatch_layout<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, p, s)            \
-   : BN == 128 ? dispatch_layout<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, p, s)            \
-               : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, p, s))
+  (pair ? (BN == 256 ? dispatch_layout_pair<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s)  \
+                     : dispatch_layout_pair<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s)) \
+   : tile_code == 512 ? dispatch_layout<T, 256, 2>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s)  \
+   : BN == 256 ? dispatch_layout<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s)            \
+   : BN == 128 ? dispatch_layout<T, 128>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s)            \
+               : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s))
   return bf16 ? TP_DISPATCH(__nv_bfloat16) : TP_DISPATCH(__half);
 #undef TP_DISPATCH
 }
@@ -918,6 +1126,7 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
   p.err = err_flag;
   p.trace = nullptr;
+  p.variant = 0;
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
   for (int i = 0; i < kMaxTp; ++i) {
@@ -927,11 +1136,12 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
     ar.out[i] = i < tp ? out_ptrs[i] : nullptr;
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const CUtensorMap& tmO = tmA;  // the fused all-reduce epilogue stores through peer pointers
   if (bf16)
-    return b_mn ? launch_gemm<__nv_bfloat16, BN, false, true, false, true>(tmA, tmB, p, s, &ar)
-                : launch_gemm<__nv_bfloat16, BN, false, false, false, true>(tmA, tmB, p, s, &ar);
-  return b_mn ? launch_gemm<__half, BN, false, true, false, true>(tmA, tmB, p, s, &ar)
-              : launch_gemm<__half, BN, false, false, false, true>(tmA, tmB, p, s, &ar);
+    return b_mn ? launch_gemm<__nv_bfloat16, BN, false, true, false, true>(tmA, tmB, tmO, p, s, &ar)
+                : launch_gemm<__nv_bfloat16, BN, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
+  return b_mn ? launch_gemm<__half, BN, false, true, false, true>(tmA, tmB, tmO, p, s, &ar)
+              : launch_gemm<__half, BN, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
 }
 
 namespace tp {
@@ -939,23 +1149,28 @@ __global__ void advance_counter_kernel(int* counter, int inc) { *counter += inc;
 }  // namespace tp
 
 // Phase trace of the CTA-pair kernel (fp16, out = A[M][K] * B[N][K]^T, no epilogue operands).
-// `trace` receives 16 int64 slots per CTA (2 * min(tiles, SMs / 2) CTAs), SM clock cycles:
+// `trace` receives 24 int64 slots per CTA (2 * min(tiles, SMs / 2) CTAs), SM clock cycles:
 //   0 kernel entry, 1 set-up done (barriers, TMEM, cluster sync), 2 producer: cycles spent
 //   waiting for free ring slots, 3 producer: last load issued, 4 MMA thread: first operands
 //   arrived, 5 MMA thread: cycles waiting for operands (after the first), 6 MMA thread: cycles
 //   waiting for a free accumulator, 7 MMA thread: last MMA issued, 8 tiles done, 9 epilogue:
 //   first accumulator ready, 10 epilogue: last accumulator ready, 11 epilogue: cycles waiting
-//   for accumulators, 12 epilogue: last store issued, 13 kernel exit.  Slots 4-8 are written by
+//   for accumulators, 12 epilogue: last store issued, 13 kernel exit, 14 epilogue: cycles in TMEM
+//   loads, 15 epilogue: cycles in the math and stores of the chunks, split into 16 waiting for a
+//   free staging buffer, 17 math and shared-memory writes, 18 proxy fence and store issue; first
+//   chunk of every tile: 19 TMEM load issue until its wait returns, 20 until a loaded register reads.  Slots 4-8 are written by
 //   the leader CTA of each pair only.
 extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B, long long ldb,
                              void* out, long long ldo, int M, int N, int K, long long* trace,
-                             int* err_flag, void* stream) {
+                             int variant, int* err_flag, void* stream) {
   using namespace tp;
   if (M <= 0 || N <= 0 || K <= 0 || (bn != 128 && bn != 256) || !trace) return kErrBadArgument;
   if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 8)) return kErrBadArgument;
   CUtensorMap tmA, tmB;
   if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, false)) return kErrDriver;
   if (!make_tmap_2d(&tmB, B, K, N, ldb, kBK, bn / 2, false)) return kErrDriver;
+  CUtensorMap tmO;
+  if (!make_tmap_out(&tmO, out, N, M, ldo, false, false)) return kErrDriver;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.num_m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
@@ -966,9 +1181,10 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
   p.err = err_flag;
   p.trace = trace;
+  p.variant = variant;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  return bn == 256 ? launch_gemm_pair<__half, 256, false, false, false, true>(tmA, tmB, p, s)
-                   : launch_gemm_pair<__half, 128, false, false, false, true>(tmA, tmB, p, s);
+  return bn == 256 ? launch_gemm_pair<__half, 256, false, false, false, true>(tmA, tmB, tmO, p, s)
+                   : launch_gemm_pair<__half, 128, false, false, false, true>(tmA, tmB, tmO, p, s);
 }
 
 // Process-wide switch for the automatic tile choice: 0 keeps every GEMM on single-CTA tiles.

@@ -206,3 +206,61 @@ extern "C" int tp_dp_reduce_adam(int dtype, int dp, int rank, int epoch, const i
   else dp_reduce_adam_kernel<__half><<<grid, 256, 0, s>>>(p);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
+
+// ---------------------------------------------------------------------------------------------
+// Link probe: how fast can SM-issued stores fill a (peer-mapped) buffer?  Used to choose the
+// store pattern of the fused compute + collective kernels.
+//   mode 0: every thread stores 16 bytes, a warp covers 512 contiguous bytes per instruction
+//   mode 1: as 0, and each CTA runs a system-scope fence after every 32 KB (what publishing a
+//           tile costs)
+//   mode 2: one thread per CTA issues 16 KB bulk copies shared -> global (cp.async.bulk)
+namespace tp {
+
+__global__ void __launch_bounds__(256, 1)
+link_probe_kernel(uint4* dst, long long n_vec, int mode) {
+  extern __shared__ __align__(128) uint8_t probe_smem[];
+  const long long per_cta = n_vec / gridDim.x;
+  uint4* d = dst + static_cast<long long>(blockIdx.x) * per_cta;
+  if (mode <= 1) {
+    const uint4 v = make_uint4(threadIdx.x, blockIdx.x, 1u, 2u);
+    long long it = 0;
+    for (long long i = threadIdx.x; i < per_cta; i += blockDim.x, ++it) {
+      d[i] = v;
+      if (mode == 1 && (it & 7) == 7) {
+        __syncthreads();
+        if (threadIdx.x == 0) __threadfence_system();
+      }
+    }
+  } else {
+    constexpr int kChunk = 16384;
+    for (int i = threadIdx.x; i < kChunk / 16; i += blockDim.x)
+      reinterpret_cast<uint4*>(probe_smem)[i] = make_uint4(i, blockIdx.x, 1u, 2u);
+    fence_proxy_async();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const long long n_chunks = per_cta * 16 / kChunk;
+      for (long long c = 0; c < n_chunks; ++c) {
+        asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(
+                         reinterpret_cast<uint64_t>(reinterpret_cast<uint8_t*>(d) + c * kChunk)),
+                     "r"(smem_u32(probe_smem)), "r"(kChunk)
+                     : "memory");
+        bulk_commit();
+        bulk_wait_read<8>();  // bounded number of copies in flight
+      }
+      bulk_wait<0>();
+    }
+  }
+}
+
+}  // namespace tp
+
+// Fills `bytes` (a multiple of 148 * 16 KB is best) at `dst` with the chosen store pattern.
+extern "C" int tp_link_probe(void* dst, long long bytes, int mode, void* stream) {
+  using namespace tp;
+  if (!dst || bytes <= 0 || mode < 0 || mode > 2) return kErrBadArgument;
+  const int grid = num_sms();
+  const long long n_vec = bytes / 16 / grid * grid;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  link_probe_kernel<<<grid, 256, 16384, s>>>(static_cast<uint4*>(dst), n_vec, mode);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}

@@ -65,7 +65,11 @@ struct ArParams {
   int epoch;                     // call index within the step; the kernel adds *epoch_base
   const int* epoch_base;         // device counter advanced once per step (graph-replay safe)
   int max_tiles;                 // capacity of the staging / flag arrays, in tiles
-  void* stage[kMaxTp];           // per rank: [tp sources][max_tiles][128][BN] 16-bit partials
+  int exchange;                  // CTA-pair kernel: every rank receives every partial tile and
+                                 // reduces it itself (one NVLink hop instead of two)
+  long long* dbg;                // optional: 8 globaltimer stamps per CTA (see tp_gemm_ar_set_debug)
+  void* stage[kMaxTp];           // per rank: [2 halves][tp sources][max_tiles][128][BN] 16-bit partials
+                                 // (the second half is used by exchange mode only)
   int* flag_a[kMaxTp];           // per rank: [max_tiles][kMaxTp] partial-arrived flags
   int* flag_b[kMaxTp];           // per rank: [max_tiles] result-arrived flags
   void* out[kMaxTp];             // per rank: the output matrix (same offset in every pool)
@@ -687,7 +691,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR, MT>;
   ArParams ar;
   if (arp) ar = *arp;
-  else ar.tp = 0;
+  else { ar.tp = 0; ar.exchange = 0; ar.dbg = nullptr; }
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -751,10 +755,112 @@ template <int BN> struct PairCfg {
 // p.trace[blockIdx.x * kTraceSlots ...] (see the slot list at tp_gemm_trace).
 constexpr int kTraceSlots = 24;
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false>
+// Phase B of the fused all-reduce for one 128 x BN tile this rank owns (staging layout of the
+// CTA-pair kernel: 16 blocks [column chunk][lane quarter] of [32 rows][32 columns]): sum the
+// partials of all ranks, add bias and residual, store the result into every rank's output.
+// Called by `nthreads` threads with tid in [0, nthreads) after the tile's flags were observed.
+// local_only: exchange mode, the other ranks reduce the tile themselves.
+template <typename T, int BN>
+__device__ __forceinline__ void ar_reduce_tile(const GemmParams& p, const ArParams& ar, int tile,
+                                               int num_m128, int tid, int nthreads, bool local_only,
+                                               long long stage_half) {
+  const int m0 = (tile % num_m128) * kBM;
+  const int n0 = (tile / num_m128) * BN;
+  const T* stage = static_cast<const T*>(ar.stage[ar.rank]) + stage_half;
+  // Four 16-byte vectors per thread and round: all loads of a round are issued before any of
+  // them is used, so a tile costs two or three memory round trips instead of one per vector.
+  constexpr int kBatch = 4;
+  constexpr int kVecs = kBM * BN / 8;
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+  for (int base = 0; base < kVecs; base += nthreads * kBatch) {
+    uint4 part[kBatch][kMaxTp > 4 ? 4 : kMaxTp];  // up to 4 sources per pass (see below)
+    uint4 bias4[kBatch], res4[kBatch];
+    float acc[kBatch][8];
+    bool ok[kBatch];
+    long long row[kBatch];
+    int col[kBatch], off[kBatch];
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      const int v = base + tid + k * nthreads;
+      const int rr = v / (BN / 8), c8 = v % (BN / 8);  // row in tile, 8-column group
+      row[k] = m0 + rr;
+      col[k] = n0 + c8 * 8;
+      ok[k] = v < kVecs && row[k] < p.M && col[k] + 8 <= p.N;
+      off[k] = ((c8 >> 2) * 4 + (rr >> 5)) * 1024 + (rr & 31) * 32 + (c8 & 3) * 8;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[k][j] = 0.0f;
+    }
+    for (int s0 = 0; s0 < ar.tp; s0 += 4) {  // sources in passes of four
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          part[k][q] = (ok[k] && s0 + q < ar.tp)
+                           ? __ldcg(reinterpret_cast<const uint4*>(
+                                 stage + (static_cast<long long>(s0 + q) * ar.max_tiles + tile) * (kBM * BN) + off[k]))
+                           : zero4;
+      if (s0 == 0) {
+#pragma unroll
+        for (int k = 0; k < kBatch; ++k) {
+          bias4[k] = (ok[k] && p.bias)
+                         ? __ldg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.bias) + col[k]))
+                         : zero4;
+          res4[k] = (ok[k] && p.residual)
+                        ? __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.residual) + row[k] * p.ldr + col[k]))
+                        : zero4;
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < kBatch; ++k)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const uint32_t w[4] = {part[k][q].x, part[k][q].y, part[k][q].z, part[k][q].w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = Elem<T>::unpack2(w[j]);
+            acc[k][2 * j] += f.x;
+            acc[k][2 * j + 1] += f.y;
+          }
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < kBatch; ++k) {
+      if (!ok[k]) continue;
+      const uint32_t bw[4] = {bias4[k].x, bias4[k].y, bias4[k].z, bias4[k].w};
+      const uint32_t rw[4] = {res4[k].x, res4[k].y, res4[k].z, res4[k].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fb = Elem<T>::unpack2(bw[j]);
+        const float2 fr = Elem<T>::unpack2(rw[j]);
+        acc[k][2 * j] += fb.x + fr.x;
+        acc[k][2 * j + 1] += fb.y + fr.y;
+      }
+      uint4 ov;
+      ov.x = Elem<T>::pack2(acc[k][0], acc[k][1]);
+      ov.y = Elem<T>::pack2(acc[k][2], acc[k][3]);
+      ov.z = Elem<T>::pack2(acc[k][4], acc[k][5]);
+      ov.w = Elem<T>::pack2(acc[k][6], acc[k][7]);
+      if (local_only) {
+        __stcg(reinterpret_cast<uint4*>(static_cast<T*>(ar.out[ar.rank]) + row[k] * p.ldo + col[k]), ov);
+      } else {
+        for (int dst = 0; dst < ar.tp; ++dst)
+          *reinterpret_cast<uint4*>(static_cast<T*>(ar.out[dst]) + row[k] * p.ldo + col[k]) = ov;
+      }
+    }
+  }
+}
+
+// AR = true fuses the tensor-parallel all-reduce exactly as gemm_kernel does (phases A-C of the
+// file comment), with 128 x 128 all-reduce tiles: each CTA of a pair owns the flags and staging
+// of its own 128 rows, so no flag needs a barrier across the pair.  In the owner's staging
+// buffer a tile is stored as 16 blocks [column chunk c][lane quarter q] of [32 rows][32 columns];
+// an epilogue warp produces exactly one such 2 KB block per chunk and copies it with fully
+// coalesced 16-byte peer stores.
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false, bool AR = false>
 __global__ void __launch_bounds__(kPairThreads, 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                 const __grid_constant__ CUtensorMap tmO, const GemmParams p) {
+                 const __grid_constant__ CUtensorMap tmO, const GemmParams p, const ArParams ar) {
+  static_assert(!AR || (BN == 128 && !OUT_F32 && !TRACE), "fused all-reduce: 256 x 128 pair tiles, 16-bit output");
   using Cfg = PairCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int HB = BN / 2;  // B rows held by one CTA
@@ -769,11 +875,15 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   uint64_t* tempty = bars + 2 * S + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * S + 4);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* s_ready = reinterpret_cast<volatile int*>(tmem_slot + 2);  // AR: owned tile ready?
+  volatile int* s_next = reinterpret_cast<volatile int*>(tmem_slot + 3);   // AR: next owned tile
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();   // 0 = leader
   long long* tr = TRACE ? p.trace + static_cast<long long>(blockIdx.x) * kTraceSlots : nullptr;
+  long long* dbg = (AR && ar.dbg) ? ar.dbg + static_cast<long long>(blockIdx.x) * 8 : nullptr;
+  if (AR && dbg && threadIdx.x == 0) dbg[0] = static_cast<long long>(globaltimer_ns());
   if (TRACE && threadIdx.x == 0) tr[0] = clock64();
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -789,6 +899,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       mbar_init(&tempty[i], 2 * kPairEpiWarps);
     }
     *abort_flag = 0;
+    *s_ready = 0;
+    *s_next = (AR && ar.exchange) ? 0 : static_cast<int>(blockIdx.x);
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -810,6 +922,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_base = *tmem_slot;
   }
   const int num_kb = (p.K + kBK - 1) / kBK;
+  const int ar_epoch = AR ? (ar.epoch + (ar.epoch_base ? *ar.epoch_base : 0)) : 0;
+  const int num_m128 = (p.M + kBM - 1) / kBM;  // AR: 128-row tiles of the output
+  // Exchange mode has no hand-shake after the reduction, so a rank may start its next call
+  // while a peer still reads this call's partials: calls alternate between two staging halves.
+  const long long stage_half =
+      (AR && ar.exchange && (ar_epoch & 1)) ? static_cast<long long>(ar.tp) * ar.max_tiles * (kBM * BN) : 0;
   if (TRACE && threadIdx.x == 0) tr[1] = clock64();
 
   if (warp == 0) {
@@ -893,6 +1011,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_commit_pair(&tfull[acc], 3);
       }
       if (TRACE) { tr[5] = stall_full; tr[6] = stall_acc; tr[7] = clock64(); tr[8] = it; }
+      if (AR && dbg) dbg[7] = static_cast<long long>(globaltimer_ns());
     }
   } else {
     const int quarter = warp & 3;      // TMEM lane quarter this warp may access
@@ -900,6 +1019,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     EpiStage es{epi_smem + (warp - 2) * kEpiBytesPerWarp, 0};
     int it = 0;
     bool ok = true;
+    // AR: index (into this rank's owned tiles) of the next one this CTA reduces
+    long long pub_ns = 0;
+    int n_early = 0;
+    int next_owned = (AR && !ar.exchange) ? static_cast<int>(blockIdx.x) : 0;
+    const int n_owned = !AR ? 0
+                        : ar.exchange ? (p.num_tiles - pair + npairs - 1) / npairs
+                                      : (num_m128 * ((p.N + BN - 1) / BN) - ar.rank + ar.tp - 1) / ar.tp;
     long long stall_epi = 0, cyc_ld = 0, cyc_rest = 0;
     long long cyc3[5] = {0, 0, 0, 0, 0};
     for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
@@ -918,6 +1044,111 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const int row0 = m0 + quarter * 32;
+      if (AR) {
+        // phase A: this warp's chunks of the partial tile go to the owner's staging buffer
+        const int m128 = m0 / kBM;
+        const int ar_tile = m128 + (tile / p.num_m_tiles) * num_m128;
+        const bool in_range = m128 < num_m128;  // M may end inside the pair tile (warp-uniform)
+        const int owner = ar_tile % ar.tp;
+        const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+        T* tile_dst = static_cast<T*>(ar.stage[owner]) +
+                      (static_cast<long long>(ar.rank) * ar.max_tiles + ar_tile) * (kBM * BN);
+#pragma unroll 1
+        for (int c = half; c < BN / 32; c += 2) {
+          uint32_t r[32];
+          __syncwarp();
+          tmem_ld_32x32(t_acc + c * 32, r);
+          tmem_ld_wait();
+          if (!in_range) continue;
+          uint8_t* sb = es.buf + (es.issued & 1) * 2048;
+          ++es.issued;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            uint4 ov;
+            ov.x = Elem<T>::pack2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+            ov.y = Elem<T>::pack2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+            ov.z = Elem<T>::pack2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+            ov.w = Elem<T>::pack2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+            *reinterpret_cast<uint4*>(sb + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = ov;
+          }
+          __syncwarp();
+          // block (c, quarter): 2 KB contiguous at the owner; lane i copies 16-byte pieces
+          // i, i + 32, i + 64, i + 96 (piece = row * 4 + part).  Exchange mode: to every rank.
+          const long long blk_off = stage_half +
+                                    (static_cast<long long>(ar.rank) * ar.max_tiles + ar_tile) * (kBM * BN) +
+                                    (c * 4 + quarter) * 1024;
+          uint4 pv[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const int piece = lane + 32 * k;
+            const int rr = piece >> 2, part = piece & 3;
+            pv[k] = *reinterpret_cast<const uint4*>(sb + rr * 64 + ((part ^ ((rr >> 1) & 3)) << 4));
+          }
+          if (ar.exchange) {
+            for (int dst = 0; dst < ar.tp; ++dst) {
+              uint4* blk = reinterpret_cast<uint4*>(static_cast<T*>(ar.stage[dst]) + blk_off);
+#pragma unroll
+              for (int k = 0; k < 4; ++k) blk[lane + 32 * k] = pv[k];
+            }
+          } else {
+            uint4* blk = reinterpret_cast<uint4*>(static_cast<T*>(ar.stage[owner]) + blk_off);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) blk[lane + 32 * k] = pv[k];
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+        // publish the tile once all eight warps have stored their blocks (named barrier 2); the
+        // release store is cumulative over the writes ordered before it by the barrier
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (threadIdx.x == 64 && in_range) {
+          const unsigned long long t_p = dbg ? globaltimer_ns() : 0;
+          if (ar.exchange) {
+            for (int dst = 0; dst < ar.tp; ++dst)
+              st_release_sys(ar.flag_a[dst] + static_cast<long long>(ar_tile) * kMaxTp + ar.rank, ar_epoch);
+          } else {
+            st_release_sys(ar.flag_a[owner] + static_cast<long long>(ar_tile) * kMaxTp + ar.rank, ar_epoch);
+          }
+          if (dbg) pub_ns += static_cast<long long>(globaltimer_ns() - t_p);
+        }
+        // Phase B between tiles: while the tensor core works on the next tile, the epilogue
+        // warps look (once, without waiting) whether a tile this CTA is to reduce has arrived
+        // from every rank, and if so reduce it now.  Reduce-scatter mode: the next tile of this
+        // rank's share; exchange mode: the oldest of this CTA's own tiles not yet reduced.
+        if (next_owned < n_owned) {
+          int otile;
+          bool o_in_range = true;
+          if (ar.exchange) {  // next_owned counts this CTA's own tiles
+            const int t2 = pair + next_owned * npairs;
+            const int o128 = (t2 % p.num_m_tiles) * 2 + static_cast<int>(cta);
+            otile = o128 + (t2 / p.num_m_tiles) * num_m128;
+            o_in_range = o128 < num_m128;
+          } else {            // next_owned indexes the tiles this rank owns
+            otile = next_owned * ar.tp + ar.rank;
+          }
+          if (threadIdx.x == 64) {
+            bool ready = true;
+            if (o_in_range)
+              for (int src = 0; src < ar.tp; ++src)
+                ready = ready &&
+                        ld_acquire_sys(ar.flag_a[ar.rank] + static_cast<long long>(otile) * kMaxTp + src) >= ar_epoch;
+            *s_ready = ready ? 1 : 0;
+          }
+          asm volatile("bar.sync 2, 256;" ::: "memory");
+          if (*s_ready) {
+            if (o_in_range) ar_reduce_tile<T, BN>(p, ar, otile, num_m128, threadIdx.x - 64, 256, ar.exchange != 0, stage_half);
+            if (!ar.exchange) {
+              asm volatile("bar.sync 2, 256;" ::: "memory");
+              if (threadIdx.x >= 64 && threadIdx.x < 64 + ar.tp)
+                st_release_sys(ar.flag_b[threadIdx.x - 64] + otile, ar_epoch);
+            }
+            next_owned += ar.exchange ? 1 : static_cast<int>(gridDim.x);
+            ++n_early;
+          }
+        }
+        continue;
+      }
       if (row0 < p.M) {
         const int nc = (min(BN, p.N - n0) + 31) / 32;
         const long long t_l = TRACE ? clock64() : 0;
@@ -933,6 +1164,64 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (TRACE && threadIdx.x == 64) { tr[11] = stall_epi; tr[12] = clock64(); tr[14] = cyc_ld; tr[15] = cyc_rest;
       tr[16] = cyc3[0]; tr[17] = cyc3[1]; tr[18] = cyc3[2]; tr[19] = cyc3[3]; tr[20] = cyc3[4]; }
     epi_drain(lane);  // the staging buffers must outlive the stores that read them
+    if (AR && threadIdx.x == 64) {
+      *s_next = next_owned;
+      if (dbg) {
+        dbg[1] = static_cast<long long>(globaltimer_ns());
+        dbg[4] = n_early;
+        dbg[5] = pub_ns;
+      }
+    }
+  }
+
+  if (AR) {
+    __syncthreads();
+    __shared__ int s_ok;
+    // phase B, remainder: the tiles that were not reduced between this CTA's own tiles
+    const int num_ar_tiles = num_m128 * ((p.N + BN - 1) / BN);
+    const int nthreads = static_cast<int>(blockDim.x);
+    if (ar.exchange) {
+      const int n_mine = (p.num_tiles - pair + npairs - 1) / npairs;
+      for (int seq = *s_next; seq < n_mine; ++seq) {
+        const int t2 = pair + seq * npairs;
+        const int o128 = (t2 % p.num_m_tiles) * 2 + static_cast<int>(cta);
+        if (o128 >= num_m128) continue;  // uniform over the CTA
+        const int tile = o128 + (t2 / p.num_m_tiles) * num_m128;
+        if (threadIdx.x == 0) {
+          bool ok = true;
+          for (int src = 0; src < ar.tp && ok; ++src)
+            ok = wait_flag(ar.flag_a[ar.rank] + static_cast<long long>(tile) * kMaxTp + src, ar_epoch, wctx,
+                           kErrWaitPeer);
+          s_ok = ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (s_ok) ar_reduce_tile<T, BN>(p, ar, tile, num_m128, threadIdx.x, nthreads, true, stage_half);
+        __syncthreads();
+      }
+      if (dbg && threadIdx.x == 0) dbg[2] = static_cast<long long>(globaltimer_ns());
+    } else {
+      const int n_owned = (num_ar_tiles - ar.rank + ar.tp - 1) / ar.tp;
+      for (int j = *s_next; j < n_owned; j += gridDim.x) {
+        const int tile = j * ar.tp + ar.rank;
+        if (threadIdx.x == 0) {
+          bool ok = true;
+          for (int src = 0; src < ar.tp && ok; ++src)
+            ok = wait_flag(ar.flag_a[ar.rank] + static_cast<long long>(tile) * kMaxTp + src, ar_epoch, wctx,
+                           kErrWaitPeer);
+          s_ok = ok ? 1 : 0;
+        }
+        __syncthreads();
+        if (s_ok) ar_reduce_tile<T, BN>(p, ar, tile, num_m128, threadIdx.x, nthreads, false, stage_half);
+        __syncthreads();
+        if (s_ok && threadIdx.x < ar.tp) st_release_sys(ar.flag_b[threadIdx.x] + tile, ar_epoch);
+      }
+      if (dbg && threadIdx.x == 0) dbg[2] = static_cast<long long>(globaltimer_ns());
+      // phase C: every tile of the output must have arrived in this rank's memory
+      for (int tile = blockIdx.x * nthreads + threadIdx.x; tile < num_ar_tiles; tile += gridDim.x * nthreads)
+        wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
+    }
+    __syncthreads();
+    if (dbg && threadIdx.x == 0) dbg[3] = static_cast<long long>(globaltimer_ns());
   }
 
   // teardown: nobody leaves (or frees TMEM) while the peer may still read this CTA's shared
@@ -958,11 +1247,11 @@ static int max_pairs() {
   return cached[dev];
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false, bool AR = false>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO,
-                            const GemmParams& p, cudaStream_t stream) {
+                            const GemmParams& p, cudaStream_t stream, const ArParams* arp = nullptr) {
   using Cfg = PairCfg<BN>;
-  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32, TRACE>;
+  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32, TRACE, AR>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -970,6 +1259,9 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
       return kErrLaunch;
     configured = true;
   }
+  ArParams ar;
+  if (arp) ar = *arp;
+  else { ar.tp = 0; ar.exchange = 0; ar.dbg = nullptr; }
   const int pairs = p.num_tiles < max_pairs() ? p.num_tiles : max_pairs();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -983,7 +1275,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p) == cudaSuccess ? kOk : kErrLaunch;
+  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p, ar) == cudaSuccess ? kOk : kErrLaunch;
 }
 
 template <typename T, int BN>
@@ -1002,6 +1294,8 @@ static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorM
 // shape); total = waves x that.  Wave quantisation matters because M is only ~1024 rows per
 // token slice.
 static bool g_pair_default = true;
+static bool g_ar_exchange = false;     // one-hop exchange instead of reduce-scatter + all-gather
+static long long* g_ar_debug = nullptr;
 
 // Measured model of one launch, in kilo-cycles: waves x (main loop of one tile, proportional to
 // K, + epilogue where it does not overlap the next tile) + exposed epilogue of the last tile.
@@ -1095,7 +1389,8 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
 
 // Fused GEMM + tensor-parallel all-reduce (see the file comment).  `out_ptrs[r]` is the address
 // of the output matrix in rank r's memory (peer-mapped), `stage_ptrs` / `flag_*_ptrs` the
-// staging and flag arrays of every rank.  BN is fixed to 128.  Every rank of the group must
+// staging and flag arrays of every rank.  All-reduce tiles are 128 x 128; the product runs on
+// 256 x 128 CTA-pair tiles unless tp_gemm_set_pair_default(0) selected the one-CTA kernel.  Every rank of the group must
 // make the same call with the same epoch = `epoch` + *`epoch_base`; the sum must grow from call
 // to call (epoch = index of the call within a step, *epoch_base advanced per step on the device).
 extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, const void* B,
@@ -1110,15 +1405,17 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 8)) return kErrBadArgument;
   constexpr int BN = 128;
   const bool bf16 = dtype == 1;
+  const bool pair = g_pair_default;  // 256 x 128 CTA-pair tiles; all-reduce tiles stay 128 x 128
+  const int BM = pair ? 2 * kBM : kBM;
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
-  p.num_m_tiles = (M + kBM - 1) / kBM;
+  p.num_m_tiles = (M + BM - 1) / BM;
   p.num_tiles = p.num_m_tiles * ((N + BN - 1) / BN);
-  if (p.num_tiles > max_tiles) return kErrTooLarge;
+  if (((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) > max_tiles) return kErrTooLarge;
   CUtensorMap tmA, tmB;
   if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16)) return kErrDriver;
   if (!(b_mn ? make_tmap_2d(&tmB, B, N, K, ldb, 64, kBK, bf16)
-             : make_tmap_2d(&tmB, B, K, N, ldb, kBK, BN, bf16)))
+             : make_tmap_2d(&tmB, B, K, N, ldb, kBK, pair ? BN / 2 : BN, bf16)))
     return kErrDriver;
   p.out = out_ptrs[rank]; p.ldo = ldo;
   p.bias = bias; p.residual = residual; p.ldr = ldr;
@@ -1129,6 +1426,8 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.variant = 0;
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
+  ar.exchange = (g_pair_default && g_ar_exchange) ? 1 : 0;
+  ar.dbg = g_ar_debug;
   for (int i = 0; i < kMaxTp; ++i) {
     ar.stage[i] = i < tp ? stage_ptrs[i] : nullptr;
     ar.flag_a[i] = i < tp ? flag_a_ptrs[i] : nullptr;
@@ -1137,6 +1436,13 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const CUtensorMap& tmO = tmA;  // the fused all-reduce epilogue stores through peer pointers
+  if (pair) {
+    if (bf16)
+      return b_mn ? launch_gemm_pair<__nv_bfloat16, BN, false, true, false, false, true>(tmA, tmB, tmO, p, s, &ar)
+                  : launch_gemm_pair<__nv_bfloat16, BN, false, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
+    return b_mn ? launch_gemm_pair<__half, BN, false, true, false, false, true>(tmA, tmB, tmO, p, s, &ar)
+                : launch_gemm_pair<__half, BN, false, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
+  }
   if (bf16)
     return b_mn ? launch_gemm<__nv_bfloat16, BN, false, true, false, true>(tmA, tmB, tmO, p, s, &ar)
                 : launch_gemm<__nv_bfloat16, BN, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
@@ -1186,6 +1492,19 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   return bn == 256 ? launch_gemm_pair<__half, 256, false, false, false, true>(tmA, tmB, tmO, p, s)
                    : launch_gemm_pair<__half, 128, false, false, false, true>(tmA, tmB, tmO, p, s);
 }
+
+// Fused all-reduce, CTA-pair kernel.  exchange = 1: every rank sends each partial tile to every
+// rank and reduces all tiles itself (one NVLink hop, (tp - 1) x the bytes); 0 (default):
+// reduce-scatter to an owner rank, then all-gather (two hops).  On two B200s the one-hop form
+// measured slower (86 vs 72 us for 1024 x 5120 x 2560).
+extern "C" void tp_gemm_ar_set_exchange(int enabled) { tp::g_ar_exchange = enabled != 0; }
+
+// Timing probe of the fused all-reduce (CTA-pair kernel): `buf` is a device array of 8 int64 per
+// CTA (296 CTAs at most) or null to switch the probe off.  Slots, in globaltimer nanoseconds:
+// 0 kernel entry, 1 all own tiles sent and published, 2 all assigned reductions done, 3 all
+// results arrived (exit), 4 reductions done between tiles, 5 ns spent in the release stores that
+// publish tiles, 7 last MMA issued (leader CTA of each pair).
+extern "C" void tp_gemm_ar_set_debug(long long* buf) { tp::g_ar_debug = buf; }
 
 // Process-wide switch for the automatic tile choice: 0 keeps every GEMM on single-CTA tiles.
 extern "C" void tp_gemm_set_pair_default(int enabled) { tp::g_pair_default = enabled != 0; }

@@ -109,7 +109,9 @@ class FusedAllReduceContext:
         self.tp = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.max_tiles = ((max_rows + 127) // 128) * ((max_cols + 127) // 128)
-        stage_bytes = self.tp * self.max_tiles * self.TILE_BYTES
+        # two halves: with two ranks the kernel exchanges partials in one hop and alternates the
+        # half from call to call (a rank may start its next call while its peer still reduces)
+        stage_bytes = 2 * self.tp * self.max_tiles * self.TILE_BYTES
         flag_a_bytes = self.max_tiles * self.KMAX_TP * 4
         flag_b_bytes = self.max_tiles * 4
         self._off_flag_a = stage_bytes

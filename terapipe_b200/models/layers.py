@@ -22,6 +22,30 @@ from ..utils import checkpoint as ckpt
 from .config import NEG_INF
 
 
+class _AssignCache(torch.autograd.Function):
+    """KV-append: write ``value`` into ``cache[index]`` in place and return ``cache``
+    (reference: transformer_models.py:177-193).  The gradient of the written region flows to
+    ``value``; the rest flows to the earlier cache.  Unlike the reference, backward does not
+    clone the whole cache gradient: it reuses the incoming buffer and zeroes the slice in it,
+    which is safe because that buffer is consumed by nobody else."""
+
+    @staticmethod
+    def forward(ctx, cache, value, index):
+        ctx.index = index
+        cache.data[index] = value  # through .data: the version counter must not move
+        return cache
+
+    @staticmethod
+    def backward(ctx, grad_cache_output):
+        grad_value = grad_cache_output[ctx.index].clone()
+        grad_cache = grad_cache_output
+        grad_cache.data[ctx.index] = 0
+        return grad_cache, grad_value, None
+
+
+assign_cache_ = _AssignCache.apply
+
+
 class MultiheadLMAttentionWithCache(nn.Module):
     def __init__(self, embed_dim, num_heads, bias=True, device="cpu"):
         super().__init__()

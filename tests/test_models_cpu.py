@@ -178,3 +178,20 @@ torch.save({"sd": ref.state_dict(), "x": x, "y": torch.cat([y0, y1]).detach()}, 
     y0, _ = mine(blob["x"][:4], cache, 0)
     y1, _ = mine(blob["x"][4:], cache, 4)
     assert torch.allclose(torch.cat([y0, y1]), blob["y"], atol=1e-5)
+
+
+def test_assign_cache_appends_in_place_and_routes_gradients():
+    """KV-append op of the reference API (transformer_models.py:177-193)."""
+    from transformer_models import assign_cache_
+    torch.manual_seed(0)
+    k1 = torch.randn(2, 3, 4, requires_grad=True)
+    k2 = torch.randn(2, 5, 4, requires_grad=True)
+    w = torch.randn(2, 8, 4)
+    cache = torch.zeros(2, 8, 4).requires_grad_()
+    c = assign_cache_(cache, k1, (slice(None), slice(0, 3)))
+    used_early = (c[:, :3] * w[:, :3]).sum()          # a consumer between the two appends
+    c = assign_cache_(c, k2, (slice(None), slice(3, 8)))
+    (used_early + (c * w).sum()).backward()
+    assert torch.equal(cache.data[:, :3], k1.data) and torch.equal(cache.data[:, 3:], k2.data)
+    assert torch.allclose(k1.grad, 2 * w[:, :3])      # seen by both consumers
+    assert torch.allclose(k2.grad, w[:, 3:])

@@ -31,6 +31,8 @@ GEMM + all-reduce kernel over NVLink peer memory (``tp_comm="fused"``).
 """
 from __future__ import annotations
 
+import os
+
 import math
 from typing import Dict, List, Optional, Sequence
 
@@ -251,6 +253,9 @@ class StageEngine:
             self.ar = FusedAllReduceContext(mpu.get_model_parallel_group(), tmax, H, pool)
             self.ar_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
             self._ar_calls = 0
+            # TERAPIPE_AR_EXCHANGE=1 selects the one-hop form of the fused all-reduce (every
+            # rank receives every partial tile); the default is reduce-scatter + all-gather
+            self.lib.tp_gemm_ar_set_exchange(int(os.environ.get("TERAPIPE_AR_EXCHANGE", "0") == "1"))
 
         def sym(name, nrows):
             if self.ar is None:

@@ -9,8 +9,9 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-def _worker(rank, world, port, tp, pp, out_dir, tp_comm):
+def _worker(rank, world, port, tp, pp, out_dir, tp_comm, exchange=False):
     import torch.distributed as dist
+    os.environ["TERAPIPE_AR_EXCHANGE"] = "1" if exchange else "0"
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -52,8 +53,9 @@ def _single_gpu_reference():
     return {k: v.cpu() for k, v in eng.named_grads().items()}, eng.loss().item()
 
 
-@pytest.mark.parametrize("tp,pp,tp_comm", [(1, 2, "nccl"), (2, 1, "nccl"), (2, 1, "fused")])
-def test_two_gpu_layouts_match_single_gpu(tp, pp, tp_comm):
+@pytest.mark.parametrize("tp,pp,tp_comm,exchange", [(1, 2, "nccl", False), (2, 1, "nccl", False),
+                                                    (2, 1, "fused", False), (2, 1, "fused", True)])
+def test_two_gpu_layouts_match_single_gpu(tp, pp, tp_comm, exchange):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     import torch.multiprocessing as mp
@@ -61,8 +63,31 @@ def test_two_gpu_layouts_match_single_gpu(tp, pp, tp_comm):
     from terapipe_b200.models import slice_state_dict
     full, loss = _single_gpu_reference()
     with tempfile.TemporaryDirectory() as d:
-        mp.spawn(_worker, args=(2, free_port(), tp, pp, d, tp_comm), nprocs=2, join=True)
+        mp.spawn(_worker, args=(2, free_port(), tp, pp, d, tp_comm, exchange), nprocs=2, join=True)
         results = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    for res in results:
+        _, pp_idx, tp_idx = res["coords"]
+        want = slice_state_dict(4, full, tp=tp, tp_rank=tp_idx, pp=pp, pp_rank=pp_idx)
+        if res["loss"] is not None:
+            assert abs(res["loss"] - loss) < 2e-3
+        for k, g in want.items():
+            rel = (res["grads"][k] - g).norm() / (g.norm() + 1e-12)
+            assert rel < 3e-2, (k, float(rel))
+
+
+@pytest.mark.parametrize("tp,pp,exchange", [(4, 1, False), (2, 2, False), (2, 2, True), (4, 1, True)])
+def test_four_gpu_fused_layouts_match_single_gpu(tp, pp, exchange):
+    """Fused GEMM + all-reduce with four-way tensor parallelism (tile owners 0..3) and combined
+    with a two-stage pipeline; both forms of the all-reduce."""
+    if torch.cuda.device_count() < 4:
+        pytest.skip("needs 4 GPUs")
+    import torch.multiprocessing as mp
+    from dist_utils import free_port
+    from terapipe_b200.models import slice_state_dict
+    full, loss = _single_gpu_reference()
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_worker, args=(4, free_port(), tp, pp, d, "fused", exchange), nprocs=4, join=True)
+        results = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(4)]
     for res in results:
         _, pp_idx, tp_idx = res["coords"]
         want = slice_state_dict(4, full, tp=tp, tp_rank=tp_idx, pp=pp, pp_rank=pp_idx)

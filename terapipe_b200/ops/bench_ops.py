@@ -225,10 +225,15 @@ def main():
     ap.add_argument("--params", type=int, default=302_000_000)
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--tile", default="0", help="gemm: comma list of tile codes to force")
+    ap.add_argument("--prefetch", type=int, default=None,
+                    help="gemm: L2 prefetch distance of the CTA-pair kernel in k-steps (0 = off)")
     ap.add_argument("--once", action="store_true")
     ap.add_argument("--flush", action="store_true")
     a = ap.parse_args()
     a.dtype = torch.float16 if a.dtype == "fp16" else torch.bfloat16
+    if a.prefetch is not None:
+        from .lib import cuda_lib
+        cuda_lib().tp_gemm_set_prefetch(a.prefetch)
     a.flush_buf = torch.empty(256 * 1024 * 1024, device="cuda", dtype=torch.uint8) if a.flush else None
     {"gemm": case_gemm, "gemm-trace": case_gemm_trace, "attn": case_attn, "norm": case_norm, "adam": case_adam}[a.case](a)
     torch.cuda.synchronize()

@@ -54,6 +54,8 @@ struct GemmParams {
   int accumulate;  // fp32 output only
   int* err;
   long long* trace;  // optional per-CTA phase stamps (trace builds of the kernel only)
+  int prefetch;      // CTA-pair kernel: operand tiles are prefetched into L2 this many k-steps
+                     // ahead of the loads that fill the ring (0 = off)
   int variant;       // trace builds only: 1 = epilogue reads TMEM and drops the values, 2 = stops
                      // after the shared-memory writes, 3 = stops after the proxy fence
 };
@@ -947,6 +949,23 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           uint8_t* sA = smem + stage * Cfg::kStageBytes;
           uint8_t* sB = sA + Cfg::kABytes;
           if (cta == 0) mbar_expect_tx(&full[stage], 2 * Cfg::kStageBytes);
+          if (p.prefetch > 0 && kb + p.prefetch < num_kb) {
+            // operands that come from DRAM (weights of a step are cold in L2) have a latency
+            // the ring alone cannot cover; an L2 prefetch further ahead does
+            const int kp = (kb + p.prefetch) * kBK;
+            if (!A_MN) {
+              tma_prefetch_2d(&tmA, kp, m0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < kBM / 64; ++c) tma_prefetch_2d(&tmA, m0 + c * 64, kp);
+            }
+            if (!B_MN) {
+              tma_prefetch_2d(&tmB, kp, n0);
+            } else {
+#pragma unroll
+              for (int c = 0; c < HB / 64; ++c) tma_prefetch_2d(&tmB, n0 + c * 64, kp);
+            }
+          }
           const uint32_t bar = mapa_u32(smem_u32(&full[stage]), 0);
           if (!A_MN) {
             tma_load_2d_pair(sA, &tmA, bar, kb * kBK, m0);
@@ -1294,6 +1313,7 @@ static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorM
 // shape); total = waves x that.  Wave quantisation matters because M is only ~1024 rows per
 // token slice.
 static bool g_pair_default = true;
+static int g_prefetch = 0;             // L2 prefetch distance of the CTA-pair kernel, in k-steps
 static bool g_ar_exchange = false;     // one-hop exchange instead of reduce-scatter + all-gather
 static long long* g_ar_debug = nullptr;
 
@@ -1374,6 +1394,7 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   p.alpha = alpha; p.act = act; p.dact = dact; p.accumulate = accumulate;
   p.err = err_flag;
   p.trace = nullptr;
+  p.prefetch = g_prefetch;
   p.variant = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define TP_DISPATCH(T)                                                                   \
@@ -1423,6 +1444,7 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
   p.err = err_flag;
   p.trace = nullptr;
+  p.prefetch = g_prefetch;
   p.variant = 0;
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
@@ -1487,6 +1509,7 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
   p.err = err_flag;
   p.trace = trace;
+  p.prefetch = g_prefetch;
   p.variant = variant;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return bn == 256 ? launch_gemm_pair<__half, 256, false, false, false, true>(tmA, tmB, tmO, p, s)
@@ -1505,6 +1528,9 @@ extern "C" void tp_gemm_ar_set_exchange(int enabled) { tp::g_ar_exchange = enabl
 // results arrived (exit), 4 reductions done between tiles, 5 ns spent in the release stores that
 // publish tiles, 7 last MMA issued (leader CTA of each pair).
 extern "C" void tp_gemm_ar_set_debug(long long* buf) { tp::g_ar_debug = buf; }
+
+// L2 prefetch distance (in 64-element k-steps) of the CTA-pair kernel's producer; 0 switches it off.
+extern "C" void tp_gemm_set_prefetch(int k_steps) { tp::g_prefetch = k_steps < 0 ? 0 : k_steps; }
 
 // Process-wide switch for the automatic tile choice: 0 keeps every GEMM on single-CTA tiles.
 extern "C" void tp_gemm_set_pair_default(int enabled) { tp::g_pair_default = enabled != 0; }

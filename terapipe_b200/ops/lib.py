@@ -71,6 +71,7 @@ def _declare(lib: ctypes.CDLL) -> None:
         "tp_gemm_ar": [I, I, P, L, P, L, L, I, I, I, P, P, L, I, I, I, P, I, P, P, P, P, P, P],
         "tp_advance_counter": [P, I, P],
         "tp_gemm_set_pair_default": [I],
+        "tp_gemm_set_prefetch": [I],
         "tp_gemm_ar_set_exchange": [I],
         "tp_gemm_ar_set_debug": [P],
         "tp_link_probe": [P, L, I, P],

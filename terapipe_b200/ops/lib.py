@@ -55,32 +55,37 @@ def host_lib() -> ctypes.CDLL:
     return _host
 
 
+# Argument types of every entry point of the kernel library that is called through `cuda_lib()`:
+# P = pointer, I = int, L = long long, F = float.  tests/test_bindings_cpu.py checks this table
+# against the `extern "C"` definitions in csrc/*.cu.
+P, I, L, F = c_void_p, c_int, c_longlong, c_float
+SIGNATURES = {
+    "tp_gemm": [I, I, I, P, L, P, L, P, L, I, I, I, I, I, F, P, P, L, I, P, I, P, L, I, P, P],
+    "tp_layernorm_fwd": [I, P, P, P, P, P, P, I, I, F, P],
+    "tp_layernorm_bwd_parts": [I],
+    "tp_layernorm_bwd": [I, P, P, P, P, P, P, P, P, P, P, I, I, P],
+    "tp_layernorm_bwd_accum": [I, P, P, P, P, P, P, P, P, I, I, P],
+    "tp_layernorm_bwd_finish": [P, I, I, P, P, P],
+    "tp_colsum": [I, P, L, I, I, P, P],
+    "tp_adam_tick": [P, F, F, P],
+    "tp_fused_adam": [I, P, P, P, P, P, L, P, F, F, F, F, F, F, P],
+    "tp_fill": [I, P, L, F, P],
+    "tp_gemm_ar": [I, I, P, L, P, L, L, I, I, I, P, P, L, I, I, I, P, I, P, P, P, P, P, P],
+    "tp_advance_counter": [P, I, P],
+    "tp_gemm_set_pair_default": [I],
+    "tp_gemm_set_prefetch": [I],
+    "tp_gemm_ar_set_exchange": [I],
+    "tp_gemm_ar_set_debug": [P],
+    "tp_link_probe": [P, L, I, P],
+    "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, I, P, P],
+    "tp_dp_reduce_adam": [I, I, I, I, P, P, P, P, P, P, P, L, L, P, F, F, F, F, F, F, P, P],
+    "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
+    "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
+}
+
+
 def _declare(lib: ctypes.CDLL) -> None:
-    P, I, L, F = c_void_p, c_int, c_longlong, c_float
-    sigs = {
-        "tp_gemm": [I, I, I, P, L, P, L, P, L, I, I, I, I, I, F, P, P, L, I, P, I, P, L, I, P, P],
-        "tp_layernorm_fwd": [I, P, P, P, P, P, P, I, I, F, P],
-        "tp_layernorm_bwd_parts": [I],
-        "tp_layernorm_bwd": [I, P, P, P, P, P, P, P, P, P, P, I, I, P],
-        "tp_layernorm_bwd_accum": [I, P, P, P, P, P, P, P, P, I, I, P],
-        "tp_layernorm_bwd_finish": [P, I, I, P, P, P],
-        "tp_colsum": [I, P, L, I, I, P, P],
-        "tp_adam_tick": [P, F, F, P],
-        "tp_fused_adam": [I, P, P, P, P, P, L, P, F, F, F, F, F, F, P],
-        "tp_fill": [I, P, L, F, P],
-        "tp_gemm_ar": [I, I, P, L, P, L, L, I, I, I, P, P, L, I, I, I, P, I, P, P, P, P, P, P],
-        "tp_advance_counter": [P, I, P],
-        "tp_gemm_set_pair_default": [I],
-        "tp_gemm_set_prefetch": [I],
-        "tp_gemm_ar_set_exchange": [I],
-        "tp_gemm_ar_set_debug": [P],
-        "tp_link_probe": [P, L, I, P],
-        "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, I, P, P],
-        "tp_dp_reduce_adam": [I, I, I, I, P, P, P, P, P, P, P, L, L, P, F, F, F, F, F, F, P, P],
-        "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
-        "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
-    }
-    for name, argtypes in sigs.items():
+    for name, argtypes in SIGNATURES.items():
         if hasattr(lib, name):
             fn = getattr(lib, name)
             fn.restype = c_int

@@ -105,20 +105,48 @@ class NCCLTransformerRunner:
 
     @timeout(seconds=500)
     def run(self, n_steps, warmup_steps=5, verbose=True):
-        times = []
+        """Times ``n_steps`` iterations.  Returns (mean, std) of the wall-clock step time in
+        seconds over the steps after the warm-up, as the reference does
+        (test_transformer_terapipe.py:289-303).  Also recorded, for the drivers' extended result
+        rows: ``last_device_ms`` (mean step time between CUDA events on the launching stream;
+        wall clock on CPU) and ``last_peak_memory_gb``."""
+        times, dev_ms = [], []
+        cuda = torch.cuda.is_available()
+        if cuda:
+            torch.cuda.reset_peak_memory_stats()
         for _ in range(n_steps):
             t0 = time.time()
+            if cuda:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
             self.step()
-            if torch.cuda.is_available():
+            if cuda:
+                e1.record()
                 torch.cuda.synchronize()
+                dev_ms.append(e0.elapsed_time(e1))
             times.append(time.time() - t0)
+            if not cuda:
+                dev_ms.append(times[-1] * 1e3)
             if verbose:
                 print("rank", self.rank, "step_time:", times[-1], flush=True)
-        kept = times[warmup_steps:] if len(times) > warmup_steps else times
+        skip = warmup_steps if len(times) > warmup_steps else 0
+        kept = times[skip:]
         mean, std = float(np.mean(kept)), float(np.std(kept))
-        if len(times) > warmup_steps:
+        self.last_device_ms = float(np.mean(dev_ms[skip:]))
+        self.last_peak_memory_gb = torch.cuda.max_memory_allocated() / 2 ** 30 if cuda else 0.0
+        if skip:
             print("rank", self.rank, "step_time_mean:", mean, "step_time_std:", std, flush=True)
         return mean, std
+
+    def max_over_ranks_device_ms(self):
+        """``last_device_ms`` of the slowest rank (the job's step time)."""
+        value = getattr(self, "last_device_ms", None)
+        if value is None or not dist.is_initialized() or dist.get_world_size() == 1:
+            return value
+        dev = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else "cpu"
+        t = torch.tensor([value], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
 
     def _grads_for(self, batch_slices, seq_slices, x):
         if self.engine_kind == "b200":

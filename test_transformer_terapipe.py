@@ -80,11 +80,17 @@ def main():
             else:
                 mean_time, std_time = runner.run(args.n_steps, verbose=args.verbose)
                 result["mean_time"], result["std_time"] = mean_time, std_time
+                # beyond the reference's schema: job throughput, device-timed step of the slowest
+                # rank, this rank's peak memory
                 result["tokens_per_s"] = batch * dp * config.seq_len / mean_time
+                result["max_over_ranks_device_ms"] = runner.max_over_ranks_device_ms()
+                result["peak_memory_gb"] = runner.last_peak_memory_gb
         except (torch.cuda.OutOfMemoryError, TimeoutError) as e:
             print(e, flush=True)
             result["mean_time"] = result["std_time"] = "OOM"
         results.append(result)
+        with open(f"results.rank{args.rank}.jsonl", "a") as f:  # one line per run and rank
+            f.write(json.dumps(result) + "\n")
         del runner
         gc.collect()
         if torch.cuda.is_available():

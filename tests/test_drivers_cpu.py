@@ -30,7 +30,9 @@ def test_sweep_driver_single_rank_writes_results(tmp_path):
         assert r["model"] == "test" and r["n_input_slices"] == 4 and r["mean_time"] > 0
         assert {"n_gpus", "batch_size", "n_batch_slices", "n_steps", "mixed_precision",
                 "model_parallel_size", "pipeline_parallel_size", "rank", "data_parallel_size",
-                "std_time"} <= set(r)
+                "std_time", "tokens_per_s", "max_over_ranks_device_ms", "peak_memory_gb"} <= set(r)
+    lines = [json.loads(l) for l in open(tmp_path / "results.rank0.jsonl")]
+    assert lines == results
 
 
 def test_launch_script_two_stage_pipeline_verify(tmp_path):

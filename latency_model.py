@@ -3,8 +3,8 @@ from the tables in ``performance_model_data/``.
 Implemented in :mod:`terapipe_b200.planner.latency_model`."""
 from terapipe_b200.planner.latency_model import *  # noqa: F401,F403
 from terapipe_b200.planner.latency_model import (SCAN_GRID, STEP_GAP, SingleLayerLatency,  # noqa: F401
-                                                 analysis_model, evaluate_split,
+                                                 analysis_model, cli, evaluate_split,
                                                  fit_single_layer_model, main, parse_json, planning)
 
 if __name__ == "__main__":
-    main()
+    cli()

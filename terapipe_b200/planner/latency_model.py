@@ -345,31 +345,59 @@ def scheme_to_dp_result(setting: Sequence, scheme: Scheme, latency: float) -> di
 # model, batch, tp, pipeline length, dp, nodes, gpus per node: single 8xB200 box settings
 B200_SETTINGS = [
     ("gpt3-1b", 8, 1, 8, 1, 1, 8),
+    ("gpt3-1b", 8, 1, 4, 1, 1, 4),
+    ("gpt3-1b", 8, 1, 2, 1, 1, 2),
     ("gpt3-13b", 8, 2, 4, 1, 1, 8),
     ("gpt3-44b", 4, 4, 2, 1, 1, 8),
 ]
 
 
-def main(settings=None, data_dir="performance_model_data", out="dp_results.json", step_gap=None):
+def main(settings=None, data_dir="performance_model_data", out="dp_results.json", step_gap=None,
+         kernel_model=False, fused_tp=True):
+    """Schedules for ``settings`` written to ``out``.  With ``kernel_model`` the latency tables
+    are not read from ``data_dir`` but synthesised from the analytic B200 kernel model
+    (``kernel_model.py``) into a scratch directory; entries are tagged with their table's origin."""
     settings = settings or B200_SETTINGS
     results = []
     for s in settings:
         try:
-            gap = step_gap
+            gap, table_dir = step_gap, data_dir
+            if kernel_model:
+                import tempfile
+                from .kernel_model import write_tables
+                table_dir = tempfile.mkdtemp(prefix="terapipe_tables_")
+                gap = gap or 64
+                write_tables(s[0], s[2], range(1, s[1] + 1), table_dir, step=gap,
+                             fused_tp=fused_tp and s[2] > 1, total_batch=s[1])
             if gap is None:  # the granularity the table was measured with
-                path = os.path.join(data_dir, f"latency_model.{s[0]}.mp_{s[2]}.json")
+                path = os.path.join(table_dir, f"latency_model.{s[0]}.mp_{s[2]}.json")
                 lens = sorted({int(k.split("_")[1]) for k in json.load(open(path))})
                 gap = min(b - a for a, b in zip(lens, lens[1:])) if len(lens) > 1 else STEP_GAP
-            scheme, latency = analysis_model(*s[:4], data_dir=data_dir, step_gap=gap)
+            scheme, latency = analysis_model(*s[:4], data_dir=table_dir, step_gap=gap,
+                                             verbose=not kernel_model)
         except FileNotFoundError as e:
             print(f"skip {s[0]}: {e}")
             continue
         if scheme is not None:
-            results.append(scheme_to_dp_result(s, scheme, latency))
+            entry = scheme_to_dp_result(s, scheme, latency)
+            entry["table"] = "kernel-model" if kernel_model else "measured"
+            results.append(entry)
     with open(out, "w") as f:
         json.dump(results, f, indent=4)
     return results
 
 
+def cli(argv=None):
+    import argparse
+    ap = argparse.ArgumentParser(description="slice schedules from latency tables")
+    ap.add_argument("--data-dir", default="performance_model_data")
+    ap.add_argument("--out", default="dp_results.json")
+    ap.add_argument("--step-gap", type=int, default=None)
+    ap.add_argument("--kernel-model", action="store_true",
+                    help="synthesise the tables from the analytic B200 kernel model")
+    a = ap.parse_args(argv)
+    return main(data_dir=a.data_dir, out=a.out, step_gap=a.step_gap, kernel_model=a.kernel_model)
+
+
 if __name__ == "__main__":
-    main()
+    cli()

@@ -117,3 +117,36 @@ def test_memory_model_golden_values():
     eight = memory_model.engine_memory_per_gpu("gpt3-1b", 8, tp=1, pp=8)
     assert 20 < one < 120 and eight < one / 6
     assert memory_model.engine_memory_per_gpu("gpt3-44b", 4, tp=4, pp=2) < 180
+
+
+def test_kernel_model_matches_recorded_step_and_behaves():
+    """Analytic B200 kernel model: calibration point, monotonicity, wave quantisation."""
+    from terapipe_b200.planner.kernel_model import B200KernelModel, predict_iteration_ms
+    km = B200KernelModel()
+    # measured on one B200: GPT3-1B shape, batch 8, 16 uniform slices, 198.0 ms per iteration
+    assert abs(predict_iteration_ms("gpt3-1b", 8, 1, 1, [8], [128] * 16, km) - 198.0) < 0.1 * 198.0
+    f0, b0 = km.layer_slice_us(2048, 16, 2048, 1, 8, 128, 0)
+    f1, b1 = km.layer_slice_us(2048, 16, 2048, 1, 8, 128, 1920)
+    assert f1 > f0 and abs(b1 - b0) < 0.3 * b0   # forward grows with the context; dK/dV + dQ trade off
+    # one more 256-row tile row than the SMs can hold in a wave costs a whole wave
+    assert km.gemm_us(1024, 6144, 2048) < km.gemm_us(1280, 6144, 2048)
+    assert km.gemm_us(1024, 2048, 8192) > 3 * km.gemm_us(1024, 2048, 2048) * 0.6
+    # more pipeline stages shorten the iteration, tensor parallelism pays a per-slice reduction
+    t = [predict_iteration_ms("gpt3-1b", 8, 1, pp, [8], [128] * 16, km) for pp in (1, 2, 4, 8)]
+    assert t[0] > t[1] > t[2] > t[3]
+    assert km.allreduce_us(1024, 5120, 2, fused=False) > km.allreduce_us(1024, 5120, 1, fused=False) == 0.0
+
+
+def test_planner_on_kernel_model_tables(tmp_path):
+    """Tables synthesised from the kernel model go through the same fit and dynamic program; the
+    schedule covers the sequence and is not worse than 16 uniform slices under the model."""
+    from terapipe_b200.planner import latency_model as lm
+    from terapipe_b200.planner.kernel_model import predict_iteration_ms
+    out = tmp_path / "dp.json"
+    res = lm.main(settings=[("gpt3-1b", 8, 1, 4, 1, 1, 4)], out=str(out), kernel_model=True)
+    assert len(res) == 1 and res[0]["table"] == "kernel-model"
+    assert sum(res[0]["input_slices"]) == 2048 and sum(res[0]["batch_slices"]) == 8
+    planned = predict_iteration_ms("gpt3-1b", 8, 1, 4, res[0]["batch_slices"], res[0]["input_slices"])
+    uniform = predict_iteration_ms("gpt3-1b", 8, 1, 4, [8], [128] * 16)
+    assert planned <= uniform * 1.001
+    assert abs(res[0]["latency"] * 1e3 - planned) < 0.05 * planned

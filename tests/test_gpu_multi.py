@@ -75,7 +75,7 @@ def test_two_gpu_layouts_match_single_gpu(tp, pp, tp_comm, exchange):
             assert rel < 3e-2, (k, float(rel))
 
 
-@pytest.mark.parametrize("tp,pp,exchange", [(4, 1, False), (2, 2, False), (2, 2, True), (4, 1, True)])
+@pytest.mark.parametrize("tp,pp,exchange", [(4, 1, False), (2, 2, False), (2, 2, True)])
 def test_four_gpu_fused_layouts_match_single_gpu(tp, pp, exchange):
     """Fused GEMM + all-reduce with four-way tensor parallelism (tile owners 0..3) and combined
     with a two-stage pipeline; both forms of the all-reduce."""

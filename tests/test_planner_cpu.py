@@ -123,8 +123,10 @@ def test_kernel_model_matches_recorded_step_and_behaves():
     """Analytic B200 kernel model: calibration point, monotonicity, wave quantisation."""
     from terapipe_b200.planner.kernel_model import B200KernelModel, predict_iteration_ms
     km = B200KernelModel()
-    # measured on one B200: GPT3-1B shape, batch 8, 16 uniform slices, 198.0 ms per iteration
-    assert abs(predict_iteration_ms("gpt3-1b", 8, 1, 1, [8], [128] * 16, km) - 198.0) < 0.1 * 198.0
+    # measured on one B200, GPT3-1B shape, batch 8: 16 / 8 / 4 uniform slices take
+    # 198.0 / 175.1 / 164.9 ms per iteration
+    for n, ms in ((16, 198.0), (8, 175.1), (4, 164.9)):
+        assert abs(predict_iteration_ms("gpt3-1b", 8, 1, 1, [8], [2048 // n] * n, km) - ms) < 0.05 * ms
     f0, b0 = km.layer_slice_us(2048, 16, 2048, 1, 8, 128, 0)
     f1, b1 = km.layer_slice_us(2048, 16, 2048, 1, 8, 128, 1920)
     assert f1 > f0 and abs(b1 - b0) < 0.3 * b0   # forward grows with the context; dK/dV + dQ trade off

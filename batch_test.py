@@ -11,6 +11,7 @@ from itertools import product
 
 from terapipe_b200.planner.memory_model import engine_memory_per_gpu
 from terapipe_b200.runtime import cli
+from terapipe_b200.runtime.cli import parse_comma_delimited_arg  # noqa: F401
 
 TODO_FILE = "experiments_remaining.json"
 

@@ -6,5 +6,7 @@ from terapipe_b200.planner.latency_model import (SCAN_GRID, STEP_GAP, SingleLaye
                                                  analysis_model, cli, evaluate_split,
                                                  fit_single_layer_model, main, parse_json, planning)
 
+from terapipe_b200.planner.latency_model import B200_SETTINGS as inputs  # noqa: E402,F401  settings list
+
 if __name__ == "__main__":
     cli()

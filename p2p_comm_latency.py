@@ -50,6 +50,41 @@ def measure(n_elems, rank, dtype=torch.float16):
     return float(np.mean(times)), float(np.std(times))
 
 
+def p2p_communication_latency(payload_size, group=None):
+    """(mean, std) one-way latency in seconds of a ``payload_size``-element fp16 message between
+    ranks 0 and 1 (name of the reference tool's measurement, p2p_comm_latency.py:14-32)."""
+    return measure(payload_size, dist.get_rank(group) if group is not None else dist.get_rank())
+
+
+def benchmark_p2p_communication(mpi_comm, rank, model_name, size_gap=32, batch_size=None,
+                                out_dir="performance_model_data"):
+    """Measure the stage-to-stage link for every message size of ``model_name`` and write
+    ``<model>.communication_latency.json`` (sizes in tokens).  ``mpi_comm`` and ``size_gap`` are
+    accepted for compatibility with the reference signature and not used: ranks come from
+    ``torch.distributed`` and the sizes from :func:`token_sizes`."""
+    _, hidden, seq_len, _ = MODEL_CONFIGS[model_name]
+    batch = batch_size or BATCH_CONFIGS.get(model_name, 8)
+    sizes = token_sizes(seq_len * batch)
+    means, stds = [], []
+    for tokens in sizes:
+        if rank < 2:
+            m, s = measure(tokens * hidden, rank)
+            means.append(m)
+            stds.append(s)
+        dist.barrier()
+    result = {"tensor_sizes": sizes, "mean": means, "std": stds}
+    if rank == 0:
+        os.makedirs(out_dir, exist_ok=True)
+        with open(os.path.join(out_dir, f"{model_name}.communication_latency.json"), "w") as f:
+            json.dump(result, f)
+    return result
+
+
+def get_local_ip_address():
+    """Single-machine launches rendezvous on the loopback address."""
+    return "127.0.0.1"
+
+
 def main():
     parser = argparse.ArgumentParser(description="stage-to-stage link latency")
     cli.add_rank_arguments(parser)
@@ -59,21 +94,11 @@ def main():
     args = parser.parse_args()
     cli.resolve_ranks(args)
     init_distributed(f"tcp://{args.ip_address}:{args.port}", args.world_size, args.rank, args.local_rank)
-    _, hidden, seq_len, _ = MODEL_CONFIGS[args.model]
-    batch = args.batch_size or BATCH_CONFIGS.get(args.model, 8)
-    sizes = token_sizes(seq_len * batch)
-    means, stds = [], []
-    for tokens in sizes:
-        if args.rank < 2:
-            m, s = measure(tokens * hidden, args.rank)
-            means.append(m)
-            stds.append(s)
-        dist.barrier()
+    res = benchmark_p2p_communication(None, args.rank, args.model, batch_size=args.batch_size,
+                                      out_dir=args.out_dir)
     if args.rank == 0:
-        os.makedirs(args.out_dir, exist_ok=True)
-        with open(os.path.join(args.out_dir, f"{args.model}.communication_latency.json"), "w") as f:
-            json.dump({"tensor_sizes": sizes, "mean": means, "std": stds}, f)
-        print("tokens, latency_us:", [(t, round(m * 1e6, 1)) for t, m in zip(sizes, means)][-4:], flush=True)
+        print("tokens, latency_us:",
+              [(t, round(m * 1e6, 1)) for t, m in zip(res["tensor_sizes"], res["mean"])][-4:], flush=True)
     dist.destroy_process_group()
 
 

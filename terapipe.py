@@ -23,6 +23,14 @@ from terapipe_b200.runtime.runner import NCCLTransformerRunner, init_distributed
 from terapipe_b200.utils import uniform_slice
 
 
+LOSS_SCALE_FACTOR = 128.0
+
+
+def loss_func(y):
+    """Training loss of the drivers: the mean of all output elements (terapipe.py:48-49)."""
+    return torch.mean(y)
+
+
 def initialize_distributed_env(distributed_init_method, rank, local_rank, world_size,
                                model_parallel_size, pipeline_parallel_size):
     init_distributed(distributed_init_method, world_size, rank, local_rank)
@@ -74,6 +82,86 @@ class TeraPipe(nn.Module):
         return _PipelineFunction.apply(self, inputs, self.pipeline.params[0])
 
 
+class TeraPipeBackwardPassHook(torch.autograd.Function):
+    """Identity on ``y`` whose backward replays the token slices in reverse order
+    (reference API, terapipe.py:154-214).  For user-written sliced forwards:
+
+    * ``outputs[i, j]`` is the output of batch slice ``i``, token slice ``j`` (attached to its
+      own autograd graph);
+    * ``cache_inputs[i, j]`` are the detached, grad-requiring cache tensors that slice ``j``
+      read, ``cache_outputs[i, j]`` the cache tensors it produced for slice ``j + 1``.
+
+    Backward walks ``j`` from last to first: slice ``j`` is differentiated with the gradient of
+    its output plus the cache gradients that slice ``j + 1`` left in ``cache_inputs[i, j + 1]``."""
+
+    @staticmethod
+    def forward(ctx, y, outputs, cache_inputs, cache_outputs, batch_slices, seq_slices, batch_dim,
+                sequence_dim, cat_outputs):
+        ctx.state = (outputs, cache_inputs, cache_outputs, list(batch_slices), list(seq_slices),
+                     batch_dim, sequence_dim, cat_outputs)
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_y):
+        from terapipe_b200.models import grid_slice_batch_and_sequence
+        outputs, cache_in, cache_out, batch_slices, seq_slices, bdim, sdim, cat = ctx.state
+        ctx.state = None
+        nb, ns = len(batch_slices), len(seq_slices)
+        grads = (grid_slice_batch_and_sequence(grad_y, batch_slices=batch_slices, seq_slices=seq_slices,
+                                               batch_dim=bdim, sequence_dim=sdim, requires_grad=False)
+                 if cat else None)
+        for i in reversed(range(nb)):
+            from_next = []
+            for j in reversed(range(ns)):
+                dy = grads[i, j] if cat else torch.empty_like(outputs[i, j])
+                produced = list(cache_out[i, j]) if j < ns - 1 else []
+                torch.autograd.backward([outputs[i, j]] + produced, [dy] + from_next)
+                from_next = [t.grad for t in cache_in[i, j]]
+        return (None,) * 9
+
+
+def terapipe_backward_hook(outputs, cache_inputs, cache_outputs, batch_slices, seq_slices,
+                           batch_dim=1, sequence_dim=0, cat_outputs=False):
+    """Tensor whose ``backward()`` drives :class:`TeraPipeBackwardPassHook`: the concatenated
+    slice outputs when ``cat_outputs`` (take a loss of it), otherwise a scalar placeholder (for
+    stages whose slice gradients arrive through their own receive operators)."""
+    with torch.no_grad():
+        if cat_outputs:
+            y = torch.cat([torch.cat(list(row), dim=sequence_dim) for row in outputs], dim=batch_dim)
+        else:
+            y = torch.tensor(0.0)
+    y.requires_grad_()
+    return TeraPipeBackwardPassHook.apply(y, outputs, cache_inputs, cache_outputs, batch_slices,
+                                          seq_slices, batch_dim, sequence_dim, cat_outputs)
+
+
+def initialize_model(args):
+    """(config, layers, pipelined_layers) of this rank's stage from driver arguments
+    (terapipe.py:274-288); ``config.n_layers`` is the stage's share of ``n_total_layers``."""
+    config = TransformerConfig.from_predefined_model(args.model, n_devices=getattr(args, "world_size", 1),
+                                                     batch_size=args.batch_size,
+                                                     n_layers=getattr(args, "n_layers", None))
+    pipelined_layers = TeraPipe(config, uniform_slice(config.batch_size, args.n_batch_slices),
+                                uniform_slice(config.seq_len, args.n_input_slices),
+                                mixed_precision=getattr(args, "mixed_precision", False))
+    config.n_total_layers = config.n_layers
+    config.n_layers = len(mpu.get_topology().layers_of_stage(
+        config.n_total_layers, mpu.get_pipeline_parallel_group_rank()))
+    return config, pipelined_layers.layers, pipelined_layers
+
+
+def verify_one_step(args):
+    """``--verify save|load`` of the drivers (terapipe.py:368-423): write, or check against, the
+    files ``input.pt``, ``model.ckpt`` and ``model.grad.ckpt`` in ``args.verify_path``."""
+    use_b200 = torch.cuda.is_available() and getattr(args, "mixed_precision", False)
+    return verify.verify_one_step(
+        args.verify_path, args.verify, model=args.model, n_layers=getattr(args, "n_layers", None),
+        batch_size=args.batch_size, tp=args.model_parallel_size, pp=args.pipeline_parallel_size,
+        n_batch_slices=args.n_batch_slices, n_input_slices=args.n_input_slices,
+        device="cuda" if torch.cuda.is_available() else "cpu",
+        engine="b200" if use_b200 else "portable")
+
+
 def measure_iteration_time(args, n_warmup_steps=2):
     config = TransformerConfig.from_predefined_model(args.model, n_devices=args.world_size,
                                                      batch_size=args.batch_size,
@@ -111,13 +199,7 @@ def main():
         if args.world_size > 1 or torch.cuda.is_available():
             init_distributed(f"tcp://{args.ip_address}:{args.port}", args.world_size, args.rank,
                              args.local_rank)
-        use_b200 = torch.cuda.is_available() and args.mixed_precision
-        out = verify.verify_one_step(
-            args.verify_path, args.verify, model=args.model, n_layers=args.n_layers,
-            batch_size=args.batch_size, tp=args.model_parallel_size, pp=args.pipeline_parallel_size,
-            n_batch_slices=args.n_batch_slices, n_input_slices=args.n_input_slices,
-            device="cuda" if torch.cuda.is_available() else "cpu",
-            engine="b200" if use_b200 else "portable")
+        out = verify_one_step(args)
         print("rank", args.rank, "verify", args.verify, out, flush=True)
     else:
         mean, std = measure_iteration_time(args)

@@ -27,6 +27,16 @@ from terapipe_b200.runtime.runner import init_distributed
 from terapipe_b200 import parallel as mpu
 
 
+def parse_json(r):
+    """Table keys ``"b_s_c"`` -> ``(b, s, c)`` (terapipe_latency_model.py:103-108)."""
+    return {tuple(int(v) for v in k.split("_")): val for k, val in r.items()}
+
+
+def format_json(r):
+    """Inverse of :func:`parse_json` (terapipe_latency_model.py:111-116)."""
+    return {"_".join(str(v) for v in k): val for k, val in r.items()}
+
+
 class TerapipeLatencyModel:
     """One layer, one slice: the slice of ``seqlen`` tokens attends to ``ctx`` cached rows."""
 

@@ -15,6 +15,7 @@ import torch
 from terapipe_b200.models import MODEL_CONFIGS, TransformerConfig
 from terapipe_b200.planner.memory_model import engine_memory_per_gpu
 from terapipe_b200.runtime import cli
+from terapipe_b200.runtime.cli import parse_comma_delimited_arg  # noqa: F401
 from terapipe_b200.runtime.runner import (LOSS_SCALE_FACTOR, NCCLTransformer,  # noqa: F401
                                           NCCLTransformerRunner)
 from terapipe_b200.utils import TimeoutError, uniform_slice

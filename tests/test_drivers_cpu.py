@@ -69,3 +69,33 @@ def test_planner_scripts_run(tmp_path):
     out = subprocess.run([sys.executable, os.path.join(ROOT, "memory_model.py")], env=_env(),
                          capture_output=True, text=True, timeout=120, check=True)
     assert out.stdout.startswith("11.48")
+
+
+def test_driver_modules_keep_the_reference_public_names():
+    """Scripts that import helpers from the drivers keep working after a switch."""
+    import importlib
+    sys.path.insert(0, ROOT)
+    wanted = {
+        "terapipe": ["LOSS_SCALE_FACTOR", "loss_func", "initialize_distributed_env", "TransformerLayers",
+                     "PipelineSendOperator", "PipelineRecvOperator", "pipeline_send", "pipeline_recv",
+                     "TeraPipeBackwardPassHook", "terapipe_backward_hook", "TeraPipe", "initialize_model",
+                     "measure_iteration_time", "slice_state_dict", "verify_one_step", "main"],
+        "test_transformer_terapipe": ["NCCLTransformer", "NCCLTransformerRunner", "parse_comma_delimited_arg",
+                                      "main", "LOSS_SCALE_FACTOR"],
+        "terapipe_latency_model": ["TerapipeLatencyModel", "parse_json", "format_json", "main"],
+        "p2p_comm_latency": ["p2p_communication_latency", "benchmark_p2p_communication",
+                             "get_local_ip_address"],
+        "latency_model": ["SCAN_GRID", "STEP_GAP", "SingleLayerLatency", "fit_single_layer_model", "planning",
+                          "evaluate_split", "analysis_model", "parse_json", "inputs"],
+        "batch_test": ["parse_comma_delimited_arg", "run_experiment", "main"],
+        "transformer_models": ["NEG_INF", "MODEL_CONFIGS", "BATCH_CONFIGS", "TransformerConfig", "assign_cache_",
+                               "MultiheadLMAttentionWithCache", "TransformerLayer",
+                               "ModelParallelMultiheadLMAttentionWithCache", "ModelParallelTransformerLayer",
+                               "SingleDeviceTransformer", "grid_slice_batch_and_sequence"],
+        "checkpoint": ["CheckpointFunction", "detach_variable", "check_backward_validity"],
+        "utils": ["TimeoutError", "timeout", "suppress_output", "set_random_seed", "mem_report", "uniform_slice"],
+    }
+    for mod, names in wanted.items():
+        m = importlib.import_module(mod)
+        missing = [n for n in names if not hasattr(m, n)]
+        assert not missing, (mod, missing)

@@ -195,3 +195,56 @@ def test_assign_cache_appends_in_place_and_routes_gradients():
     assert torch.equal(cache.data[:, :3], k1.data) and torch.equal(cache.data[:, 3:], k2.data)
     assert torch.allclose(k1.grad, 2 * w[:, :3])      # seen by both consumers
     assert torch.allclose(k2.grad, w[:, 3:])
+
+
+def test_terapipe_backward_hook_replays_slices_in_reverse():
+    """Reference API for user-written sliced forwards (terapipe.py:154-214): a toy layer whose
+    slice j reads a running 'cache' (prefix sums) produced by the earlier slices."""
+    import numpy as np
+    from terapipe import loss_func, terapipe_backward_hook
+    from transformer_models import grid_slice_batch_and_sequence
+    torch.manual_seed(0)
+    L, B, H = 8, 2, 3
+    w = torch.randn(H, H, requires_grad=True)
+    x = torch.randn(L, B, H)
+
+    def whole(xx):  # y_t = (x_t + sum_{s<t} x_s @ w) @ w
+        prefix = torch.cumsum(xx @ w, 0) - xx @ w
+        return (xx + prefix) @ w
+
+    ref_loss = loss_func(whole(x))
+    ref_loss.backward()
+    ref_grad, w.grad = w.grad.clone(), None
+
+    batch_slices, seq_slices = [1, 1], [3, 5]
+    xs = grid_slice_batch_and_sequence(x, batch_slices, seq_slices)
+    shape = (len(batch_slices), len(seq_slices))
+    outputs, cache_in, cache_out = (np.empty(shape, dtype=object) for _ in range(3))
+    for i in range(shape[0]):
+        carry = torch.zeros(xs[i, 0].shape[1], H)          # sum of x_s @ w over earlier slices
+        for j in range(shape[1]):
+            c_in = carry.detach().requires_grad_()
+            proj = xs[i, j] @ w
+            prefix = torch.cumsum(proj, 0) - proj + c_in
+            outputs[i, j] = (xs[i, j] + prefix) @ w
+            carry = c_in + proj.sum(0)
+            cache_in[i, j], cache_out[i, j] = [c_in], [carry]
+    y = terapipe_backward_hook(outputs, cache_in, cache_out, batch_slices, seq_slices, cat_outputs=True)
+    loss = loss_func(y)
+    loss.backward()
+    assert torch.allclose(loss, ref_loss, atol=1e-6)
+    assert torch.allclose(w.grad, ref_grad, atol=1e-5)
+
+
+def test_module_style_helpers_exist_and_build_a_stage():
+    """initialize_model / LOSS_SCALE_FACTOR of the module-style driver (terapipe.py:30,274-288)."""
+    import argparse
+    import terapipe as tpipe
+    assert tpipe.LOSS_SCALE_FACTOR == 128.0
+    args = argparse.Namespace(model="test", batch_size=2, n_batch_slices=1, n_input_slices=4,
+                              mixed_precision=False, world_size=1, n_layers=2)
+    config, layers, pipelined = tpipe.initialize_model(args)
+    assert config.n_total_layers == 2 and config.n_layers == 2
+    y = pipelined(torch.randn(config.seq_len, 2, config.embedding_dim))
+    tpipe.loss_func(y).backward()
+    assert all(p.grad is not None for p in pipelined.parameters())

@@ -129,7 +129,14 @@ def slices_from_args(args, seq_len):
         with open(args.schedule) as f:
             sched = json.load(f)
         if isinstance(sched, list):
-            sched = sched[args.schedule_index]
+            # a dp_results list: the entry planned for this model and layout if there is one,
+            # otherwise the entry at --schedule-index
+            world = int(os.environ.get("WORLD_SIZE", "1"))
+            pp = args.pp if args.pp is not None else world // args.tp
+            match = [e for e in sched if e.get("model_name") == args.model and
+                     e.get("model_parallel_size") == args.tp and e.get("pipeline_length") == pp and
+                     e.get("batch_size") == args.batch]
+            sched = match[0] if match else sched[args.schedule_index]
         return list(sched["batch_slices"]), list(sched["input_slices"])
     return uniform_slice(args.batch, args.batch_slices), uniform_slice(seq_len, args.seq_slices)
 

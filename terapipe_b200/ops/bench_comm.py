@@ -24,8 +24,21 @@ from ..parallel.symm import FusedAllReduceContext
 from . import functional as F
 from .lib import check, cuda_lib
 
-PEAK_TFLOPS = 1638.7      # measured cuBLAS bf16/fp16 burst on this pool (MEASURED_PEAKS.json)
 LINK_GBS = 770.0          # measured peer copy bandwidth per direction
+
+
+def _measured_peak_tflops(default=1638.7):
+    """cuBLAS bf16/fp16 burst throughput measured on this machine pool: read from
+    ``MEASURED_PEAKS.json`` at the repository root when present, else the recorded value."""
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", "..", "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["bf16_tflops"])
+    except (OSError, KeyError, ValueError):
+        return default
+
+
+PEAK_TFLOPS = _measured_peak_tflops()
 
 
 def _max_ms(fn, world, n=20, warm=5):

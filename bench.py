@@ -51,7 +51,8 @@ def parse_args():
     ap.add_argument("--seq-slices", type=int, default=16)
     ap.add_argument("--batch-slices", type=int, default=1)
     ap.add_argument("--schedule", default=None,
-                    help="JSON file with batch_slices / input_slices lists, or a dp_results.json list")
+                    help="JSON file with batch_slices / input_slices lists, a dp_results.json list, "
+                         "or 'auto' (dynamic program over the B200 kernel model)")
     ap.add_argument("--schedule-index", type=int, default=0, help="entry of a dp_results.json list")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--activation", default=None, choices=[None, "gelu", "relu"])
@@ -125,6 +126,14 @@ def dist_env():
 
 def slices_from_args(args, seq_len):
     from terapipe_b200.utils import uniform_slice
+    if args.schedule == "auto":
+        # planned for this model and layout on kernel-model tables (every rank computes the same)
+        from terapipe_b200.planner.latency_model import auto_schedule
+        world = int(os.environ.get("WORLD_SIZE", "1"))
+        pp = args.pp if args.pp is not None else world // args.tp
+        bs, ss, _ = auto_schedule(args.model, args.batch, args.tp, pp, fused_tp=args.tp_comm == "fused",
+                                  n_layers=args.n_layers)
+        return bs, ss
     if args.schedule:
         with open(args.schedule) as f:
             sched = json.load(f)

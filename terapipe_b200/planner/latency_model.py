@@ -387,6 +387,25 @@ def main(settings=None, data_dir="performance_model_data", out="dp_results.json"
     return results
 
 
+def auto_schedule(model_name, batch_size, tp, pp, fused_tp=True, step=64, n_layers=None):
+    """(batch_slices, input_slices, predicted seconds) for one layout, planned on tables
+    synthesised from the analytic B200 kernel model (no measurement files needed)."""
+    import shutil
+    import tempfile
+    from .kernel_model import write_tables
+    table_dir = tempfile.mkdtemp(prefix="terapipe_tables_")
+    try:
+        write_tables(model_name, tp, range(1, batch_size + 1), table_dir, step=step,
+                     fused_tp=fused_tp and tp > 1, total_batch=batch_size)
+        scheme, latency = analysis_model(model_name, batch_size, tp, pp, data_dir=table_dir,
+                                         step_gap=step, n_layers=n_layers, verbose=False)
+    finally:
+        shutil.rmtree(table_dir, ignore_errors=True)
+    if scheme is None:
+        raise RuntimeError(f"no feasible schedule for {model_name} batch {batch_size} tp {tp} pp {pp}")
+    return [b for b, _ in scheme], list(scheme[0][1]), latency
+
+
 def cli(argv=None):
     import argparse
     ap = argparse.ArgumentParser(description="slice schedules from latency tables")

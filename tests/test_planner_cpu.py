@@ -152,3 +152,10 @@ def test_planner_on_kernel_model_tables(tmp_path):
     uniform = predict_iteration_ms("gpt3-1b", 8, 1, 4, [8], [128] * 16)
     assert planned <= uniform * 1.001
     assert abs(res[0]["latency"] * 1e3 - planned) < 0.05 * planned
+
+
+def test_auto_schedule_for_a_layout():
+    from terapipe_b200.planner.latency_model import auto_schedule
+    bs, ss, latency = auto_schedule("gpt3-1b", 8, 1, 8)
+    assert sum(bs) == 8 and sum(ss) == 2048 and 0.02 < latency < 0.06
+    assert len(set(bs)) == 1                      # equal batch slices (the engine's requirement)

@@ -4,7 +4,8 @@
                       batch_slices=[8], seq_slices=[128] * 16)
     loss = trainer.train_step(host_input)      # H2D copy, forward, backward, Adam, loss D2H
 
-``batch_size`` is the batch of ONE data-parallel replica; the data-parallel size is
+``seq_slices="auto"`` plans batch and token slices with the dynamic program over the B200 kernel
+model.  ``batch_size`` is the batch of ONE data-parallel replica; the data-parallel size is
 ``world_size // (tp * pp)``.  Inputs are hidden states ``[seq, batch, hidden]`` (the
 benchmark harness has no embedding, as in the reference, terapipe.py:48-49); the loss is
 the mean of the final output.
@@ -40,6 +41,13 @@ class Trainer:
         self.config = TransformerConfig.from_predefined_model(
             model, n_devices=self.topo.world_size, batch_size=batch_size, n_layers=n_layers,
             activation=activation)
+        if isinstance(seq_slices, str):
+            if seq_slices != "auto":
+                raise ValueError("seq_slices is a list of lengths or 'auto'")
+            # slice schedule from the dynamic program over the B200 kernel model
+            from ..planner.latency_model import auto_schedule
+            batch_slices, seq_slices, _ = auto_schedule(model, batch_size, tp, pp,
+                                                        fused_tp=tp_comm == "fused", n_layers=n_layers)
         batch_slices = list(batch_slices) if batch_slices else [batch_size]
         seq_slices = list(seq_slices) if seq_slices else [self.config.seq_len]
         self.dtype = _DTYPES[dtype]

@@ -56,16 +56,20 @@ def engine_memory_per_gpu(model_name, batch_size, tp=1, pp=1, n_layers=None,
                           keep_gelu_input=True) -> float:
     """Peak GB per GPU of the sm_100a engine for one data-parallel replica.
 
-    Per layer and token it stores the layer input, both LayerNorm outputs, the
-    post-attention residual stream (4H fp16, replicated over TP), and 1/tp of QKV (3H),
-    the attention output (H) and the FFN activation (4H, twice when GeLU keeps its
-    input); plus fp32 dK/dV accumulators (2H/tp) and LSE."""
+    Per layer and token the engine keeps (16-bit unless noted): the layer input, both LayerNorm
+    outputs and the post-attention residual stream (4H, replicated over TP); 1/tp of QKV (3H),
+    of the attention output (H) and of the FFN activation (4H, twice when GeLU keeps its input);
+    the full-length gradient buffers of the layer output and of the post-attention stream (2H)
+    and 1/tp of those of the FFN pre-activation (4H), QKV (3H) and attention output (H);
+    LayerNorm statistics (4 fp32) and log-sum-exp / delta rows (2 fp32 per local head).
+    Parameters cost 18 bytes each (16-bit model, fp32 master, two Adam moments, fp32 gradient)."""
     layers, hidden, seq_len, heads = MODEL_CONFIGS[model_name]
     layers = n_layers if n_layers is not None else layers
     per_stage = -(-layers // pp)
     tokens = batch_size * seq_len
     act_elems = 4 * hidden + (3 * hidden + hidden + (8 if keep_gelu_input else 4) * hidden) / tp
-    act = tokens * act_elems * _F16 + tokens * (2 * hidden / tp) * _F32 + tokens * heads / tp * _F32
+    grad_elems = 2 * hidden + (4 * hidden + 3 * hidden + hidden) / tp
+    act = tokens * (act_elems + grad_elems) * _F16 + tokens * (4 + 2 * heads / tp) * _F32
     params = _layer_params(hidden, tp) * (_F16 + 4 * _F32)
     io = 4 * tokens * hidden * _F16
     return (per_stage * (act + params) + io) / 2 ** 30

@@ -117,6 +117,10 @@ def test_memory_model_golden_values():
     eight = memory_model.engine_memory_per_gpu("gpt3-1b", 8, tp=1, pp=8)
     assert 20 < one < 120 and eight < one / 6
     assert memory_model.engine_memory_per_gpu("gpt3-44b", 4, tp=4, pp=2) < 180
+    # 1B on one GPU: 24 layers x (16384 tokens x 26 H x 2 B of activations and gradient buffers
+    # + 50.4 M parameters x 18 B) is about 60 GB
+    assert abs(one - 59.6) < 1.0
+    assert memory_model.engine_memory_per_gpu("gpt3-175b", 2, tp=8, pp=1, n_layers=8) < 60
 
 
 def test_kernel_model_matches_recorded_step_and_behaves():

@@ -4,8 +4,8 @@
 activations incl. materialised ``[B*heads, L, L]`` fp16 scores and fp32 probabilities,
 and 14 bytes of parameter state per parameter.  ``engine_memory_per_gpu`` models the
 sm_100a engine instead: no score/probability storage (fused attention), fp32 main grads
-(18 bytes per parameter), fp32 dK/dV accumulators, and it takes plain GPU counts, so it
-is defined for 1, 2 or 4 GPUs as well.
+(18 bytes per parameter), full-length 16-bit gradient buffers per layer, and it takes plain
+GPU counts, so it is defined for 1, 2 or 4 GPUs as well.
 """
 from __future__ import annotations
 

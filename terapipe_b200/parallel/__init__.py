@@ -15,7 +15,9 @@ from .initialize import (destroy_model_parallel, get_data_parallel_group,
 from .layers import (ColumnParallelLinear, ParallelEmbedding, RowParallelLinear,
                      VocabParallelEmbedding)
 from .mappings import (copy_to_model_parallel_region, gather_from_model_parallel_region,
-                       reduce_from_model_parallel_region, scatter_to_model_parallel_region)
+                       gather_from_sequence_parallel_region, reduce_from_model_parallel_region,
+                       reduce_scatter_to_sequence_parallel_region, scatter_to_model_parallel_region,
+                       scatter_to_sequence_parallel_region)
 from .random import checkpoint, get_cuda_rng_tracker, model_parallel_cuda_manual_seed
 from .topology import Topology
 from .utils import VocabUtility, divide, ensure_divisibility, split_tensor_along_last_dim

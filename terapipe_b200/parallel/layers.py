@@ -16,7 +16,8 @@ from torch.nn import init
 
 from .initialize import get_model_parallel_rank, get_model_parallel_world_size
 from .mappings import (copy_to_model_parallel_region, gather_from_model_parallel_region,
-                       reduce_from_model_parallel_region, scatter_to_model_parallel_region)
+                       gather_from_sequence_parallel_region, reduce_from_model_parallel_region,
+                       reduce_scatter_to_sequence_parallel_region, scatter_to_model_parallel_region)
 from .utils import VocabUtility, divide
 
 
@@ -93,10 +94,13 @@ class ColumnParallelLinear(nn.Module):
 
     def __init__(self, input_size, output_size, bias=True, gather_output=True,
                  init_method=init.xavier_normal_, stride=1, initialize_locally=False,
-                 keep_master_weight_for_test=False, device="cpu"):
+                 keep_master_weight_for_test=False, device="cpu", sequence_parallel=False):
         super().__init__()
         self.input_size, self.output_size = input_size, output_size
         self.gather_output = gather_output
+        # sequence_parallel: the input holds this rank's chunk of the tokens (dim 0); it is
+        # all-gathered before the product (backward: reduce-scatter of the input gradient)
+        self.sequence_parallel = sequence_parallel
         tp = get_model_parallel_world_size()
         self.output_size_per_partition = divide(output_size, tp)
         self.weight = nn.Parameter(torch.empty(self.output_size_per_partition, input_size))
@@ -114,7 +118,9 @@ class ColumnParallelLinear(nn.Module):
         self.to(device)
 
     def forward(self, x):
-        y = F.linear(copy_to_model_parallel_region(x), self.weight, self.bias)
+        x = gather_from_sequence_parallel_region(x) if self.sequence_parallel \
+            else copy_to_model_parallel_region(x)
+        y = F.linear(x, self.weight, self.bias)
         return gather_from_model_parallel_region(y) if self.gather_output else y
 
 
@@ -125,10 +131,13 @@ class RowParallelLinear(nn.Module):
 
     def __init__(self, input_size, output_size, bias=True, input_is_parallel=False,
                  init_method=init.xavier_normal_, stride=1, initialize_locally=False,
-                 keep_master_weight_for_test=False, device="cpu"):
+                 keep_master_weight_for_test=False, device="cpu", sequence_parallel=False):
         super().__init__()
         self.input_size, self.output_size = input_size, output_size
         self.input_is_parallel = input_is_parallel
+        # sequence_parallel: partial products are reduce-scattered over the tokens (dim 0)
+        # instead of all-reduced; the output is this rank's token chunk
+        self.sequence_parallel = sequence_parallel
         tp = get_model_parallel_world_size()
         self.input_size_per_partition = divide(input_size, tp)
         self.weight = nn.Parameter(torch.empty(output_size, self.input_size_per_partition))
@@ -153,7 +162,8 @@ class RowParallelLinear(nn.Module):
                 torch.cuda.synchronize()
             dist.barrier()
             t0 = time.time()
-        y = reduce_from_model_parallel_region(partial)
+        y = reduce_scatter_to_sequence_parallel_region(partial) if self.sequence_parallel \
+            else reduce_from_model_parallel_region(partial)
         if return_reduce_time:
             if partial.is_cuda:
                 torch.cuda.synchronize()

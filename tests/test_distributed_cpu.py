@@ -164,3 +164,36 @@ def test_surviving_rank_raises_when_peer_dies():
     errors = run_ranks(_rank_dies, 2, timeout_s=20, expect_failure=True)
     assert 1 in errors and "injected failure" in errors[1]
     assert 0 in errors          # the sender's p2p call fails or times out instead of hanging
+
+
+def _rank_sequence_parallel(rank, world):
+    """Column/Row parallel pair on token-sharded activations against the unsharded product."""
+    import torch.nn.functional as F
+    from terapipe_b200 import parallel as mpu
+    mpu.initialize_model_parallel(world, 1, verbose=False)
+    torch.manual_seed(0)
+    col = mpu.ColumnParallelLinear(16, 24, gather_output=False, keep_master_weight_for_test=True,
+                                   sequence_parallel=True)
+    row = mpu.RowParallelLinear(24, 16, input_is_parallel=True, keep_master_weight_for_test=True,
+                                sequence_parallel=True)
+    torch.manual_seed(1)
+    x_full = torch.randn(8, 3, 16)                       # [tokens, batch, hidden], replicated
+    x_full.requires_grad_()
+    x_loc = mpu.scatter_to_sequence_parallel_region(x_full)          # my tokens
+    y_loc = row(torch.relu(col(x_loc)))                              # my tokens of the output
+    y = mpu.gather_from_sequence_parallel_region(y_loc, tensor_parallel_output_grad=False)
+    w = torch.arange(y.numel(), dtype=torch.float32).view_as(y) / y.numel()
+    (y * w).sum().backward()
+    xr = x_full.detach().clone().requires_grad_()
+    ref = F.linear(torch.relu(F.linear(xr, col.master_weight)), row.master_weight)
+    (ref * w).sum().backward()
+    return {"y_err": (y - ref).abs().max().item(), "dx_err": (x_full.grad - xr.grad).abs().max().item(),
+            "loc_tokens": x_loc.shape[0], "y_loc_tokens": y_loc.shape[0]}
+
+
+def test_sequence_parallel_mappings_two_ranks():
+    for r in run_ranks(_rank_sequence_parallel, 2):
+        assert r["loc_tokens"] == 4 and r["y_loc_tokens"] == 4
+        assert r["y_err"] < 1e-5
+        # every rank holds the full input gradient after the backward all-gather of the scatter
+        assert r["dx_err"] < 1e-5

@@ -47,7 +47,7 @@ assign_cache_ = _AssignCache.apply
 
 
 class MultiheadLMAttentionWithCache(nn.Module):
-    def __init__(self, embed_dim, num_heads, bias=True, device="cpu"):
+    def __init__(self, embed_dim, num_heads, bias=True, device="cpu", sequence_parallel=False):
         super().__init__()
         tp = mpu.get_model_parallel_world_size()
         if num_heads % tp or embed_dim % num_heads:
@@ -58,16 +58,21 @@ class MultiheadLMAttentionWithCache(nn.Module):
         self.head_dim = embed_dim // num_heads
         self.scaling = self.head_dim ** -0.5
         self.model_parallel_size = tp
+        # sequence_parallel: input and output hold this rank's chunk of the slice's tokens; the
+        # projections all-gather / reduce-scatter over the tensor-parallel group
         self.in_proj = mpu.ColumnParallelLinear(embed_dim, 3 * embed_dim, bias=bias,
-                                                gather_output=False, device=device)
+                                                gather_output=False, device=device,
+                                                sequence_parallel=sequence_parallel)
         self.out_proj = mpu.RowParallelLinear(embed_dim, embed_dim, bias=bias,
-                                              input_is_parallel=True, device=device)
+                                              input_is_parallel=True, device=device,
+                                              sequence_parallel=sequence_parallel)
 
     # -- building blocks ---------------------------------------------------------
     def project_qkv(self, x):
         """``x [t, b, H]`` -> ``q, k, v`` each ``[b*h, t, d]`` (q already scaled)."""
-        t, b, _ = x.shape
-        qkv = self.in_proj(x).view(t, b * self.num_heads, 3 * self.head_dim).transpose(0, 1)
+        qkv = self.in_proj(x)                      # all tokens of the slice, this rank's heads
+        t, b = qkv.shape[0], qkv.shape[1]
+        qkv = qkv.view(t, b * self.num_heads, 3 * self.head_dim).transpose(0, 1)
         q, k, v = qkv.chunk(3, dim=-1)
         return q * self.scaling, k, v
 
@@ -140,7 +145,7 @@ class TransformerLayer(nn.Module):
     reference's ModelParallelTransformerLayer (transformer_models.py:314-327)."""
 
     def __init__(self, embedding_dim, ffn_embedding_dim, num_attention_heads, device="cpu",
-                 checkpoint_gradients=False, activation="gelu"):
+                 checkpoint_gradients=False, activation="gelu", sequence_parallel=False):
         super().__init__()
         tp = mpu.get_model_parallel_world_size()
         if ffn_embedding_dim % tp:
@@ -148,13 +153,21 @@ class TransformerLayer(nn.Module):
         self.model_parallel_size = tp
         self.checkpoint_gradients = checkpoint_gradients
         self.activation = activation
+        # sequence_parallel: the layer's input and output, both LayerNorms and the residual adds
+        # work on this rank's chunk of the slice's tokens (1/tp of the activation memory and
+        # LayerNorm work); the replicated parameters then receive partial gradients, see
+        # allreduce_sequence_parallel_grads
+        self.sequence_parallel = sequence_parallel and tp > 1
         self.attn_ln = nn.LayerNorm(embedding_dim).to(device)
-        self.attn = MultiheadLMAttentionWithCache(embedding_dim, num_attention_heads, device=device)
+        self.attn = MultiheadLMAttentionWithCache(embedding_dim, num_attention_heads, device=device,
+                                                  sequence_parallel=self.sequence_parallel)
         self.fc_ln = nn.LayerNorm(embedding_dim).to(device)
         self.fc1 = mpu.ColumnParallelLinear(embedding_dim, ffn_embedding_dim,
-                                            gather_output=False, device=device)
+                                            gather_output=False, device=device,
+                                            sequence_parallel=self.sequence_parallel)
         self.fc2 = mpu.RowParallelLinear(ffn_embedding_dim, embedding_dim,
-                                         input_is_parallel=True, device=device)
+                                         input_is_parallel=True, device=device,
+                                         sequence_parallel=self.sequence_parallel)
 
     def _act(self, z):
         return F.gelu(z) if self.activation == "gelu" else F.relu(z)
@@ -171,6 +184,20 @@ class TransformerLayer(nn.Module):
         a, cache = self.attn(self.attn_ln(x), full_cache, cache_len,
                              checkpoint_gradients=self.checkpoint_gradients)
         return self._ffn(x + a), cache
+
+
+    def allreduce_sequence_parallel_grads(self):
+        """With ``sequence_parallel`` every rank sees only its tokens, so the gradients of the
+        parameters that are replicated over the tensor-parallel group (LayerNorm weights and
+        biases, the biases of the row-parallel projections) are partial: sum them."""
+        if not self.sequence_parallel:
+            return
+        import torch.distributed as dist
+        group = mpu.get_model_parallel_group()
+        for p in (*self.attn_ln.parameters(), *self.fc_ln.parameters(), self.attn.out_proj.bias,
+                  self.fc2.bias):
+            if p is not None and p.grad is not None:
+                dist.all_reduce(p.grad, group=group)
 
 
 ModelParallelTransformerLayer = TransformerLayer

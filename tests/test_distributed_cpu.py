@@ -197,3 +197,41 @@ def test_sequence_parallel_mappings_two_ranks():
         assert r["y_err"] < 1e-5
         # every rank holds the full input gradient after the backward all-gather of the scatter
         assert r["dx_err"] < 1e-5
+
+
+def _rank_sequence_parallel_layer(rank, world):
+    """A layer on token-sharded activations (two slices with a KV prefix) against the same layer
+    with replicated activations."""
+    from terapipe_b200 import parallel as mpu
+    from terapipe_b200.models import TransformerLayer
+    mpu.initialize_model_parallel(world, 1, verbose=False)
+    out = {}
+    for sp in (False, True):
+        torch.manual_seed(0)
+        layer = TransformerLayer(32, 128, 4, sequence_parallel=sp)
+        torch.manual_seed(1)
+        x = torch.randn(12, 2, 32)
+        slices = [x[:8].clone().requires_grad_(), x[8:].clone().requires_grad_()]
+        ys, pk, pv = [], None, None
+        for xs in slices:
+            inp = mpu.scatter_to_sequence_parallel_region(xs) if sp else xs
+            y, nk, nv = layer.forward_slice(inp, pk, pv)
+            if sp:
+                y = mpu.gather_from_sequence_parallel_region(y, tensor_parallel_output_grad=False)
+            ys.append(y)
+            pk = nk if pk is None else torch.cat([pk, nk], 1)
+            pv = nv if pv is None else torch.cat([pv, nv], 1)
+        y = torch.cat(ys, 0)
+        (y * torch.linspace(0, 1, y.numel()).view_as(y)).sum().backward()
+        layer.allreduce_sequence_parallel_grads()
+        out[sp] = {"y": y.detach(), "dx": torch.cat([s.grad for s in slices], 0),
+                   "grads": {k: p.grad.clone() for k, p in layer.named_parameters()}}
+    return out
+
+
+def test_sequence_parallel_layer_matches_replicated_layer():
+    for r in run_ranks(_rank_sequence_parallel_layer, 2):
+        assert torch.allclose(r[True]["y"], r[False]["y"], atol=1e-5)
+        assert torch.allclose(r[True]["dx"], r[False]["dx"], atol=1e-5)
+        for k, g in r[False]["grads"].items():
+            assert torch.allclose(r[True]["grads"][k], g, atol=2e-5), k

@@ -37,11 +37,12 @@ class TransformerLayers(nn.Module):
 
     def __init__(self, n_layers, embedding_dim, ffn_embedding_dim, num_attention_heads,
                  mixed_precision=False, device="cpu", checkpoint_gradients=False,
-                 activation="gelu", dtype=torch.float16):
+                 activation="gelu", dtype=torch.float16, sequence_parallel=False):
         super().__init__()
         self.layers = nn.ModuleList([
             TransformerLayer(embedding_dim, ffn_embedding_dim, num_attention_heads, device=device,
-                             checkpoint_gradients=checkpoint_gradients, activation=activation)
+                             checkpoint_gradients=checkpoint_gradients, activation=activation,
+                             sequence_parallel=sequence_parallel)
             for _ in range(n_layers)])
         if mixed_precision:
             self.to(dtype)
@@ -65,7 +66,10 @@ class PortablePipeline:
     def __init__(self, config: TransformerConfig, batch_slices: Sequence[int],
                  seq_slices: Sequence[int], mixed_precision=False, checkpoint_gradients=False,
                  device: Optional[str] = None, dtype=torch.float16, seed: int = 0, lr=1e-10,
-                 loss_scale: float = LOSS_SCALE_FACTOR):
+                 loss_scale: float = LOSS_SCALE_FACTOR, sequence_parallel: bool = False):
+        """``sequence_parallel``: between the GEMM pairs every tensor-parallel rank keeps only
+        its chunk of a slice's tokens (LayerNorm, residual stream, and what travels between
+        pipeline stages: 1/tp of the bytes per link); slice lengths must divide by tp."""
         self.config = config
         self.batch_slices, self.seq_slices = list(batch_slices), list(seq_slices)
         self.mixed_precision = mixed_precision
@@ -73,6 +77,9 @@ class PortablePipeline:
         self.loss_scale = loss_scale if mixed_precision else 1.0
         self.device = device or ("cuda" if torch.cuda.is_available() else "cpu")
         self.topo = mpu.get_topology()
+        self.sequence_parallel = bool(sequence_parallel) and self.topo.tp > 1
+        if self.sequence_parallel and any(t % self.topo.tp for t in self.seq_slices):
+            raise ValueError("sequence_parallel needs slice lengths divisible by the tensor-parallel size")
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self.dp_idx, self.pp_idx, self.tp_idx = self.topo.coords(self.rank)
         self.is_first, self.is_last = self.pp_idx == 0, self.pp_idx == self.topo.pp - 1
@@ -86,8 +93,14 @@ class PortablePipeline:
         self.layers = TransformerLayers(
             len(self.layer_ids), config.embedding_dim, config.ffn_embedding_dim,
             config.num_attention_heads, mixed_precision, self.device, checkpoint_gradients,
-            config.activation, dtype)
+            config.activation, dtype, sequence_parallel=self.sequence_parallel)
         self.params: List[torch.Tensor] = list(self.layers.parameters())
+        # parameters replicated over the TP group whose gradients are partial (per token chunk)
+        # under sequence parallelism: LayerNorm weights / biases, biases of row-parallel layers
+        self._partial_grad_ids = [i for i, (n, _) in enumerate(self.layers.named_parameters())
+                                  if n.endswith(("attn_ln.weight", "attn_ln.bias", "fc_ln.weight",
+                                                 "fc_ln.bias", "out_proj.bias", "fc2.bias"))] \
+            if self.sequence_parallel else []
         self.main_grads = [torch.zeros_like(p, dtype=torch.float32) for p in self.params]
         if mixed_precision:
             self.master = [p.detach().clone().float().requires_grad_() for p in self.params]
@@ -127,10 +140,13 @@ class PortablePipeline:
             cache = self.layers.create_cache(b, cfg.seq_len)
             c = 0
             for si, t in enumerate(self.seq_slices):
+                t_loc = t // self.topo.tp if self.sequence_parallel else t
                 if self.is_first:
                     x = grid[bi, si]
+                    if self.sequence_parallel:  # my chunk of the slice's tokens
+                        x = x[self.tp_idx * t_loc:(self.tp_idx + 1) * t_loc].contiguous()
                 else:
-                    x = torch.empty(t, b, cfg.embedding_dim, device=self.device, dtype=self.low_dtype)
+                    x = torch.empty(t_loc, b, cfg.embedding_dim, device=self.device, dtype=self.low_dtype)
                     p2p.recv_forward(x)
                 x.requires_grad_(True)
                 h, prefixes, news = x, [], []
@@ -150,6 +166,8 @@ class PortablePipeline:
                     p2p.send_forward(h.detach())
                 c += t
         if self.is_last:
+            if self.sequence_parallel:  # every rank summed its token chunks only
+                dist.all_reduce(loss_sum, group=mpu.get_model_parallel_group())
             self.last_loss = float(loss_sum) / (cfg.seq_len * cfg.batch_size * cfg.embedding_dim)
         return rec
 
@@ -171,7 +189,8 @@ class PortablePipeline:
                 x, y, prefixes, news, c, t, _ = rec[bi, si]
                 if self.is_last and output_grad is not None:
                     boff = sum(self.batch_slices[:bi])
-                    dy = output_grad[c:c + t, boff:boff + b].to(y.dtype).contiguous()
+                    r0 = c + (self.tp_idx * (t // self.topo.tp) if self.sequence_parallel else 0)
+                    dy = output_grad[r0:r0 + y.shape[0], boff:boff + b].to(y.dtype).contiguous()
                 elif self.is_last:
                     dy = torch.full_like(y, self.loss_scale / numel)
                 else:
@@ -200,6 +219,14 @@ class PortablePipeline:
 
     # ---- gradient reduction and update ---------------------------------------------
     def allreduce_params(self):
+        if self._partial_grad_ids:
+            flat = torch.cat([self.main_grads[i].reshape(-1) for i in self._partial_grad_ids])
+            dist.all_reduce(flat, group=mpu.get_model_parallel_group())
+            off = 0
+            for i in self._partial_grad_ids:
+                g = self.main_grads[i]
+                g.copy_(flat[off:off + g.numel()].view_as(g))
+                off += g.numel()
         dp = self.topo.dp
         if dp == 1:
             return

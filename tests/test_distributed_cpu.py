@@ -22,13 +22,13 @@ def _single_rank_reference(n_layers=4, batch=2):
     return p.last_loss, p.named_grads(), x
 
 
-def _rank_pipeline(rank, world, tp, pp, batch_slices, seq_slices):
+def _rank_pipeline(rank, world, tp, pp, batch_slices, seq_slices, sequence_parallel=False):
     from terapipe_b200 import parallel as mpu
     from terapipe_b200.runtime.portable import PortablePipeline
     mpu.initialize_model_parallel(tp, pp, verbose=False)
     topo = mpu.get_topology()
     cfg = _cfg()
-    p = PortablePipeline(cfg, batch_slices, seq_slices, device="cpu")
+    p = PortablePipeline(cfg, batch_slices, seq_slices, device="cpu", sequence_parallel=sequence_parallel)
     x = p.create_inputs(0) if p.is_first else None
     p.compute_grads(x)
     out = {"coords": topo.coords(rank), "loss": p.last_loss, "grads": p.named_grads(),
@@ -55,6 +55,21 @@ def test_parallel_layouts_match_single_rank(tp, pp, world):
         if world // (tp * pp) == 1:   # with DP replicas the inputs differ per replica
             for k, g in want.items():
                 assert torch.allclose(res["grads"][k], g, atol=2e-6, rtol=1e-4), (rank, k)
+
+
+@pytest.mark.parametrize("tp,pp,world", [(2, 1, 2), (2, 2, 4)])
+def test_sequence_parallel_pipeline_matches_single_rank(tp, pp, world):
+    """Token-sharded activations between the GEMM pairs and on the pipeline links."""
+    from terapipe_b200.models import slice_state_dict
+    loss, full_grads, _ = _single_rank_reference()
+    results = run_ranks(_rank_pipeline, world, tp, pp, [1, 1], [8, 24, 16, 16], True)
+    for rank, res in enumerate(results):
+        _, pp_idx, tp_idx = res["coords"]
+        if pp_idx == pp - 1:
+            assert abs(res["loss"] - loss) < 1e-5
+        want = slice_state_dict(4, full_grads, tp=tp, tp_rank=tp_idx, pp=pp, pp_rank=pp_idx)
+        for k, g in want.items():
+            assert torch.allclose(res["grads"][k], g, atol=2e-6, rtol=1e-4), (rank, k)
 
 
 def _rank_dp(rank, world):

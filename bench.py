@@ -60,6 +60,8 @@ def parse_args():
     ap.add_argument("--dp-comm", default="nccl", choices=["nccl", "fused"])
     ap.add_argument("--no-graph", action="store_true", help="never capture the step in a CUDA graph")
     ap.add_argument("--graph", action="store_true", help="capture even when the stage communicates")
+    ap.add_argument("--launch-plan", action="store_true",
+                    help="stages that run eagerly replay recorded launch lists (see runtime/launch_plan.py)")
     ap.add_argument("--no-e2e", action="store_true")
     return ap.parse_args()
 
@@ -196,6 +198,8 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=device)
     pp = args.pp if args.pp is not None else world // args.tp
+    if args.launch_plan:
+        os.environ["TERAPIPE_LAUNCH_PLAN"] = "1"
     seq_len = MODEL_CONFIGS[args.model][2]
     batch_slices, seq_slices = slices_from_args(args, seq_len)
     trainer = Trainer(args.model, batch_size=args.batch, tp=args.tp, pp=pp,
@@ -255,7 +259,8 @@ def run_ours(args):
                        "seq_len": cfg.seq_len, "parallelism": f"pp{pp}xtp{args.tp}xdp{trainer.topo.dp}",
                        "batch_slices": batch_slices, "seq_slices": seq_slices,
                        "activation": cfg.activation, "mixed_precision": "fp32 master + Adam, loss scale 128",
-                       "cuda_graph": bool(trainer.engine.use_graph), "tp_comm": trainer.engine.tp_comm, "dp_comm": trainer.engine.dp_comm,
+                       "cuda_graph": bool(trainer.engine.use_graph),
+                       "launch_plan": trainer.engine._plan is not None, "tp_comm": trainer.engine.tp_comm, "dp_comm": trainer.engine.dp_comm,
                        "l2": "per-step working set (weights + activations, several GB) far exceeds the 126 MB L2"},
             "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
         }

@@ -85,7 +85,7 @@ class StageEngine:
     def __init__(self, config: TransformerConfig, batch_slices: Sequence[int],
                  seq_slices: Sequence[int], dtype=torch.float16, loss_scale=LOSS_SCALE_FACTOR,
                  lr=1e-10, seed=0, init="device", use_graph: Optional[bool] = None,
-                 tp_comm="nccl", dp_comm="nccl", device=None):
+                 tp_comm="nccl", dp_comm="nccl", device=None, launch_plan: Optional[bool] = None):
         assert torch.cuda.is_available(), "StageEngine needs a CUDA device (sm_100a)"
         self.cfg = config
         self.batch_slices, self.seq_slices = list(batch_slices), list(seq_slices)
@@ -151,6 +151,17 @@ class StageEngine:
                      and (self.tp == 1 or self.tp_comm == "fused"))
         self.use_graph = nccl_free if use_graph is None else (bool(use_graph) and nccl_free)
         self._graph = None
+        # Recorded launch plans (runtime/launch_plan.py) for stages that cannot use a CUDA graph:
+        # the launches of every slice segment are recorded once and replayed.  Off unless asked
+        # for (argument, or TERAPIPE_LAUNCH_PLAN=1); segments must hold this library's launches
+        # only, so a stage whose slices all-reduce through NCCL keeps deriving its launches.
+        want_plan = (os.environ.get("TERAPIPE_LAUNCH_PLAN", "0") == "1") if launch_plan is None \
+            else bool(launch_plan)
+        self._plan = None
+        if want_plan and not self.use_graph and (self.tp == 1 or self.tp_comm == "fused"):
+            from .launch_plan import RecordingLibrary, SegmentCache
+            self.lib = RecordingLibrary(self.lib)
+            self._plan = SegmentCache(self.lib, on_error=lambda rc, name: F.check(rc, name))
         self.timeline = None   # set to a utils.trace.SliceTimeline to record per-slice device times
         self.step_count = 0
         self._streams_ready = False
@@ -479,6 +490,15 @@ class StageEngine:
     def _refresh_handles(self):
         self._stream = torch.cuda.current_stream().cuda_stream
         self._status_ptr = self.status.data_ptr()
+        if self._plan is not None:
+            self._plan.validate((self._stream, self._status_ptr))
+
+    def _segment(self, key, fn, *args):
+        """Run one launch-only part of the step: directly, or through the recorded plan."""
+        if self._plan is None:
+            fn(*args)
+        else:
+            self._plan.run(key, fn, *args)
 
     def _setup_streams(self):
         if self._streams_ready:
@@ -527,9 +547,9 @@ class StageEngine:
                     recvs[(bi, si)].wait()
                 if self.timeline is not None:
                     with self.timeline.slice("forward", bi, si):
-                        self._forward_slice(sl)
+                        self._segment(("forward", bi, si), self._forward_slice, sl)
                 else:
-                    self._forward_slice(sl)
+                    self._segment(("forward", bi, si), self._forward_slice, sl)
                 if pipelined and not self.is_last:
                     _, b, _, t, r0 = sl
                     sends.append(dist.isend(self.X[self.n_layers][r0:r0 + t * b],
@@ -544,14 +564,14 @@ class StageEngine:
                     recvs[(bi, si)].wait()
                 if self.timeline is not None:
                     with self.timeline.slice("backward", bi, si):
-                        self._backward_slice(sl)
+                        self._segment(("backward", bi, si), self._backward_slice, sl)
                 else:
-                    self._backward_slice(sl)
+                    self._segment(("backward", bi, si), self._backward_slice, sl)
                 if pipelined and not self.is_first:
                     _, b, _, t, r0 = sl
                     sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank(),
                                             group=self._link_prev))
-        self._weight_grads()
+        self._segment(("weight_grads",), self._weight_grads)
         for w in sends:
             w.wait()
 

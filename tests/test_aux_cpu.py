@@ -111,3 +111,49 @@ def test_checkpoint_roundtrip_and_reshard(tmp_path):
         for name in PARAM_ORDER:
             assert torch.equal(e.param(0, name, e.master), full[f"layers.layers.{s}.{name}"]), name
             assert torch.equal(e.param(0, name, e.exp_avg), 2 * full[f"layers.layers.{s}.{name}"])
+
+
+def test_launch_plan_records_once_and_replays():
+    """Recorded launch plans of the engine (host logic only; a fake kernel library)."""
+    from terapipe_b200.runtime.launch_plan import RecordingLibrary, SegmentCache
+
+    class FakeLib:
+        def __init__(self):
+            self.log = []
+            self.fail_next = False
+
+        def tp_a(self, x, y):
+            self.log.append(("a", x, y))
+            return 0
+
+        def tp_b(self, x):
+            self.log.append(("b", x))
+            rc, self.fail_next = (-3 if self.fail_next else 0), False
+            return rc
+
+    fake = FakeLib()
+    lib = RecordingLibrary(fake)
+    cache = SegmentCache(lib)
+    derived = []
+
+    def segment(i):            # argument derivation happens only while recording
+        derived.append(i)
+        lib.tp_a(i, 10 * i)
+        lib.tp_b(i + 1)
+
+    cache.validate("stream0")
+    for _ in range(3):
+        cache.run(("fwd", 0), segment, 1)
+        cache.run(("fwd", 1), segment, 2)
+    assert derived == [1, 2]                                   # recorded once per key
+    assert fake.log == [("a", 1, 10), ("b", 2), ("a", 2, 20), ("b", 3)] * 3
+    assert cache.replayed == 8
+    lib.tp_a(7, 7)                                             # calls outside a segment just run
+    assert fake.log[-1] == ("a", 7, 7) and len(cache.segments) == 2
+    cache.validate("stream1")                                  # new token: recordings dropped
+    assert not cache.segments
+    fake.fail_next = True
+    cache.run(("fwd", 0), segment, 1)                          # a failing launch is not cached
+    assert ("fwd", 0) not in cache.segments
+    cache.run(("fwd", 0), segment, 1)
+    assert ("fwd", 0) in cache.segments

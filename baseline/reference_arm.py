@@ -76,96 +76,114 @@ def _cat_out_across_devices(torch) -> None:
     torch.cat = cat
 
 
-def _unavailable(why: str) -> None:
-    print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+class ReferenceArm:
+    """The unmodified reference behind the block interface of bench.py: ``setup`` (imports and
+    process group), ``measure`` (one model / layout / slice schedule through the reference's own
+    ``NCCLTransformerRunner.step``), ``tp_block`` and ``finish``."""
+    name = "reference"
 
+    def __init__(self, args, timed_steps, ClockSampler, slices_for, config_dict, l2_note):
+        self.args = args
+        self.timed_steps, self.ClockSampler = timed_steps, ClockSampler
+        self.slices_for, self.config_dict, self.l2_note = slices_for, config_dict, l2_note
 
-def run(args, dist_env, timed_steps, ClockSampler, slices_from_args) -> None:
-    rank, world, local = dist_env()
-    if not os.path.isfile(os.path.join(REF, "test_transformer_terapipe.py")):
-        if rank == 0:
-            _unavailable("baseline/_ref is missing: the reference has not been installed")
-        return
-    # the reference's modules (mpu, utils, transformer_models, ...) must win over anything else
-    for p in (os.path.join(HERE, "apex_stub"), REF):
-        sys.path.insert(0, p)
-    for name in ("mpu", "utils", "transformer_models", "checkpoint", "memory_model"):
-        sys.modules.pop(name, None)
-    try:
+    def setup(self, rank, world, local):
+        """Returns None when ready, else the reason the reference cannot run here."""
+        self.rank, self.world, self.local = rank, world, local
+        if not os.path.isfile(os.path.join(REF, "test_transformer_terapipe.py")):
+            return "baseline/_ref is missing: the reference has not been installed"
+        # the reference's modules (mpu, utils, transformer_models, ...) must win over anything else
+        for p in (os.path.join(HERE, "apex_stub"), REF):
+            sys.path.insert(0, p)
+        for name in ("mpu", "utils", "transformer_models", "checkpoint", "memory_model"):
+            sys.modules.pop(name, None)
+        try:
+            import torch
+            import torch.distributed as dist
+            if not torch.cuda.is_available():
+                return "no CUDA device"
+            torch.cuda.set_device(local)
+            self.device = torch.device("cuda", local)
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            os.environ.setdefault("MASTER_PORT", "29533")
+            os.environ.setdefault("RANK", str(rank))
+            os.environ.setdefault("WORLD_SIZE", str(world))
+            with contextlib.redirect_stdout(sys.stderr):
+                dist.init_process_group("nccl", device_id=self.device)
+                import test_transformer_terapipe as ref
+                ref.np = _NumpyCompat(ref.np)
+                _autograd_grad_returns_list(torch)
+                _cat_out_across_devices(torch)
+                assert os.path.dirname(os.path.abspath(ref.__file__)) == REF
+            self.ref = ref
+        except Exception as e:  # noqa: BLE001
+            return f"reference set-up failed: {type(e).__name__}: {str(e)[:200]}"
+        return None
+
+    def measure(self, spec, steps, warmup, main=False, **_):
+        import gc
         import torch
-        import torch.distributed as dist
-        if not torch.cuda.is_available():
-            if rank == 0:
-                _unavailable("no CUDA device")
-            return
-        torch.cuda.set_device(local)
-        device = torch.device("cuda", local)
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ.setdefault("MASTER_PORT", "29533")
-        os.environ.setdefault("RANK", str(rank))
-        os.environ.setdefault("WORLD_SIZE", str(world))
         with contextlib.redirect_stdout(sys.stderr):
-            dist.init_process_group("nccl", device_id=device)
-            import test_transformer_terapipe as ref
-            ref.np = _NumpyCompat(ref.np)
-            _autograd_grad_returns_list(torch)
-            _cat_out_across_devices(torch)
             from transformer_models import MODEL_CONFIGS, TransformerConfig
-            assert os.path.dirname(os.path.abspath(ref.__file__)) == REF
-            pp = args.pp if args.pp is not None else world // args.tp
-            dp = world // (args.tp * pp)
-            config = TransformerConfig.from_predefined_model(args.model, n_devices=world,
-                                                             batch_size=args.batch)
-            if args.n_layers is not None:
-                config.n_layers = args.n_layers
-            seq_len = MODEL_CONFIGS[args.model][2]
-
-            from utils import uniform_slice
-            if args.schedule:
-                with open(args.schedule) as f:
-                    sched = json.load(f)
-                if isinstance(sched, list):
-                    sched = sched[getattr(args, "schedule_index", 0)]
-                batch_slices, seq_slices = list(sched["batch_slices"]), list(sched["input_slices"])
-            else:
-                batch_slices = uniform_slice(args.batch, args.batch_slices)
-                seq_slices = uniform_slice(seq_len, args.seq_slices)
-            runner = ref.NCCLTransformerRunner(
-                config, batch_slices, seq_slices, "env://", world, dp, args.tp, pp, rank, local,
-                mixed_precision=True, use_mpi=False, init_process_group=False,
-                checkpoint_gradients=False)
-            warmup = max(args.warmup, 3)
+            import mpu as ref_mpu
+            tp, pp = spec["tp"], spec["pp"]
+            dp = self.world // (tp * pp)
+            config = TransformerConfig.from_predefined_model(spec["model"], n_devices=self.world,
+                                                             batch_size=spec["batch"])
+            if spec.get("n_layers") is not None:
+                config.n_layers = spec["n_layers"]
+            seq_len = MODEL_CONFIGS[spec["model"]][2]
+            batch_slices, seq_slices = self.slices_for(spec, seq_len, self.args if main else None)
+            recompute = bool(spec.get("checkpoint_gradients", False))
+            torch.cuda.reset_peak_memory_stats()
+            runner = self.ref.NCCLTransformerRunner(
+                config, batch_slices, seq_slices, "env://", self.world, dp, tp, pp, self.rank,
+                self.local, mixed_precision=True, use_mpi=False, init_process_group=False,
+                checkpoint_gradients=recompute)
             for _ in range(warmup):
                 runner.step()
-            sampler = ClockSampler(local)
-            if rank == 0:
+            sampler = self.ClockSampler(self.local)
+            if self.rank == 0:
                 sampler.start()
-            ms = timed_steps(runner.step, args.steps, world, device)
-            clocks = sampler.stop() if rank == 0 else None
-        ms_per_step = ms / args.steps
-        tokens = args.batch * seq_len * dp
-        if rank == 0:
-            value = tokens / (ms_per_step / 1e3)
-            print(json.dumps({
-                "metric": "training throughput (tokens/s), GPT-3-shaped decoder, fwd+bwd+Adam per iteration",
-                "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-                "warmup": warmup, "ms_per_step": ms_per_step, "iteration_latency_s": ms_per_step / 1e3,
-                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-                "dtype": "fp16", "data": "synthetic N(0,1) hidden states created on the device by the reference's own step(), random-init weights",
-                "impl": "reference",
-                "config": {"model": args.model, "n_layers": config.n_layers,
-                           "global_batch": tokens // seq_len, "seq_len": seq_len,
-                           "parallelism": f"pp{pp}xtp{args.tp}xdp{dp}", "batch_slices": batch_slices,
-                           "seq_slices": seq_slices, "activation": "relu (the reference's layer)",
-                           "optimizer": "torch.optim.Adam(fused=True) standing in for apex FusedAdam",
-                           "l2": "per-step working set far exceeds the 126 MB L2"},
-                "gpu_launches": None, "clocks": clocks,
-                "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0,
-                        "d2h_bytes_per_step": 0,
-                        "note": "the reference's public step() draws its inputs on the device and reads nothing back; this repeats the device-timed number"},
-            }), flush=True)
+            ms = self.timed_steps(runner.step, steps, self.world, self.device)
+            clocks = sampler.stop() if self.rank == 0 else None
+            peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
+            del runner
+            ref_mpu.destroy_model_parallel()
+            gc.collect()
+            torch.cuda.empty_cache()
+        ms_per_step = ms / steps
+        tokens = spec["batch"] * seq_len * dp
+        value = tokens / (ms_per_step / 1e3)
+        return {
+            "value": value, "unit": "tokens/s", "tokens_per_s": value, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "iteration_latency_s": ms_per_step / 1e3,
+            "data": "synthetic N(0,1) hidden states created on the device by the reference's own "
+                    "step(), random-init weights",
+            "config": self.config_dict(
+                model=spec["model"], n_layers=config.n_layers, hidden=config.embedding_dim,
+                heads=config.num_attention_heads, global_batch=tokens // seq_len, seq_len=seq_len,
+                parallelism=f"pp{pp}xtp{tp}xdp{dp}", batch_slices=batch_slices, seq_slices=seq_slices,
+                activation="relu", mixed_precision="fp32 master weights, loss scale 128",
+                optimizer="torch.optim.Adam(fused=True) standing in for apex FusedAdam",
+                attention_recompute=recompute, cuda_graph=False, launch_plan=False,
+                tp_comm="nccl" if tp > 1 else "none", dp_comm="nccl" if dp > 1 else "none",
+                l2=self.l2_note),
+            "gpu_launches": None, "clocks": clocks,
+            "e2e": {"value": value, "unit": "tokens/s", "ms_per_step": ms_per_step,
+                    "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "the reference's public step() draws its inputs on the device and reads "
+                            "nothing back; this repeats the device-timed number"},
+            "peak_memory_gb_torch_allocator": round(peak_gb, 2),
+        }
+
+    def tp_block(self, spec, steps, warmup):
+        block = self.measure(spec, steps, warmup)
+        return {"config": block["config"], "steps": steps, "warmup": warmup,
+                "modes": {"nccl": {"ms_per_step": block["ms_per_step"], "tokens_per_s": block["value"],
+                                   "clocks": block["clocks"]}}}
+
+    def finish(self):
+        import torch.distributed as dist
         dist.barrier()
         dist.destroy_process_group()
-    except Exception as e:  # noqa: BLE001
-        if rank == 0:
-            _unavailable(f"reference run failed: {type(e).__name__}: {str(e)[:200]}")

@@ -1,32 +1,46 @@
 #!/usr/bin/env python
-"""Headline benchmark: training-iteration throughput of a GPT-3-shaped decoder stack.
+"""Headline benchmark: training-iteration throughput of GPT-3-shaped decoder stacks.
 
     python bench.py --gpus N --steps K --warmup W            (N = 1)
     python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...   (N > 1)
 
-Default workload (every N): GPT3-1B shape (24 layers, hidden 2048, 16 heads, seq 2048),
-global batch 8, fp16 mixed precision with fp32 master weights + Adam, 16 uniform token
-slices, pipeline = N stages x tensor-parallel 1.  Synthetic N(0,1) inputs, random-init
-weights.  Total work is fixed as N grows (strong scaling).  ``--model gpt3-13b --tp 2 --pp 4``
-etc. select the larger layouts on 8 GPUs.
+``value`` (every N): GPT3-1B shape (24 layers, hidden 2048, 16 heads, seq 2048), global batch 8,
+fp16 mixed precision with fp32 master weights + Adam, 16 uniform token slices, pipeline = N
+stages x tensor-parallel 1.  Synthetic N(0,1) inputs, random-init weights.  Total work is fixed
+as N grows (strong scaling).
 
-Rank 0 prints ONE JSON line.  ``value`` is tokens/s of the whole job, timed on the device
-(CUDA events, max over ranks) over exactly K steps after W warm-up steps; ``e2e`` repeats
-the measurement through ``Trainer.train_step`` with the per-step host->device input copy
-(from pinned memory) and device->host loss read inside the timed region.
+Further blocks ride in the same JSON line, each timed the same way with its own step count:
 
-``--impl reference`` runs the unmodified reference (installed under ``baseline/_ref``)
-through its own ``NCCLTransformerRunner.step`` on the same model/config/slices.
+* N = 8: ``headline`` (GPT3-13B, pipeline 4 x tensor-parallel 2), ``headline_44b`` (GPT3-44B,
+  pipeline 2 x tensor-parallel 4, batch 4) and ``headline_tp8`` (8 layers of GPT3-175B width,
+  tensor-parallel 8, batch 2), with the fused GEMM + collective kernels;
+* N = 2, 4: ``tp_block``: 4 layers of GPT3-13B width with tensor-parallel N, once per
+  tensor-parallel communication mode (NCCL after the GEMM, fused all-reduce, sequence-parallel
+  reduce-scatter / all-gather), with the relative error of the gradients against the NCCL mode.
+
+Rank 0 prints ONE JSON line.  Times are CUDA events around exactly K steps after W >= 3 warm-up
+steps, maximum over ranks; ``e2e`` repeats the measurement through ``Trainer.train_step`` with
+the per-step host->device input copy (from pinned memory) and the device->host loss read inside
+the timed region.
+
+``--impl reference`` runs the unmodified reference (installed under ``baseline/_ref``) through
+its own ``NCCLTransformerRunner.step`` on the same models, layouts and slices, block by block.
+
+Every block runs under a host-side deadline: if it is still running after ``--block-timeout``
+seconds, rank 0 prints the line with what has been measured so far (the block is marked
+``timed_out``) and every rank leaves with status 0, so one stuck block cannot lose the others.
 """
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
 import subprocess
 import sys
 import tempfile
+import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -35,6 +49,18 @@ sys.path.insert(0, ROOT)
 # No published single-box number exists for these configs: the reference's numbers are
 # 192-384 V100 cluster latencies, so there is nothing to divide by.
 BASELINE_TOKENS_PER_S = None
+
+METRIC = "training throughput (tokens/s), GPT-3-shaped decoder, fwd+bwd+Adam per iteration"
+
+# Extra blocks by GPU count.  `steps` caps the timed steps of the block (warm-up is always >= 3).
+HEADLINE_BLOCKS = {
+    "headline": dict(model="gpt3-13b", batch=8, tp=2, pp=4, seq_slices=16, batch_slices=1, steps=5),
+    "headline_tp8": dict(model="gpt3-175b", n_layers=8, batch=2, tp=8, pp=1, seq_slices=8,
+                         batch_slices=1, steps=5),
+    "headline_44b": dict(model="gpt3-44b", batch=4, tp=4, pp=2, seq_slices=8, batch_slices=1,
+                         steps=3, checkpoint_gradients=True),
+}
+TP_BLOCK = dict(model="gpt3-13b", n_layers=4, batch=8, pp=1, seq_slices=16, batch_slices=1, steps=5)
 
 
 def parse_args():
@@ -56,13 +82,17 @@ def parse_args():
     ap.add_argument("--schedule-index", type=int, default=0, help="entry of a dp_results.json list")
     ap.add_argument("--dtype", default="fp16", choices=["fp16", "bf16"])
     ap.add_argument("--activation", default=None, choices=[None, "gelu", "relu"])
-    ap.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
+    ap.add_argument("--tp-comm", default="fused", choices=["nccl", "fused", "sp"])
     ap.add_argument("--dp-comm", default="nccl", choices=["nccl", "fused"])
     ap.add_argument("--no-graph", action="store_true", help="never capture the step in a CUDA graph")
     ap.add_argument("--graph", action="store_true", help="capture even when the stage communicates")
     ap.add_argument("--launch-plan", action="store_true",
                     help="stages that run eagerly replay recorded launch lists (see runtime/launch_plan.py)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--blocks", default="auto",
+                    help="'auto' (the blocks of this GPU count), 'none', or a comma list of block names")
+    ap.add_argument("--block-timeout", type=float, default=None,
+                    help="seconds a single block may take (default 420 ours, 900 reference)")
     return ap.parse_args()
 
 
@@ -119,6 +149,39 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+class Deadline:
+    """Host-side guard of one block: when the armed time runs out, rank 0 emits the JSON line
+    with what exists and every rank ends its process with status 0."""
+
+    def __init__(self, rank, emit):
+        self.rank, self.emit = rank, emit
+        self.until, self.label = None, None
+        self.lock = threading.Lock()
+        threading.Thread(target=self._watch, daemon=True).start()
+
+    def arm(self, seconds, label):
+        with self.lock:
+            self.until, self.label = time.time() + seconds, label
+
+    def disarm(self):
+        with self.lock:
+            self.until = None
+
+    def _watch(self):
+        while True:
+            time.sleep(1.0)
+            with self.lock:
+                expired = self.until is not None and time.time() > self.until
+                label = self.label
+            if expired:
+                if self.rank == 0:
+                    self.emit(label)
+                else:
+                    time.sleep(3.0)
+                sys.stdout.flush()
+                os._exit(0)
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -126,30 +189,38 @@ def dist_env():
     return rank, world, local
 
 
-def slices_from_args(args, seq_len):
+def config_dict(**kw):
+    """The `config` object of a block; both arms fill the same keys."""
+    keys = ("model", "n_layers", "hidden", "heads", "global_batch", "seq_len", "parallelism",
+            "batch_slices", "seq_slices", "activation", "mixed_precision", "optimizer",
+            "attention_recompute", "cuda_graph", "launch_plan", "tp_comm", "dp_comm", "l2")
+    return {k: kw.get(k) for k in keys}
+
+
+L2_NOTE = "per-step working set (weights + activations, several GB) far exceeds the 126 MB L2"
+
+
+def slices_for(spec, seq_len, args=None):
+    """(batch_slices, seq_slices) of a block: uniform, or from --schedule for the main block."""
     from terapipe_b200.utils import uniform_slice
-    if args.schedule == "auto":
-        # planned for this model and layout on kernel-model tables (every rank computes the same)
+    if args is not None and args.schedule == "auto":
         from terapipe_b200.planner.latency_model import auto_schedule
-        world = int(os.environ.get("WORLD_SIZE", "1"))
-        pp = args.pp if args.pp is not None else world // args.tp
-        bs, ss, _ = auto_schedule(args.model, args.batch, args.tp, pp, fused_tp=args.tp_comm == "fused",
-                                  n_layers=args.n_layers)
+        bs, ss, _ = auto_schedule(spec["model"], spec["batch"], spec["tp"], spec["pp"],
+                                  fused_tp=args.tp_comm != "nccl", n_layers=spec.get("n_layers"))
         return bs, ss
-    if args.schedule:
+    if args is not None and args.schedule:
         with open(args.schedule) as f:
             sched = json.load(f)
         if isinstance(sched, list):
-            # a dp_results list: the entry planned for this model and layout if there is one,
-            # otherwise the entry at --schedule-index
-            world = int(os.environ.get("WORLD_SIZE", "1"))
-            pp = args.pp if args.pp is not None else world // args.tp
-            match = [e for e in sched if e.get("model_name") == args.model and
-                     e.get("model_parallel_size") == args.tp and e.get("pipeline_length") == pp and
-                     e.get("batch_size") == args.batch]
+            match = [e for e in sched if e.get("model_name") == spec["model"] and
+                     e.get("model_parallel_size") == spec["tp"] and
+                     e.get("pipeline_length") == spec["pp"] and e.get("batch_size") == spec["batch"]]
             sched = match[0] if match else sched[args.schedule_index]
         return list(sched["batch_slices"]), list(sched["input_slices"])
-    return uniform_slice(args.batch, args.batch_slices), uniform_slice(seq_len, args.seq_slices)
+    if "seq_slice_list" in spec:
+        return list(spec["batch_slice_list"]), list(spec["seq_slice_list"])
+    return (uniform_slice(spec["batch"], spec.get("batch_slices", 1)),
+            uniform_slice(seq_len, spec["seq_slices"]))
 
 
 def max_over_ranks(value, world, device):
@@ -184,103 +255,239 @@ def timed_steps(step_fn, steps, world, device):
     return max_over_ranks(e0.elapsed_time(e1), world, device)
 
 
-def run_ours(args):
-    import torch
-    import torch.distributed as dist
-    from terapipe_b200.models import MODEL_CONFIGS
-    from terapipe_b200.runtime.trainer import Trainer
+# ---------------------------------------------------------------------------------------------
+class OursArm:
+    """This repository's engine through its public API (`Trainer`)."""
+    name = "ours"
 
-    rank, world, local = dist_env()
-    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
-    torch.cuda.set_device(local)
-    device = torch.device("cuda", local)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("nccl", device_id=device)
-    pp = args.pp if args.pp is not None else world // args.tp
-    if args.launch_plan:
-        os.environ["TERAPIPE_LAUNCH_PLAN"] = "1"
-    seq_len = MODEL_CONFIGS[args.model][2]
-    batch_slices, seq_slices = slices_from_args(args, seq_len)
-    trainer = Trainer(args.model, batch_size=args.batch, tp=args.tp, pp=pp,
-                      batch_slices=batch_slices, seq_slices=seq_slices,
-                      dtype=args.dtype, n_layers=args.n_layers, activation=args.activation or "gelu",
-                      use_graph=(False if args.no_graph else (True if args.graph else None)),
-                      tp_comm=args.tp_comm, dp_comm=args.dp_comm)
-    cfg = trainer.config
-    tokens = cfg.batch_size * cfg.seq_len * trainer.topo.dp
+    def __init__(self, args):
+        self.args = args
 
-    # ---- device-timed: inputs already resident, K steps
-    trainer.load_input(trainer.synthetic_input(0))
-    for _ in range(max(args.warmup, 3)):
-        trainer.engine.step()
-    launches0 = trainer.engine.launch_count
-    sampler = ClockSampler(local)
-    if rank == 0:
-        sampler.start()
-    ms = timed_steps(trainer.engine.step, args.steps, world, device)
-    clocks = sampler.stop() if rank == 0 else None
-    launches = trainer.engine.launch_count - launches0
-    trainer.engine.check_status()
-    ms_per_step = ms / args.steps
+    def setup(self, rank, world, local):
+        import torch
+        import torch.distributed as dist
+        self.rank, self.world, self.local = rank, world, local
+        torch.cuda.set_device(local)
+        self.device = torch.device("cuda", local)
+        if world > 1:
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            dist.init_process_group("nccl", device_id=self.device)
+        if self.args.launch_plan:
+            os.environ["TERAPIPE_LAUNCH_PLAN"] = "1"
+        return None
 
-    # ---- end to end through the public API: pinned host input -> H2D, step, loss -> D2H
-    e2e = None
-    if not args.no_e2e:
-        host_inputs = [trainer.synthetic_input(i, pinned=True) for i in range(2)]
-        state = {"i": 0, "loss": None}
+    def _trainer(self, spec, batch_slices, seq_slices, tp_comm):
+        from terapipe_b200.runtime.trainer import Trainer
+        a = self.args
+        return Trainer(spec["model"], batch_size=spec["batch"], tp=spec["tp"], pp=spec["pp"],
+                       batch_slices=batch_slices, seq_slices=seq_slices, dtype=a.dtype,
+                       n_layers=spec.get("n_layers"), activation=a.activation or "gelu",
+                       use_graph=(False if a.no_graph else (True if a.graph else None)),
+                       tp_comm=tp_comm, dp_comm=a.dp_comm)
 
-        def e2e_step():
-            x = host_inputs[state["i"] % 2] if host_inputs[0] is not None else None
-            state["loss"] = trainer.train_step(x)
-            state["i"] += 1
+    def measure(self, spec, steps, warmup, main=False, tp_comm=None, keep_grads=False):
+        import torch
+        from terapipe_b200.models import MODEL_CONFIGS
+        a = self.args
+        seq_len = MODEL_CONFIGS[spec["model"]][2]
+        batch_slices, seq_slices = slices_for(spec, seq_len, a if main else None)
+        tp_comm = tp_comm or a.tp_comm
+        torch.cuda.reset_peak_memory_stats()
+        trainer = self._trainer(spec, batch_slices, seq_slices, tp_comm)
+        eng = trainer.engine
+        cfg = trainer.config
+        tokens = cfg.batch_size * cfg.seq_len * trainer.topo.dp
 
-        for _ in range(2):
-            e2e_step()
-        ms_e2e = timed_steps(e2e_step, args.steps, world, device)
-        h2d = cfg.seq_len * cfg.batch_size * cfg.embedding_dim * 2
-        e2e = {"value": tokens / (ms_e2e / args.steps / 1e3), "unit": "tokens/s",
-               "ms_per_step": ms_e2e / args.steps, "h2d_bytes_per_step": h2d,
-               "d2h_bytes_per_step": 4, "last_loss": state["loss"]}
+        # ---- device-timed: inputs already resident, K steps
+        trainer.load_input(trainer.synthetic_input(0))
+        for _ in range(warmup):
+            eng.step()
+        launches0 = eng.launch_count
+        sampler = ClockSampler(self.local)
+        if self.rank == 0:
+            sampler.start()
+        ms = timed_steps(eng.step, steps, self.world, self.device)
+        clocks = sampler.stop() if self.rank == 0 else None
+        launches = eng.launch_count - launches0
+        eng.check_status()
+        ms_per_step = ms / steps
 
-    if rank == 0:
+        # ---- end to end through the public API: pinned host input -> H2D, step, loss -> D2H
+        e2e = None
+        if not a.no_e2e:
+            host_inputs = [trainer.synthetic_input(i, pinned=True) for i in range(2)]
+            state = {"i": 0, "loss": None}
+
+            def e2e_step():
+                x = host_inputs[state["i"] % 2] if host_inputs[0] is not None else None
+                state["loss"] = trainer.train_step(x)
+                state["i"] += 1
+
+            for _ in range(2):
+                e2e_step()
+            ms_e2e = timed_steps(e2e_step, steps, self.world, self.device)
+            trainer.finish()
+            h2d = cfg.seq_len * cfg.batch_size * cfg.embedding_dim * 2
+            e2e = {"value": tokens / (ms_e2e / steps / 1e3), "unit": "tokens/s",
+                   "ms_per_step": ms_e2e / steps, "h2d_bytes_per_step": h2d,
+                   "d2h_bytes_per_step": 8, "last_loss": state["loss"]}
+        grads = None
+        if keep_grads:
+            trainer.load_input(trainer.synthetic_input(0))
+            eng.compute_grads()
+            grads = eng.grad.clone()
+        peak_gb = torch.cuda.max_memory_allocated() / 2 ** 30
         value = tokens / (ms_per_step / 1e3)
-        out = {
-            "metric": "training throughput (tokens/s), GPT-3-shaped decoder, fwd+bwd+Adam per iteration",
-            "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
-            "iteration_latency_s": ms_per_step / 1e3,
-            "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": (value / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
-            "dtype": args.dtype, "data": "synthetic N(0,1) hidden states, random-init weights",
-            "impl": "ours",
-            "config": {"model": args.model, "n_layers": cfg.n_layers, "hidden": cfg.embedding_dim,
-                       "heads": cfg.num_attention_heads, "global_batch": cfg.batch_size * trainer.topo.dp,
-                       "seq_len": cfg.seq_len, "parallelism": f"pp{pp}xtp{args.tp}xdp{trainer.topo.dp}",
-                       "batch_slices": batch_slices, "seq_slices": seq_slices,
-                       "activation": cfg.activation, "mixed_precision": "fp32 master + Adam, loss scale 128",
-                       "cuda_graph": bool(trainer.engine.use_graph),
-                       "launch_plan": trainer.engine._plan is not None, "tp_comm": trainer.engine.tp_comm, "dp_comm": trainer.engine.dp_comm,
-                       "l2": "per-step working set (weights + activations, several GB) far exceeds the 126 MB L2"},
+        pp, tp, dp = trainer.topo.pp, trainer.topo.tp, trainer.topo.dp
+        block = {
+            "value": value, "unit": "tokens/s", "tokens_per_s": value, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms_per_step, "iteration_latency_s": ms_per_step / 1e3,
+            "config": config_dict(
+                model=spec["model"], n_layers=cfg.n_layers, hidden=cfg.embedding_dim,
+                heads=cfg.num_attention_heads, global_batch=cfg.batch_size * dp, seq_len=cfg.seq_len,
+                parallelism=f"pp{pp}xtp{tp}xdp{dp}", batch_slices=batch_slices, seq_slices=seq_slices,
+                activation=cfg.activation, mixed_precision="fp32 master weights, loss scale 128",
+                optimizer="fused mixed-precision Adam (this library)",
+                attention_recompute=True, cuda_graph=("step" if eng.use_graph else
+                                                      ("segments" if eng._seg_graphs is not None else False)),
+                launch_plan=eng._plan is not None, tp_comm=eng.tp_comm, dp_comm=eng.dp_comm, l2=L2_NOTE),
             "gpu_launches": launches, "clocks": clocks, "e2e": e2e,
+            "peak_memory_gb_torch_allocator": round(peak_gb, 2),
         }
-        print(json.dumps(out), flush=True)
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        trainer.close()
+        del trainer, eng
+        gc.collect()
+        torch.cuda.empty_cache()
+        return (block, grads) if keep_grads else block
+
+    def tp_block(self, spec, steps, warmup):
+        """Tensor-parallel layer stack once per communication mode; gradients compared with the
+        NCCL mode's."""
+        import torch
+        out = {"config": None, "modes": {}}
+        ref_grads = None
+        modes = ["nccl", "fused"]
+        from terapipe_b200.runtime.engine import StageEngine
+        if "sp" in getattr(StageEngine, "TP_COMM_MODES", ()):
+            modes.append("sp")
+        for mode in modes:
+            block, grads = self.measure(spec, steps, warmup, tp_comm=mode, keep_grads=True)
+            entry = {"ms_per_step": block["ms_per_step"], "tokens_per_s": block["value"],
+                     "e2e_ms_per_step": block["e2e"]["ms_per_step"] if block["e2e"] else None,
+                     "gpu_launches": block["gpu_launches"], "clocks": block["clocks"]}
+            if ref_grads is None:
+                ref_grads = grads
+            else:
+                num = (grads.double() - ref_grads.double()).norm() ** 2
+                den = ref_grads.double().norm() ** 2
+                t = torch.stack([num, den])
+                if self.world > 1:
+                    import torch.distributed as dist
+                    dist.all_reduce(t)
+                entry["grad_rel_err_vs_nccl"] = float((t[0] / t[1]).sqrt().item())
+            out["modes"][mode] = entry
+            if out["config"] is None or mode == self.args.tp_comm:
+                out["config"] = block["config"]
+            out["steps"], out["warmup"] = block["steps"], block["warmup"]
+            del grads
+        del ref_grads
+        torch.cuda.empty_cache()
+        return out
+
+    def finish(self):
+        import torch.distributed as dist
+        if self.world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
 
 
-def run_reference(args):
-    from baseline.reference_arm import run as run_ref
-    run_ref(args, dist_env, timed_steps, ClockSampler, slices_from_args)
+def make_arm(args):
+    if args.impl == "reference":
+        from baseline.reference_arm import ReferenceArm
+        return ReferenceArm(args, timed_steps, ClockSampler, slices_for, config_dict, L2_NOTE)
+    return OursArm(args)
 
 
 def main():
     args = parse_args()
-    if args.impl == "reference":
-        run_reference(args)
+    rank, world, local = dist_env()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    warmup = max(args.warmup, 3)
+    arm = make_arm(args)
+    why = arm.setup(rank, world, local)
+    if why is not None:                      # the reference arm could not be set up
+        if rank == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+        return
+
+    out = {"metric": METRIC, "impl": arm.name, "n_gpus": world, "higher_is_better": True,
+           "scaling": "strong", "dtype": args.dtype if arm.name == "ours" else "fp16"}
+    printed = threading.Event()
+
+    def emit(timed_out_label=None):
+        if rank != 0 or printed.is_set():
+            return
+        printed.set()
+        if timed_out_label is not None:
+            out.setdefault(timed_out_label, {})
+            if isinstance(out[timed_out_label], dict):
+                out[timed_out_label]["timed_out"] = True
+        print(json.dumps(out), flush=True)
+
+    limit = args.block_timeout or (420.0 if arm.name == "ours" else 900.0)
+    deadline = Deadline(rank, emit)
+
+    main_spec = dict(model=args.model, n_layers=args.n_layers, batch=args.batch, tp=args.tp,
+                     pp=args.pp if args.pp is not None else world // args.tp,
+                     seq_slices=args.seq_slices, batch_slices=args.batch_slices)
+    deadline.arm(2 * limit, "main")
+    blk = arm.measure(main_spec, args.steps, warmup, main=True)
+    deadline.disarm()
+    out.update({"value": blk["value"], "unit": "tokens/s", "steps": blk["steps"], "warmup": blk["warmup"],
+                "ms_per_step": blk["ms_per_step"], "iteration_latency_s": blk["iteration_latency_s"],
+                "vs_baseline": (blk["value"] / BASELINE_TOKENS_PER_S) if BASELINE_TOKENS_PER_S else None,
+                "data": blk.get("data", "synthetic N(0,1) hidden states, random-init weights"),
+                "config": blk["config"], "gpu_launches": blk["gpu_launches"], "clocks": blk["clocks"],
+                "e2e": blk["e2e"]})
+    if "peak_memory_gb_torch_allocator" in blk:
+        out["peak_memory_gb_torch_allocator"] = blk["peak_memory_gb_torch_allocator"]
+
+    # ---- further blocks
+    default_main = (args.model == "gpt3-1b" and args.tp == 1 and args.pp is None and args.n_layers is None)
+    if args.blocks == "auto":
+        names = []
+        if default_main and world == 8:
+            names = list(HEADLINE_BLOCKS)
+        elif default_main and world in (2, 4):
+            names = ["tp_block"]
+    elif args.blocks == "none":
+        names = []
     else:
-        run_ours(args)
+        names = [n for n in args.blocks.split(",") if n]
+    for name in names:
+        deadline.arm(limit, name)
+        try:
+            if name == "tp_block":
+                spec = dict(TP_BLOCK, tp=world)
+                out[name] = arm.tp_block(spec, min(args.steps, spec["steps"]), warmup)
+            else:
+                spec = dict(HEADLINE_BLOCKS[name])
+                if spec["tp"] * spec["pp"] != world:
+                    out[name] = {"skipped": f"needs {spec['tp'] * spec['pp']} GPUs"}
+                    continue
+                out[name] = arm.measure(spec, min(args.steps, spec["steps"]), warmup)
+        except Exception as e:  # noqa: BLE001
+            # The other ranks may be inside a collective of this block: report what exists and
+            # leave; their own deadlines end them.  (Rank 0 prints; any other rank just leaves
+            # and rank 0's deadline prints the line.)
+            out[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+            emit()
+            sys.stdout.flush()
+            os._exit(0)
+        finally:
+            deadline.disarm()
+    emit()
+    arm.finish()
 
 
 if __name__ == "__main__":

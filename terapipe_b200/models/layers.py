@@ -25,9 +25,9 @@ from .config import NEG_INF
 class _AssignCache(torch.autograd.Function):
     """KV-append: write ``value`` into ``cache[index]`` in place and return ``cache``
     (reference: transformer_models.py:177-193).  The gradient of the written region flows to
-    ``value``; the rest flows to the earlier cache.  Unlike the reference, backward does not
-    clone the whole cache gradient: it reuses the incoming buffer and zeroes the slice in it,
-    which is safe because that buffer is consumed by nobody else."""
+    ``value``; the rest flows to the earlier cache.  Backward never writes into the incoming
+    gradient (autograd may hand over a caller's ``grad_outputs`` tensor or a retained ``.grad``):
+    the gradient of the earlier cache is a new tensor with the slice zeroed."""
 
     @staticmethod
     def forward(ctx, cache, value, index):
@@ -38,8 +38,8 @@ class _AssignCache(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_cache_output):
         grad_value = grad_cache_output[ctx.index].clone()
-        grad_cache = grad_cache_output
-        grad_cache.data[ctx.index] = 0
+        grad_cache = grad_cache_output.clone()
+        grad_cache[ctx.index] = 0
         return grad_cache, grad_value, None
 
 

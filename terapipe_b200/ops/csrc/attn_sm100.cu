@@ -766,3 +766,5 @@ extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int 
   return bf16 ? attn_bwd_launch<__nv_bfloat16, 64>(qkv, o, do_full, ld_do, p, true, s)
               : attn_bwd_launch<__half, 64>(qkv, o, do_full, ld_do, p, false, s);
 }
+
+TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_attn)

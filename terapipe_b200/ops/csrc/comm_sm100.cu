@@ -100,7 +100,7 @@ __device__ __forceinline__ bool spin_until(const int* p, int target, int* err, i
     if ((++spins & 0x3F) == 0) {
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > g_wait_limit_ns) {
         if (err) atomicCAS(err, 0, code);
         return false;
       }
@@ -263,4 +263,17 @@ extern "C" int tp_link_probe(void* dst, long long bytes, int mode, void* stream)
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   link_probe_kernel<<<grid, 256, 16384, s>>>(static_cast<uint4*>(dst), n_vec, mode);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// Limit of every bounded device-side wait of this library (mbarrier, peer flags), on the current
+// device; the default is 2 s.  Call it with no kernel of the library in flight.
+TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_comm)
+extern "C" int tp_set_wait_limit_ns_gemm(unsigned long long ns);
+extern "C" int tp_set_wait_limit_ns_attn(unsigned long long ns);
+extern "C" int tp_set_wait_limit_ns(unsigned long long ns) {
+  if (ns == 0) return kErrBadArgument;
+  if (cudaDeviceSynchronize() != cudaSuccess) return kErrDriver;
+  const int a = tp_set_wait_limit_ns_comm(ns), b = tp_set_wait_limit_ns_gemm(ns),
+            c = tp_set_wait_limit_ns_attn(ns);
+  return (a | b | c) ? kErrDriver : kOk;
 }

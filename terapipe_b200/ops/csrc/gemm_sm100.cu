@@ -94,7 +94,7 @@ __device__ __forceinline__ bool wait_flag(const int* p, int target, const WaitCt
       if (*w.abort_smem) return false;
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > g_wait_limit_ns) {
         report_timeout(w, code);
         return false;
       }
@@ -1471,6 +1471,8 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   return b_mn ? launch_gemm<__half, BN, false, true, false, true>(tmA, tmB, tmO, p, s, &ar)
               : launch_gemm<__half, BN, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
 }
+
+TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_gemm)
 
 namespace tp {
 __global__ void advance_counter_kernel(int* counter, int inc) { *counter += inc; }

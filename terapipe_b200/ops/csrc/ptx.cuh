@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for sm_100a: mbarrier, TMA (cp.async.bulk.tensor, each CTA
 // fetching its own tiles), tcgen05 (TMEM allocation, MMA, commit, TMEM loads) and the UMMA
-// shared-memory / instruction descriptors.  Every wait is bounded: after kWaitLimitNs the
+// shared-memory / instruction descriptors.  Every wait is bounded: after g_wait_limit_ns the
 // wait gives up, records an error code through `report_timeout` and returns false, so a
 // kernel can release its TMEM and return instead of hanging the device.
 #pragma once
@@ -12,7 +12,14 @@
 
 namespace tp {
 
-constexpr unsigned long long kWaitLimitNs = 2000000000ull;  // 2 s per wait
+// Limit of every device-side wait, in nanoseconds (default 2 s).  The variable exists once per
+// translation unit; tp_set_wait_limit_ns() (comm_sm100.cu) sets all of them on the current
+// device, which lets a test make a wait run out within milliseconds.
+static __device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+#define TP_DEFINE_WAIT_LIMIT_SETTER(fn_name)                                               \
+  extern "C" int fn_name(unsigned long long ns) {                                           \
+    return cudaMemcpyToSymbol(tp::g_wait_limit_ns, &ns, sizeof(ns)) == cudaSuccess ? 0 : -2; \
+  }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -87,7 +94,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
       if (*w.abort_smem) return false;
       unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
-      else if (now - t0 > kWaitLimitNs) {
+      else if (now - t0 > g_wait_limit_ns) {
         report_timeout(w, code);
         return false;
       }

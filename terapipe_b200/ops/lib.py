@@ -79,6 +79,7 @@ SIGNATURES = {
     "tp_link_probe": [P, L, I, P],
     "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, I, P, P],
     "tp_dp_reduce_adam": [I, I, I, I, P, P, P, P, P, P, P, L, L, P, F, F, F, F, F, F, P, P],
+    "tp_set_wait_limit_ns": [L],
     "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
     "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
 }

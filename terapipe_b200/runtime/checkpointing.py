@@ -35,9 +35,36 @@ def _atomic_save(obj, path: str) -> None:
     os.replace(tmp, path)
 
 
+def _gather_sharded_state(engine) -> None:
+    """With the fused data-parallel update (``dp_comm="fused"``) a rank keeps master weights and
+    Adam moments up to date only for the chunk of the flat parameter space it owns.  Before a
+    save every replica fetches the other chunks from their owners, so that each replica's
+    buffers are complete again (collective over the data-parallel group)."""
+    import torch.distributed as dist
+    from .. import parallel as mpu
+    if engine.dp_sym is None:
+        return
+    group = mpu.get_data_parallel_group()
+    n = engine.layout.total
+    chunk = ((n + engine.dp - 1) // engine.dp + 3) // 4 * 4
+    for buf in (engine.master, engine.exp_avg, engine.exp_avg_sq):
+        padded = torch.zeros(chunk * engine.dp, dtype=buf.dtype, device=buf.device)
+        mine = buf[engine._dp_begin:engine._dp_end]
+        own = torch.zeros(chunk, dtype=buf.dtype, device=buf.device)
+        own[:mine.numel()] = mine
+        dist.all_gather_into_tensor(padded, own, group=group)
+        buf.copy_(padded[:n])
+
+
 def save_checkpoint(engine, directory: str) -> str:
-    """Write this rank's shard (call on every rank; replicas other than dp 0 may skip)."""
+    """Write this rank's shard.  Call it on every rank, between steps: with the fused
+    data-parallel update the replicas first exchange the chunks of master weights and moments
+    they own (a collective), and the ranks of a tensor- or data-parallel group meet at a host
+    barrier afterwards, so that no rank runs ahead into a device-side wait while another is
+    still writing its file."""
+    import torch.distributed as dist
     os.makedirs(directory, exist_ok=True)
+    _gather_sharded_state(engine)
     blob = {
         "version": FORMAT_VERSION,
         "layout": {"tp": engine.tp, "pp": engine.pp, "dp": engine.dp, "tp_rank": engine.tp_idx,
@@ -51,11 +78,15 @@ def save_checkpoint(engine, directory: str) -> str:
     }
     path = shard_path(directory, engine.pp_idx, engine.tp_idx, engine.dp_idx)
     _atomic_save(blob, path)
+    if dist.is_available() and dist.is_initialized():
+        dist.barrier()
     return path
 
 
 def load_checkpoint(engine, directory: str) -> dict:
-    """Restore this rank's shard written with the SAME layout; returns the shard's metadata."""
+    """Restore this rank's shard written with the SAME layout; returns the shard's metadata.
+    Every data-parallel replica reads the shard of replica 0 (complete, see save_checkpoint)."""
+    import torch.distributed as dist
     from .engine import PARAM_ORDER
     path = shard_path(directory, engine.pp_idx, engine.tp_idx, 0)
     blob = torch.load(path, map_location="cpu")
@@ -63,6 +94,11 @@ def load_checkpoint(engine, directory: str) -> dict:
     if (lay["tp"], lay["pp"]) != (engine.tp, engine.pp):
         raise ValueError(f"checkpoint layout tp{lay['tp']}xpp{lay['pp']} differs from the engine's "
                          f"tp{engine.tp}xpp{engine.pp}; run reshard() first")
+    if lay["n_layers"] != engine.cfg.n_layers:
+        raise ValueError(f"checkpoint holds {lay['n_layers']} layers, the engine {engine.cfg.n_layers}")
+    if float(blob.get("loss_scale", engine.loss_scale)) != float(engine.loss_scale):
+        raise ValueError(f"checkpoint was written with loss scale {blob['loss_scale']}, the engine "
+                         f"uses {engine.loss_scale}")
     for key, buf in (("master", engine.master), ("exp_avg", engine.exp_avg),
                      ("exp_avg_sq", engine.exp_avg_sq)):
         for l in range(engine.n_layers):
@@ -72,6 +108,9 @@ def load_checkpoint(engine, directory: str) -> dict:
     engine.adam_state.copy_(blob["adam_state"])
     engine.step_count = blob["step"]
     torch.set_rng_state(blob["rng"]["torch"])
+    if dist.is_available() and dist.is_initialized():
+        torch.cuda.synchronize()
+        dist.barrier()
     return {"step": blob["step"], "layout": lay}
 
 

@@ -85,7 +85,8 @@ class StageEngine:
     def __init__(self, config: TransformerConfig, batch_slices: Sequence[int],
                  seq_slices: Sequence[int], dtype=torch.float16, loss_scale=LOSS_SCALE_FACTOR,
                  lr=1e-10, seed=0, init="device", use_graph: Optional[bool] = None,
-                 tp_comm="nccl", dp_comm="nccl", device=None, launch_plan: Optional[bool] = None):
+                 tp_comm="nccl", dp_comm="nccl", device=None, launch_plan: Optional[bool] = None,
+                 segment_graphs: Optional[bool] = None):
         assert torch.cuda.is_available(), "StageEngine needs a CUDA device (sm_100a)"
         self.cfg = config
         self.batch_slices, self.seq_slices = list(batch_slices), list(seq_slices)
@@ -162,6 +163,18 @@ class StageEngine:
             from .launch_plan import RecordingLibrary, SegmentCache
             self.lib = RecordingLibrary(self.lib)
             self._plan = SegmentCache(self.lib, on_error=lambda rc, name: F.check(rc, name))
+        # Stages that cannot put the whole step into one CUDA graph (they talk to their pipeline
+        # neighbours through NCCL) still capture every launch-only part of the step (one token
+        # slice forward or backward, the weight gradients, the optimizer) in a graph of its own
+        # and replay it between the NCCL calls, so the host issues one graph launch instead of
+        # ~16 kernel launches per layer.  A segment that all-reduces through NCCL is not captured.
+        seg_ok = (not self.use_graph and self._plan is None
+                  and (self.tp == 1 or self.tp_comm != "nccl")
+                  and os.environ.get("TERAPIPE_SEGMENT_GRAPHS", "1") != "0")
+        if segment_graphs is not None:
+            seg_ok = seg_ok and bool(segment_graphs)
+        self._seg_graphs = {} if seg_ok else None
+        self._cap_stream = None
         self.timeline = None   # set to a utils.trace.SliceTimeline to record per-slice device times
         self.step_count = 0
         self._streams_ready = False
@@ -494,11 +507,43 @@ class StageEngine:
             self._plan.validate((self._stream, self._status_ptr))
 
     def _segment(self, key, fn, *args):
-        """Run one launch-only part of the step: directly, or through the recorded plan."""
-        if self._plan is None:
-            fn(*args)
-        else:
+        """Run one launch-only part of the step: directly, through the recorded plan, or as a
+        CUDA graph of its own (first call eager, second call captured, then replayed)."""
+        if self._plan is not None:
             self._plan.run(key, fn, *args)
+        elif self._seg_graphs is not None:
+            self._run_graphed(key, fn, *args)
+        else:
+            fn(*args)
+
+    def _run_graphed(self, key, fn, *args):
+        ent = self._seg_graphs.get(key)
+        ar0 = getattr(self, "_ar_calls", 0)
+        if ent is None:
+            # first time: eager (kernel attributes get set, nothing may be captured before that)
+            fn(*args)
+            self._seg_graphs[key] = [None, getattr(self, "_ar_calls", 0) - ar0]
+            return
+        if ent[0] is None:
+            if self._cap_stream is None:
+                self._cap_stream = torch.cuda.Stream()
+            graph = torch.cuda.CUDAGraph()
+            outer = self._stream
+            # thread-local capture mode: NCCL's watchdog thread may query events meanwhile
+            with torch.cuda.stream(self._cap_stream):
+                graph.capture_begin(capture_error_mode="thread_local")
+                try:
+                    self._stream = self._cap_stream.cuda_stream
+                    fn(*args)
+                finally:
+                    graph.capture_end()
+                    self._stream = outer
+            if self.ar is not None:
+                self._ar_calls = ar0     # the captured launches did not run
+            ent[0] = graph
+        ent[0].replay()
+        if self.ar is not None:
+            self._ar_calls += ent[1]     # epochs baked into the graph stay in step with the host
 
     def _setup_streams(self):
         if self._streams_ready:
@@ -611,7 +656,10 @@ class StageEngine:
             self.grad.zero_()
         self._forward_backward()
         if update:
-            self._reduce_and_update()
+            if self.dp == 1 or self.dp_sym is not None:
+                self._segment(("update",), self._reduce_and_update)
+            else:
+                self._reduce_and_update()
 
     def set_input(self, x: torch.Tensor) -> None:
         """Copy this replica's ``[L, B, H]`` input into the stage-0 activation buffer.  Rows are
@@ -672,3 +720,17 @@ class StageEngine:
 
     def check_status(self):
         F.check_device_status(self.device)
+
+    def close(self) -> None:
+        """Release the peer-mapped buffers (collective over the tensor- and data-parallel groups;
+        call it between steps).  The engine must not be used afterwards."""
+        self._graph = None
+        if self._seg_graphs is not None:
+            self._seg_graphs.clear()
+        torch.cuda.synchronize()
+        if self.ar is not None:
+            self.ar.close()
+            self.ar = None
+        if self.dp_sym is not None:
+            self.dp_sym.close()
+            self.dp_sym = None

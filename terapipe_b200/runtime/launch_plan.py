@@ -81,6 +81,10 @@ class SegmentCache:
                 seg = self.lib.end()
             if seg is not None:
                 self.segments[key] = seg
+            else:
+                # a dropped recording would leave the others with call counters that no longer
+                # line up with what the host derives: start over
+                self.segments.clear()
             return
         for f, a in seg:
             rc = f(*a)

@@ -56,6 +56,9 @@ class Trainer:
                                   loss_scale=loss_scale, lr=lr, seed=seed, init=init,
                                   use_graph=use_graph, tp_comm=tp_comm, dp_comm=dp_comm)
         self._staging = None
+        # host mirror of the device status word (bounded device waits report through it)
+        self._status_host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._status_event = None
 
     @property
     def is_first_stage(self) -> bool:
@@ -82,11 +85,48 @@ class Trainer:
     def train_step(self, x: Optional[torch.Tensor] = None) -> Optional[float]:
         """One iteration end to end.  ``x`` is the replica's host (ideally pinned) or device
         input on first-stage ranks; returns the loss as a Python float on last-stage ranks."""
+        self._raise_on_device_timeout()          # status of the previous step (already on the host)
         self.load_input(x)
         self.engine.step()
         if self.is_last_stage:
-            return float(self.engine.loss().item())
+            # one synchronising read brings back the loss and the status word together
+            both = torch.stack([self.engine.loss().reshape(()),
+                                self.engine.status[0].to(torch.float32)]).tolist()
+            self._check_code(int(both[1]))
+            return float(both[0])
+        self._status_host.copy_(self.engine.status, non_blocking=True)
+        self._status_event = torch.cuda.Event()
+        self._status_event.record()
         return None
+
+    def _check_code(self, code: int) -> None:
+        if code != 0:
+            from ..ops.lib import CommTimeout
+            self.engine.status.zero_()
+            raise CommTimeout(f"a device-side wait timed out during the step (code {code}): "
+                              "a peer did not reach the same kernel within the wait limit")
+
+    def _raise_on_device_timeout(self) -> None:
+        """Raise :class:`CommTimeout` if the previous step left a time-out code in the status
+        word.  Ranks that do not read a loss learn of it here, one step later, without ever
+        stalling the host on the device."""
+        if self._status_event is not None:
+            self._status_event.synchronize()
+            self._status_event = None
+            self._check_code(int(self._status_host[0]))
+
+    def finish(self) -> None:
+        """Wait for the device and surface a pending time-out (call after the last step)."""
+        torch.cuda.synchronize()
+        self._status_event = None
+        self._check_code(int(self.engine.status.item()))
+
+    def close(self) -> None:
+        """Free the engine's peer-mapped memory and forget the parallel layout, so that another
+        Trainer with a different layout can be built in the same process (collective)."""
+        self.engine.close()
+        self.engine = None
+        mpu.destroy_model_parallel()
 
     def compute_grads(self, x: Optional[torch.Tensor] = None):
         self.load_input(x)

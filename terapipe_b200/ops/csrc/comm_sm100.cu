@@ -265,6 +265,117 @@ extern "C" int tp_link_probe(void* dst, long long bytes, int mode, void* stream)
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Small collectives of the sequence-parallel tensor-parallel path (all over peer-mapped memory,
+// plain loads / stores and system-scope flags, every wait bounded).
+namespace tp {
+
+struct PeerPtrs {
+  void* ptr[kMaxDp];
+  int* flags[kMaxDp];
+  int n, rank, epoch;
+  const int* epoch_base;
+  int* counter;
+  int* err;
+};
+
+// Copy `n_vec` 16-byte vectors from `src` (local) to the same offset of every other rank's
+// buffer, then raise flags[r][rank] = epoch at every other rank r (last CTA).
+__global__ void __launch_bounds__(256) ag_push_kernel(const uint4* __restrict__ src, long long n_vec,
+                                                      const PeerPtrs pp) {
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < n_vec;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const uint4 v = __ldcg(src + i);
+    for (int r = 0; r < pp.n; ++r)
+      if (r != pp.rank) static_cast<uint4*>(pp.ptr[r])[i] = v;
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (atomicAdd(reinterpret_cast<unsigned*>(pp.counter), 1u) == gridDim.x - 1) {
+      *pp.counter = 0;
+      const int epoch = pp.epoch + (pp.epoch_base ? *pp.epoch_base : 0);
+      __threadfence_system();
+      for (int r = 0; r < pp.n; ++r)
+        if (r != pp.rank) st_release_sys_i(pp.flags[r] + pp.rank, epoch);
+    }
+  }
+}
+
+// Barrier over the group: raise flags[r][rank] = epoch at every rank, wait for all of mine.
+__global__ void group_barrier_kernel(const PeerPtrs pp) {
+  const int epoch = pp.epoch + (pp.epoch_base ? *pp.epoch_base : 0);
+  const int r = threadIdx.x;
+  if (r < pp.n) {
+    __threadfence_system();
+    st_release_sys_i(pp.flags[r] + pp.rank, epoch);
+    spin_until(pp.flags[pp.rank] + r, epoch, pp.err, kErrWaitPeer);
+  }
+}
+
+// out[i] += sum over ranks r of ptr[r][i], i < n (fp32; peer loads).
+__global__ void __launch_bounds__(256) peer_sum_kernel(float* __restrict__ out, int n, const PeerPtrs pp) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float t = 0.0f;
+  for (int r = 0; r < pp.n; ++r) t += __ldcg(static_cast<const float*>(pp.ptr[r]) + i);
+  out[i] += t;
+}
+
+static bool make_peer_ptrs(PeerPtrs* pp, void* const* ptrs, int* const* flag_ptrs, int n, int rank,
+                           int epoch, const int* epoch_base, int* counter, int* err) {
+  if (n < 1 || n > kMaxDp || rank < 0 || rank >= n) return false;
+  for (int i = 0; i < kMaxDp; ++i) {
+    pp->ptr[i] = (ptrs && i < n) ? ptrs[i] : nullptr;
+    pp->flags[i] = (flag_ptrs && i < n) ? flag_ptrs[i] : nullptr;
+  }
+  pp->n = n; pp->rank = rank; pp->epoch = epoch; pp->epoch_base = epoch_base; pp->counter = counter;
+  pp->err = err;
+  return true;
+}
+
+}  // namespace tp
+
+// All-gather by push: `bytes` (a multiple of 16) at `src` in this rank's buffer go to dst_ptrs[r]
+// for every other rank r, then flag_ptrs[r][rank] = epoch + *epoch_base.  Consumer: tp_gemm_ag.
+extern "C" int tp_ag_push(const void* src, long long bytes, void* const* dst_ptrs, int* const* flag_ptrs,
+                          int n, int rank, int epoch, const int* epoch_base, int* counter, void* stream) {
+  if (bytes <= 0 || bytes % 16 || !dst_ptrs || !flag_ptrs || !counter) return kErrBadArgument;
+  PeerPtrs pp;
+  if (!make_peer_ptrs(&pp, dst_ptrs, flag_ptrs, n, rank, epoch, epoch_base, counter, nullptr))
+    return kErrBadArgument;
+  const long long n_vec = bytes / 16;
+  long long blocks = (n_vec + 255) / 256;
+  if (blocks > 2ll * num_sms()) blocks = 2ll * num_sms();
+  ag_push_kernel<<<static_cast<int>(blocks), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), n_vec, pp);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// Device-side barrier of a tensor-parallel group between steps: flag_ptrs[r] is rank r's barrier
+// flag array (n ints), epoch + *epoch_base must grow from call to call.  A wait that runs out
+// writes kErrWaitPeer to *err.
+extern "C" int tp_group_barrier(int* const* flag_ptrs, int n, int rank, int epoch, const int* epoch_base,
+                                int* err, void* stream) {
+  if (!flag_ptrs) return kErrBadArgument;
+  PeerPtrs pp;
+  if (!make_peer_ptrs(&pp, nullptr, flag_ptrs, n, rank, epoch, epoch_base, nullptr, err))
+    return kErrBadArgument;
+  group_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pp);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// out[i] += sum_r src_ptrs[r][i] for i < n floats (src_ptrs[r]: the same region of every rank's
+// peer-mapped buffer, complete on every rank: call tp_group_barrier first).
+extern "C" int tp_peer_sum(float* out, int n, void* const* src_ptrs, int n_ranks, int rank, void* stream) {
+  if (n <= 0 || !src_ptrs) return kErrBadArgument;
+  PeerPtrs pp;
+  if (!make_peer_ptrs(&pp, src_ptrs, nullptr, n_ranks, rank, 0, nullptr, nullptr, nullptr))
+    return kErrBadArgument;
+  peer_sum_kernel<<<(n + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(out, n, pp);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
 // Limit of every bounded device-side wait of this library (mbarrier, peer flags), on the current
 // device; the default is 2 s.  Call it with no kernel of the library in flight.
 TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_comm)

@@ -12,6 +12,38 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
+// Output fan-out of the LayerNorm kernels under sequence-parallel tensor parallelism: the kernel
+// runs on this rank's token shard and stores each output row at the same offset into the buffer
+// of EVERY rank of the group (dst[0..n); plain peer stores over NVLink for the others), which is
+// the all-gather the following column-parallel GEMM needs.  When all CTAs are done, the last one
+// raises flags[r][rank] = epoch + *epoch_base at every other rank r; the consumer (tp_gemm_ag)
+// waits for that value.  n == 1 and flags unset: an ordinary single-destination kernel.
+constexpr int kMaxPush = 8;
+struct PushDst {
+  void* dst[kMaxPush];
+  int* flags[kMaxPush];
+  int n, rank, epoch;
+  const int* epoch_base;
+  int* counter;   // zero between launches; counts finished CTAs
+};
+
+__device__ __forceinline__ void push_signal(const PushDst& pd) {
+  if (pd.n <= 1 || pd.counter == nullptr) return;
+  __threadfence_system();   // this thread's peer stores are visible system-wide
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned total = gridDim.x * gridDim.y;
+    if (atomicAdd(reinterpret_cast<unsigned*>(pd.counter), 1u) == total - 1) {
+      *pd.counter = 0;
+      const int epoch = pd.epoch + (pd.epoch_base ? *pd.epoch_base : 0);
+      __threadfence_system();
+      for (int r = 0; r < pd.n; ++r)
+        if (r != pd.rank)
+          asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(pd.flags[r] + pd.rank), "r"(epoch) : "memory");
+    }
+  }
+}
+
 // Sum over the CTA; every thread gets the result.  `red` holds >= 33 floats.
 __device__ __forceinline__ float block_sum(float v, float* red) {
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
@@ -74,7 +106,7 @@ __device__ __forceinline__ float group_sum(float v, float* red, int slot, int gr
 template <typename T, int NV, int WPR>
 __global__ void __launch_bounds__(LnGeom<WPR>::kThreads)
 layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
-                     const T* __restrict__ beta, T* __restrict__ y, float* __restrict__ mean_out,
+                     const T* __restrict__ beta, const PushDst pd, float* __restrict__ mean_out,
                      float* __restrict__ rstd_out, int rows, int H, float eps) {
   using G = LnGeom<WPR>;
   __shared__ float red[2 * G::kRowsPerCta * WPR + 1];
@@ -109,23 +141,25 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
     }
   }
   const float rstd = rsqrtf(group_sum<WPR>(q, red, 1, grp, wr, lane) / H + eps);
-  if (!row_ok) return;
-  if (wr == 0 && lane == 0) {
-    mean_out[row] = mean;
-    rstd_out[row] = rstd;
-  }
+  if (row_ok) {
+    if (wr == 0 && lane == 0) {
+      mean_out[row] = mean;
+      rstd_out[row] = rstd;
+    }
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int col = ((i * WPR + wr) * 32 + lane) * 8;
-    if (col < H) {
-      float g[8], b[8], o[8];
-      load8(gamma + col, g);
-      load8(beta + col, b);
+    for (int i = 0; i < NV; ++i) {
+      const int col = ((i * WPR + wr) * 32 + lane) * 8;
+      if (col < H) {
+        float g[8], b[8], o[8];
+        load8(gamma + col, g);
+        load8(beta + col, b);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
-      store8(y + row * H + col, o);
+        for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
+        for (int d = 0; d < pd.n; ++d) store8(static_cast<T*>(pd.dst[d]) + row * H + col, o);
+      }
     }
   }
+  push_signal(pd);
 }
 
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ dres), g = dy * gamma.
@@ -137,7 +171,7 @@ template <typename T, int NV, int WPR>
 __global__ void __launch_bounds__(LnGeom<WPR>::kThreads)
 layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                      const float* __restrict__ mean, const float* __restrict__ rstd,
-                     const T* __restrict__ gamma, const T* __restrict__ dres, T* __restrict__ dx,
+                     const T* __restrict__ gamma, const T* __restrict__ dres, const PushDst pd,
                      float* __restrict__ scratch, int rows, int H, int accumulate_slots) {
   using G = LnGeom<WPR>;
   extern __shared__ float part_smem[];  // [2][H]
@@ -194,7 +228,7 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
 #pragma unroll
             for (int j = 0; j < 8; ++j) o[j] += r[j];
           }
-          store8(dx + row * H + col, o);
+          for (int d = 0; d < pd.n; ++d) store8(static_cast<T*>(pd.dst[d]) + row * H + col, o);
         }
       }
     }
@@ -236,11 +270,13 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
     }
     __stcg(reinterpret_cast<float4*>(sg + c), v);
   }
+  push_signal(pd);
 }
 
 // dgamma[c] += sum_p scratch[p][0][c]; dbeta[c] += sum_p scratch[p][1][c]; optionally clears the
 // slots afterwards.  blockDim = (32, 8): 32 columns per CTA, 8 lanes over the slots (4 loads in
 // flight per thread), fixed-order tree in shared memory.
+// clear bit 0: zero the slots afterwards; bit 1: overwrite dgamma/dbeta instead of adding.
 __global__ void layernorm_bwd_reduce_kernel(float* __restrict__ scratch, int parts, int H,
                                             float* __restrict__ dgamma, float* __restrict__ dbeta,
                                             int clear) {
@@ -257,7 +293,7 @@ __global__ void layernorm_bwd_reduce_kernel(float* __restrict__ scratch, int par
       s3 += __ldcg(scratch + (p + 24) * stride + c);
     }
     for (; p < parts; p += 8) s0 += __ldcg(scratch + p * stride + c);
-    if (clear)
+    if (clear & 1)
       for (int q = threadIdx.y; q < parts; q += 8) scratch[q * stride + c] = 0.0f;
   }
   sm[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
@@ -266,8 +302,13 @@ __global__ void layernorm_bwd_reduce_kernel(float* __restrict__ scratch, int par
     float t = 0.0f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) t += sm[i][threadIdx.x];
-    if (c < H) dgamma[c] += t;
-    else dbeta[c - H] += t;
+    if (clear & 2) {
+      if (c < H) dgamma[c] = t;
+      else dbeta[c - H] = t;
+    } else {
+      if (c < H) dgamma[c] += t;
+      else dbeta[c - H] += t;
+    }
   }
 }
 
@@ -390,22 +431,64 @@ static inline bool ln_geometry(int H, int* nv, int* wpr) {
     default: TP_LN_DISPATCH_WPR(T, 4, CALL) break;        \
   }
 
-extern "C" int tp_layernorm_fwd(int dtype, const void* x, const void* gamma, const void* beta,
-                                void* y, float* mean, float* rstd, int rows, int H, float eps,
-                                void* stream) {
+namespace tp {
+static PushDst single_dst(void* y) {
+  PushDst pd;
+  for (int i = 0; i < kMaxPush; ++i) { pd.dst[i] = nullptr; pd.flags[i] = nullptr; }
+  pd.dst[0] = y;
+  pd.n = 1; pd.rank = 0; pd.epoch = 0; pd.epoch_base = nullptr; pd.counter = nullptr;
+  return pd;
+}
+
+static bool make_push(PushDst* pd, void* const* dst_ptrs, int* const* flag_ptrs, int n, int rank,
+                      int epoch, const int* epoch_base, int* counter) {
+  if (n < 1 || n > kMaxPush || rank < 0 || rank >= n || !dst_ptrs || !flag_ptrs || !counter) return false;
+  for (int i = 0; i < kMaxPush; ++i) {
+    pd->dst[i] = i < n ? dst_ptrs[i] : nullptr;
+    pd->flags[i] = i < n ? flag_ptrs[i] : nullptr;
+  }
+  pd->n = n; pd->rank = rank; pd->epoch = epoch; pd->epoch_base = epoch_base; pd->counter = counter;
+  return true;
+}
+
+static int layernorm_fwd_launch(int dtype, const void* x, const void* gamma, const void* beta,
+                                const PushDst& pd, float* mean, float* rstd, int rows, int H,
+                                float eps, cudaStream_t s) {
   if (rows <= 0) return kOk;
   int nv, wpr;
   if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define LN_FWD(T, NV, WPR)                                                                       \
   layernorm_fwd_kernel<T, NV, WPR>                                                               \
       <<<(rows + LnGeom<WPR>::kRowsPerCta - 1) / LnGeom<WPR>::kRowsPerCta, LnGeom<WPR>::kThreads, \
          0, s>>>(static_cast<const T*>(x), static_cast<const T*>(gamma),                         \
-                 static_cast<const T*>(beta), static_cast<T*>(y), mean, rstd, rows, H, eps)
+                 static_cast<const T*>(beta), pd, mean, rstd, rows, H, eps)
   if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_FWD) }
   else { TP_LN_DISPATCH(__half, LN_FWD) }
 #undef LN_FWD
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+}  // namespace tp
+
+extern "C" int tp_layernorm_fwd(int dtype, const void* x, const void* gamma, const void* beta,
+                                void* y, float* mean, float* rstd, int rows, int H, float eps,
+                                void* stream) {
+  return layernorm_fwd_launch(dtype, x, gamma, beta, single_dst(y), mean, rstd, rows, H, eps,
+                              static_cast<cudaStream_t>(stream));
+}
+
+// LayerNorm forward of this rank's token shard whose output rows go to the same place in the
+// buffer of every rank of a tensor-parallel group (`y_ptrs[r]`, r < n; entry `rank` is the local
+// buffer), followed by a flag at every peer: flag_ptrs[r][rank] = epoch + *epoch_base.
+// `counter` is a zero-initialised device int used to find the last CTA.  The consumer is
+// tp_gemm_ag with the same epoch.
+extern "C" int tp_layernorm_fwd_push(int dtype, const void* x, const void* gamma, const void* beta,
+                                     void* const* y_ptrs, float* mean, float* rstd, int rows, int H,
+                                     float eps, int n, int rank, int* const* flag_ptrs, int epoch,
+                                     const int* epoch_base, int* counter, void* stream) {
+  PushDst pd;
+  if (!make_push(&pd, y_ptrs, flag_ptrs, n, rank, epoch, epoch_base, counter)) return kErrBadArgument;
+  return layernorm_fwd_launch(dtype, x, gamma, beta, pd, mean, rstd, rows, H, eps,
+                              static_cast<cudaStream_t>(stream));
 }
 
 // Number of CTA slots the backward writes; scratch must hold parts * 2 * H floats.
@@ -430,9 +513,9 @@ static int ln_parts(int rows, int wpr) {
 // mode 1: ADD the CTA partials into the persistent slots `scratch` (zero-initialised by the
 //         caller) and leave dgamma/dbeta alone; tp_layernorm_bwd_finish folds them later.
 static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const float* mean,
-                                const float* rstd, const void* gamma, const void* dres, void* dx,
-                                float* dgamma, float* dbeta, float* scratch, int rows, int H,
-                                int mode, cudaStream_t s) {
+                                const float* rstd, const void* gamma, const void* dres,
+                                const PushDst& pd, float* dgamma, float* dbeta, float* scratch,
+                                int rows, int H, int mode, cudaStream_t s) {
   if (rows <= 0) return kOk;
   int nv, wpr;
   if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
@@ -444,7 +527,7 @@ static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const 
     if (smem > 48 * 1024) ln_allow_smem(kern);                                                  \
     kern<<<parts, LnGeom<WPR>::kThreads, smem, s>>>(                                            \
         static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                        \
-        static_cast<const T*>(gamma), static_cast<const T*>(dres), static_cast<T*>(dx), scratch, \
+        static_cast<const T*>(gamma), static_cast<const T*>(dres), pd, scratch,                  \
         rows, H, mode);                                                                         \
   }
   if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_BWD) }
@@ -461,8 +544,8 @@ extern "C" int tp_layernorm_bwd(int dtype, const void* dy, const void* x, const 
                                 const float* rstd, const void* gamma, const void* dres, void* dx,
                                 float* dgamma, float* dbeta, float* scratch, int rows, int H,
                                 void* stream) {
-  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, dx, dgamma, dbeta, scratch,
-                              rows, H, 0, static_cast<cudaStream_t>(stream));
+  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, single_dst(dx), dgamma, dbeta,
+                              scratch, rows, H, 0, static_cast<cudaStream_t>(stream));
 }
 
 // Variant that only accumulates into persistent partial slots (tp_layernorm_bwd_parts(rows)
@@ -470,8 +553,21 @@ extern "C" int tp_layernorm_bwd(int dtype, const void* dy, const void* x, const 
 extern "C" int tp_layernorm_bwd_accum(int dtype, const void* dy, const void* x, const float* mean,
                                       const float* rstd, const void* gamma, const void* dres,
                                       void* dx, float* slots, int rows, int H, void* stream) {
-  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, dx, nullptr, nullptr, slots,
-                              rows, H, 1, static_cast<cudaStream_t>(stream));
+  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, single_dst(dx), nullptr, nullptr,
+                              slots, rows, H, 1, static_cast<cudaStream_t>(stream));
+}
+
+// tp_layernorm_bwd_accum on this rank's token shard with the input gradient rows stored into the
+// buffer of every rank of the group and a flag raised at every peer (see tp_layernorm_fwd_push).
+extern "C" int tp_layernorm_bwd_accum_push(int dtype, const void* dy, const void* x, const float* mean,
+                                           const float* rstd, const void* gamma, const void* dres,
+                                           void* const* dx_ptrs, float* slots, int rows, int H, int n,
+                                           int rank, int* const* flag_ptrs, int epoch,
+                                           const int* epoch_base, int* counter, void* stream) {
+  PushDst pd;
+  if (!make_push(&pd, dx_ptrs, flag_ptrs, n, rank, epoch, epoch_base, counter)) return kErrBadArgument;
+  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, pd, nullptr, nullptr, slots, rows,
+                              H, 1, static_cast<cudaStream_t>(stream));
 }
 
 // Fold `parts` slots into dgamma/dbeta (+=) and clear them for the next backward pass.
@@ -479,6 +575,15 @@ extern "C" int tp_layernorm_bwd_finish(float* slots, int parts, int H, float* dg
                                        void* stream) {
   layernorm_bwd_reduce_kernel<<<(2 * H + 31) / 32, dim3(32, 8), 0, static_cast<cudaStream_t>(stream)>>>(
       slots, parts, H, dgamma, dbeta, 1);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
+// As tp_layernorm_bwd_finish, but dgamma/dbeta are overwritten with the folded sums (used when the
+// sums of several ranks are added up afterwards, see tp_peer_sum).
+extern "C" int tp_layernorm_bwd_finish_assign(float* slots, int parts, int H, float* dgamma,
+                                              float* dbeta, void* stream) {
+  layernorm_bwd_reduce_kernel<<<(2 * H + 31) / 32, dim3(32, 8), 0, static_cast<cudaStream_t>(stream)>>>(
+      slots, parts, H, dgamma, dbeta, 3);
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
@@ -572,6 +677,6 @@ extern "C" int tp_layernorm_bwd_noalloc(int dtype, const void* dy, const void* x
     scratch_of_device[dev] = p;
   }
   // mode 0 writes every slot it later reads, so stale contents of the shared array are harmless
-  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, dx, dgamma, dbeta,
+  return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, single_dst(dx), dgamma, dbeta,
                               scratch_of_device[dev], rows, H, 0, static_cast<cudaStream_t>(stream));
 }

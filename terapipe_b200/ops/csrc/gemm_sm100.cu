@@ -40,6 +40,17 @@ namespace tp {
 struct GemmParams {
   int M, N, K;
   int num_m_tiles, num_tiles;
+  // CTA-pair kernel: tile order.  m_major = 0: consecutive tiles walk down a column of the output
+  // (tile -> m = tile % num_m_tiles); m_major = 1: they walk along a row block, and the row
+  // blocks are visited starting at m_first and wrapping around (used to put the row blocks whose
+  // operands or results live on this rank first or last).
+  int num_n_tiles, m_major, m_first;
+  // All-gather wait (CTA-pair kernel, A stored [M][K]): rows [s * ag_rows, (s + 1) * ag_rows) of A
+  // were written into this GPU's memory by rank s; before loading rows of another rank the
+  // producer waits until ag_flags[s] >= ag_epoch + *ag_epoch_base.  ag_flags == nullptr: no wait.
+  const int* ag_flags;
+  const int* ag_epoch_base;
+  int ag_epoch, ag_rows, ag_rank;
   void* out;
   long long ldo;
   const void* bias;
@@ -69,6 +80,7 @@ struct ArParams {
   int max_tiles;                 // capacity of the staging / flag arrays, in tiles
   int exchange;                  // CTA-pair kernel: every rank receives every partial tile and
                                  // reduces it itself (one NVLink hop instead of two)
+  int rows_per_rank;             // reduce-scatter kernel: rank s owns rows [s * rows_per_rank, ...)
   long long* dbg;                // optional: 8 globaltimer stamps per CTA (see tp_gemm_ar_set_debug)
   void* stage[kMaxTp];           // per rank: [2 halves][tp sources][max_tiles][128][BN] 16-bit partials
                                  // (the second half is used by exchange mode only)
@@ -352,6 +364,49 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtens
   }
 }
 
+// Reduce-scatter: add the 16-bit partial results that the other ranks stored in this rank's
+// staging buffer to the fp32 accumulators of one 32-column chunk (thread = row).  `part` points at
+// this thread's 32 values (64 contiguous bytes) in source 0's copy of the chunk; the copies of
+// the sources are `stride` elements apart; source `self` is the accumulator itself.
+template <typename T>
+__device__ __forceinline__ void add_partials(uint32_t (&r)[32], const T* part, long long stride,
+                                             int n_src, int self) {
+  const uint4 zero4 = make_uint4(0, 0, 0, 0);
+#pragma unroll 1
+  for (int s0 = 0; s0 < n_src; s0 += 2) {
+    const bool ua = s0 != self, ub = (s0 + 1 < n_src) && (s0 + 1 != self);
+    uint4 a[4], b[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      a[g] = ua ? __ldcg(reinterpret_cast<const uint4*>(part + s0 * stride + g * 8)) : zero4;
+      b[g] = ub ? __ldcg(reinterpret_cast<const uint4*>(part + (s0 + 1) * stride + g * 8)) : zero4;
+    }
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t aw[4] = {a[g].x, a[g].y, a[g].z, a[g].w};
+      const uint32_t bw[4] = {b[g].x, b[g].y, b[g].z, b[g].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = Elem<T>::unpack2(aw[j]);
+        const float2 fb = Elem<T>::unpack2(bw[j]);
+        r[g * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j]) + (fa.x + fb.x));
+        r[g * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j + 1]) + (fa.y + fb.y));
+      }
+    }
+  }
+}
+
+// Output-tile coordinates of the CTA-pair kernel (see GemmParams::m_major).
+__device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int& m_idx, int& n_idx) {
+  if (p.m_major) {
+    n_idx = tile % p.num_n_tiles;
+    m_idx = (tile / p.num_n_tiles + p.m_first) % p.num_m_tiles;
+  } else {
+    m_idx = tile % p.num_m_tiles;
+    n_idx = tile / p.num_m_tiles;
+  }
+}
+
 // Epilogue of one warp's 32 rows over `nc` 32-column chunks of an accumulator at TMEM address
 // `t_acc` (lane quarter already applied); the warp takes chunks c_first, c_first + c_step, ...
 // The chunk code exists once (it is large); the TMEM
@@ -361,7 +416,8 @@ template <typename T, bool OUT_F32, bool TRACE = false>
 __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtensorMap* tmO,
                                               EpiStage& es, uint32_t t_acc, int nc, int row0, int n0,
                                               int lane, int c_first = 0, int c_step = 1,
-                                              long long* cyc = nullptr) {
+                                              long long* cyc = nullptr, const T* part = nullptr,
+                                              long long part_stride = 0, int n_src = 0, int self = 0) {
   const long long row = row0 + lane;
   const bool row_ok = row < p.M;
   uint32_t r[32];
@@ -398,6 +454,7 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtenso
 #pragma unroll 1
   for (int c = c_first; c < nc; c += c_step) {
     tmem_ld_wait();
+    if (part) add_partials<T>(r, part + c * 4096, part_stride, n_src, self);
     epilogue_chunk<T, OUT_F32, TRACE>(p, tmO, es, r, row, row_ok, n0 + c * 32, row0, lane,
                                       c + c_step < nc ? t_acc + (c + c_step) * 32 : 0u, cyc);
   }
@@ -693,7 +750,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR, MT>;
   ArParams ar;
   if (arp) ar = *arp;
-  else { ar.tp = 0; ar.exchange = 0; ar.dbg = nullptr; }
+  else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; ar.dbg = nullptr; }
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -858,11 +915,24 @@ __device__ __forceinline__ void ar_reduce_tile(const GemmParams& p, const ArPara
 // buffer a tile is stored as 16 blocks [column chunk c][lane quarter q] of [32 rows][32 columns];
 // an epilogue warp produces exactly one such 2 KB block per chunk and copies it with fully
 // coalesced 16-byte peer stores.
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false, bool AR = false>
-__global__ void __launch_bounds__(kPairThreads, 1)
+//
+// RS = true fuses a reduce-scatter over the rows instead: rank s ends with rows
+// [s * rows_per_rank, (s + 1) * rows_per_rank) of the summed product (rows_per_rank a multiple of
+// 32).  An epilogue warp whose 32 rows belong to another rank pushes its chunks to that rank's
+// staging buffer exactly as in phase A above; an extra warp (warp 10) publishes a 128-row block
+// once all eight epilogue warps have stored their part, so no epilogue warp ever waits for the
+// NVLink round trip of a system-scope release.  A warp whose rows belong to this rank waits for
+// the other ranks' partials of its block and adds them, in fp32, to its accumulator inside the
+// regular epilogue (bias, residual, staged TMA store).  With m_major tile order and the row
+// blocks of this rank visited last, the partials have arrived long before they are needed and
+// nothing follows the last tile: no second hop, no result flags.
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false, bool AR = false,
+          bool RS = false>
+__global__ void __launch_bounds__(kPairThreads + (RS ? 32 : 0), 1)
 gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
                  const __grid_constant__ CUtensorMap tmO, const GemmParams p, const ArParams ar) {
   static_assert(!AR || (BN == 128 && !OUT_F32 && !TRACE), "fused all-reduce: 256 x 128 pair tiles, 16-bit output");
+  static_assert(!RS || (BN == 128 && !OUT_F32 && !TRACE && !AR && !A_MN), "fused reduce-scatter: 256 x 128 pair tiles, 16-bit output");
   using Cfg = PairCfg<BN>;
   constexpr int S = Cfg::kStages;
   constexpr int HB = BN / 2;  // B rows held by one CTA
@@ -879,6 +949,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   volatile int* s_ready = reinterpret_cast<volatile int*>(tmem_slot + 2);  // AR: owned tile ready?
   volatile int* s_next = reinterpret_cast<volatile int*>(tmem_slot + 3);   // AR: next owned tile
+  uint64_t* pub_full = bars + 2 * S + 6;                                    // RS: block stored by all warps
+  volatile int* pub_done = reinterpret_cast<volatile int*>(bars + 2 * S + 8);  // RS: blocks published
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -903,6 +975,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     *abort_flag = 0;
     *s_ready = 0;
     *s_next = (AR && ar.exchange) ? 0 : static_cast<int>(blockIdx.x);
+    if (RS) {
+      mbar_init(&pub_full[0], kPairEpiWarps);
+      mbar_init(&pub_full[1], kPairEpiWarps);
+      *pub_done = 0;
+    }
     fence_barrier_init();
     prefetch_tmap(&tmA);
     prefetch_tmap(&tmB);
@@ -913,7 +990,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // The producer warp starts loading at once; the other five warps meet again after the TMEM
   // allocation (named barrier 1, 288 threads).
   uint32_t tmem_base = 0;
-  if (warp >= 1) {
+  if (warp >= 1 && warp < 10) {
     if (warp == 1) {
       tmem_alloc_pair(tmem_slot, Cfg::kTmemCols);
       tmem_relinquish_pair();
@@ -924,12 +1001,13 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     tmem_base = *tmem_slot;
   }
   const int num_kb = (p.K + kBK - 1) / kBK;
-  const int ar_epoch = AR ? (ar.epoch + (ar.epoch_base ? *ar.epoch_base : 0)) : 0;
+  const int ar_epoch = (AR || RS) ? (ar.epoch + (ar.epoch_base ? *ar.epoch_base : 0)) : 0;
   const int num_m128 = (p.M + kBM - 1) / kBM;  // AR: 128-row tiles of the output
-  // Exchange mode has no hand-shake after the reduction, so a rank may start its next call
-  // while a peer still reads this call's partials: calls alternate between two staging halves.
+  // Exchange mode and the reduce-scatter have no hand-shake after the reduction, so a rank may
+  // start its next call while a peer still reads this call's partials: calls alternate between
+  // two staging halves.
   const long long stage_half =
-      (AR && ar.exchange && (ar_epoch & 1)) ? static_cast<long long>(ar.tp) * ar.max_tiles * (kBM * BN) : 0;
+      (((AR && ar.exchange) || RS) && (ar_epoch & 1)) ? static_cast<long long>(ar.tp) * ar.max_tiles * (kBM * BN) : 0;
   if (TRACE && threadIdx.x == 0) tr[1] = clock64();
 
   if (warp == 0) {
@@ -938,9 +1016,27 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       uint32_t phase = 0;
       bool ok = true;
       long long stall = 0;
+      unsigned ag_seen = 0;  // ranks whose rows are known to have arrived
       for (int tile = pair; tile < p.num_tiles && ok; tile += npairs) {
-        const int m0 = (tile % p.num_m_tiles) * (2 * kBM) + static_cast<int>(cta) * kBM;
-        const int n0 = (tile / p.num_m_tiles) * BN + static_cast<int>(cta) * HB;
+        int m_idx, n_idx;
+        pair_tile_coords(p, tile, m_idx, n_idx);
+        const int m0 = m_idx * (2 * kBM) + static_cast<int>(cta) * kBM;
+        const int n0 = n_idx * BN + static_cast<int>(cta) * HB;
+        if (!A_MN && p.ag_flags != nullptr && m0 < p.M) {
+          const int last_row = min(m0 + kBM, p.M) - 1;
+          const int target = p.ag_epoch + (p.ag_epoch_base ? *p.ag_epoch_base : 0);
+          bool waited = false;
+          for (int src = m0 / p.ag_rows; src <= last_row / p.ag_rows && ok; ++src) {
+            if (src == p.ag_rank || (ag_seen >> src) & 1u) continue;
+            ok = wait_flag(p.ag_flags + src, target, wctx, kErrWaitPeer);
+            ag_seen |= 1u << src;
+            waited = true;
+          }
+          if (!ok) break;
+          // the rows were written by generic-proxy stores of another GPU; the loads below go
+          // through the async proxy
+          if (waited) asm volatile("fence.proxy.async.global;" ::: "memory");
+        }
         for (int kb = 0; kb < num_kb; ++kb) {
           const long long t_w = TRACE ? clock64() : 0;
           ok = mbar_wait(&empty[stage], phase ^ 1, wctx, kErrWaitProducer);
@@ -1032,7 +1128,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (TRACE) { tr[5] = stall_full; tr[6] = stall_acc; tr[7] = clock64(); tr[8] = it; }
       if (AR && dbg) dbg[7] = static_cast<long long>(globaltimer_ns());
     }
-  } else {
+  } else if (warp < 10) {
     const int quarter = warp & 3;      // TMEM lane quarter this warp may access
     const int half = (warp - 2) >> 2;  // which of the two warps of that quarter
     EpiStage es{epi_smem + (warp - 2) * kEpiBytesPerWarp, 0};
@@ -1050,8 +1146,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
-      const int m0 = (tile % p.num_m_tiles) * (2 * kBM) + static_cast<int>(cta) * kBM;
-      const int n0 = (tile / p.num_m_tiles) * BN;
+      int m_idx, n_idx;
+      pair_tile_coords(p, tile, m_idx, n_idx);
+      const int m0 = m_idx * (2 * kBM) + static_cast<int>(cta) * kBM;
+      const int n0 = n_idx * BN;
       const long long t_e = TRACE ? clock64() : 0;
       ok = mbar_wait(&tfull[acc], acc_phase, wctx, kErrWaitEpilogue);
       if (!ok) break;
@@ -1063,10 +1161,84 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       tc_fence_after();
       const int row0 = m0 + quarter * 32;
+      if (RS) {
+        const int unit = m0 / kBM + n_idx * num_m128;   // 128-row block x column tile
+        const int owner = min(row0 / ar.rows_per_rank, ar.tp - 1);
+        const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
+        const long long tile_elems = kBM * BN;
+        if (row0 < p.M && owner == ar.rank) {
+          // rows of this rank: the other ranks' partials join the accumulator in the epilogue
+          int got = 1;
+          if (lane == 0) {
+            for (int src = 0; src < ar.tp && got; ++src)
+              if (src != ar.rank)
+                got = wait_flag(ar.flag_a[ar.rank] + static_cast<long long>(unit) * kMaxTp + src, ar_epoch,
+                                wctx, kErrWaitPeer) ? 1 : 0;
+          }
+          got = __shfl_sync(0xffffffffu, got, 0);
+          const T* part = static_cast<const T*>(ar.stage[ar.rank]) + stage_half + unit * tile_elems +
+                          quarter * 1024 + lane * 32;
+          const int nc = (min(BN, p.N - n0) + 31) / 32;
+          epilogue_rows<T, OUT_F32, false>(p, &tmO, es, t_acc, nc, row0, n0, lane, half, 2, nullptr,
+                                           got ? part : nullptr, ar.max_tiles * tile_elems, ar.tp, ar.rank);
+        } else if (row0 < p.M) {
+          // rows of another rank: 16-bit partial chunks into its staging buffer
+          if (es.issued > 0) {          // the buffers may still be read by earlier tile stores
+            if (lane == 0) bulk_wait_read<0>();
+            __syncwarp();
+          }
+          T* dst = static_cast<T*>(ar.stage[owner]) + stage_half +
+                   (static_cast<long long>(ar.rank) * ar.max_tiles + unit) * tile_elems + quarter * 1024;
+#pragma unroll 1
+          for (int c = half; c < BN / 32; c += 2) {
+            uint32_t r[32];
+            __syncwarp();
+            tmem_ld_32x32(t_acc + c * 32, r);
+            tmem_ld_wait();
+            uint8_t* sb = es.buf + (c & 2 ? 2048 : 0);
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 ov;
+              ov.x = Elem<T>::pack2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+              ov.y = Elem<T>::pack2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+              ov.z = Elem<T>::pack2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+              ov.w = Elem<T>::pack2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+              *reinterpret_cast<uint4*>(sb + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) = ov;
+            }
+            __syncwarp();
+            uint4* blk = reinterpret_cast<uint4*>(dst + c * 4096);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const int piece = lane + 32 * k;
+              const int rr = piece >> 2, part = piece & 3;
+              blk[piece] = *reinterpret_cast<const uint4*>(sb + rr * 64 + ((part ^ ((rr >> 1) & 3)) << 4));
+            }
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
+          // hand the block to the publishing warp; it keeps at most two blocks outstanding
+          if (it >= 2) {
+            unsigned spins = 0;
+            unsigned long long t0 = 0;
+            while (*pub_done < it - 1 && !*abort_flag) {
+              if ((++spins & 0xFF) == 0) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > g_wait_limit_ns) { report_timeout(wctx, kErrWaitEpilogue); break; }
+              }
+            }
+          }
+          mbar_arrive(&pub_full[it & 1]);
+        }
+        continue;
+      }
       if (AR) {
         // phase A: this warp's chunks of the partial tile go to the owner's staging buffer
         const int m128 = m0 / kBM;
-        const int ar_tile = m128 + (tile / p.num_m_tiles) * num_m128;
+        const int ar_tile = m128 + n_idx * num_m128;
         const bool in_range = m128 < num_m128;  // M may end inside the pair tile (warp-uniform)
         const int owner = ar_tile % ar.tp;
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
@@ -1193,6 +1365,42 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   }
 
+  if (RS && warp == 10 && lane == 0) {
+    // publishing warp: after all eight epilogue warps have stored their part of a 128-row block,
+    // make the stores visible system-wide and raise the block's flag at every rank that owns rows
+    // of it.  The release fence waits for the NVLink round trip; only this thread pays for it.
+    int it = 0;
+    bool ok = true;
+    for (int tile = pair; tile < p.num_tiles && ok; tile += npairs, ++it) {
+      int m_idx, n_idx;
+      pair_tile_coords(p, tile, m_idx, n_idx);
+      const int m0 = m_idx * (2 * kBM) + static_cast<int>(cta) * kBM;
+      ok = mbar_wait(&pub_full[it & 1], (it >> 1) & 1, wctx, kErrWaitEpilogue);
+      if (!ok) break;
+      if (m0 < p.M) {
+        const int unit = m0 / kBM + n_idx * num_m128;
+        int last = -1;
+        bool fenced = false;
+        for (int q = 0; q < 4; ++q) {
+          const int row0 = m0 + q * 32;
+          if (row0 >= p.M) break;
+          const int owner = min(row0 / ar.rows_per_rank, ar.tp - 1);
+          if (owner == ar.rank || owner == last) continue;
+          if (!fenced) {
+            __threadfence_system();
+            fenced = true;
+          }
+          asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(
+                           ar.flag_a[owner] + static_cast<long long>(unit) * kMaxTp + ar.rank),
+                       "r"(ar_epoch)
+                       : "memory");
+          last = owner;
+        }
+      }
+      *pub_done = it + 1;
+    }
+  }
+
   if (AR) {
     __syncthreads();
     __shared__ int s_ok;
@@ -1266,11 +1474,12 @@ static int max_pairs() {
   return cached[dev];
 }
 
-template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false, bool AR = false>
+template <typename T, int BN, bool A_MN, bool B_MN, bool OUT_F32, bool TRACE = false, bool AR = false,
+          bool RS = false>
 static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUtensorMap& tmO,
                             const GemmParams& p, cudaStream_t stream, const ArParams* arp = nullptr) {
   using Cfg = PairCfg<BN>;
-  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32, TRACE, AR>;
+  auto kern = gemm_pair_kernel<T, BN, A_MN, B_MN, OUT_F32, TRACE, AR, RS>;
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -1280,11 +1489,11 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   }
   ArParams ar;
   if (arp) ar = *arp;
-  else { ar.tp = 0; ar.exchange = 0; ar.dbg = nullptr; }
+  else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; ar.dbg = nullptr; }
   const int pairs = p.num_tiles < max_pairs() ? p.num_tiles : max_pairs();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(kPairThreads, 1, 1);
+  cfg.blockDim = dim3(kPairThreads + (RS ? 32 : 0), 1, 1);  // RS: one more warp publishes blocks
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = stream;
   cudaLaunchAttribute attr[1];
@@ -1352,11 +1561,22 @@ static int pick_tile(int M, int N, int K, int forced, bool allow_256x256, bool a
 
 }  // namespace tp
 
-extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const void* B,
-                       long long ldb, void* out, long long ldo, int out_f32, int accumulate, int M,
-                       int N, int K, float alpha, const void* bias, const void* residual,
-                       long long ldr, int act, void* aux_out, int dact, const void* aux_in,
-                       long long ld_aux, int force_bn, int* err_flag, void* stream) {
+namespace tp {
+// All-gather wait of a product whose A rows were pushed into this GPU's memory by the ranks of a
+// tensor-parallel group (see GemmParams::ag_flags).
+struct AgWait {
+  const int* flags;
+  const int* epoch_base;
+  int epoch, rows_per_rank, rank;
+};
+}  // namespace tp
+
+static int gemm_impl(int dtype, int a_mn, int b_mn, const void* A, long long lda, const void* B,
+                     long long ldb, void* out, long long ldo, int out_f32, int accumulate, int M,
+                     int N, int K, float alpha, const void* bias, const void* residual,
+                     long long ldr, int act, void* aux_out, int dact, const void* aux_in,
+                     long long ld_aux, int force_bn, int* err_flag, void* stream,
+                     const tp::AgWait* ag) {
   using namespace tp;
   if (M <= 0 || N <= 0 || K <= 0) return kErrBadArgument;
   if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % (out_f32 ? 4 : 8))) return kErrBadArgument;
@@ -1368,7 +1588,12 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   const bool common_layout = (!a_mn && !out_f32) || (a_mn && b_mn && out_f32);
   // only the three layouts of a Linear layer's forward / dgrad / wgrad products have the
   // 256-row tiles instantiated
-  const int tile_code = pick_tile(M, N, K, force_bn, common_layout, common_layout);
+  int tile_code = pick_tile(M, N, K, force_bn, common_layout, common_layout);
+  if (ag) {
+    // the wait lives in the CTA-pair kernel's producer
+    if (a_mn || !common_layout || ag->rows_per_rank <= 0) return kErrBadArgument;
+    if (tile_code < 1000) tile_code = (N % 256 == 0 && N >= 2048) ? 1256 : 1128;
+  }
   const bool pair = tile_code > 1000;
   const int BN = pair ? tile_code - 1000 : (tile_code == 512 ? 256 : tile_code);
   const int BM = (pair || tile_code == 512) ? 256 : kBM;   // rows of one output tile
@@ -1387,7 +1612,17 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.num_m_tiles = (M + BM - 1) / BM;
-  p.num_tiles = p.num_m_tiles * ((N + BN - 1) / BN);
+  p.num_n_tiles = (N + BN - 1) / BN;
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  p.m_major = 0; p.m_first = 0;
+  p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
+  if (ag) {
+    // row blocks of this rank first: their operands are local, the others are still arriving
+    p.m_major = 1;
+    p.m_first = static_cast<int>((static_cast<long long>(ag->rank) * ag->rows_per_rank) / BM) % p.num_m_tiles;
+    p.ag_flags = ag->flags; p.ag_epoch_base = ag->epoch_base; p.ag_epoch = ag->epoch;
+    p.ag_rows = ag->rows_per_rank; p.ag_rank = ag->rank;
+  }
   p.out = out; p.ldo = ldo;
   p.bias = bias; p.residual = residual; p.ldr = ldr;
   p.aux_out = aux_out; p.aux_in = aux_in; p.ld_aux = ld_aux;
@@ -1406,6 +1641,31 @@ extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long l
                : dispatch_layout<T, 64>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s))
   return bf16 ? TP_DISPATCH(__nv_bfloat16) : TP_DISPATCH(__half);
 #undef TP_DISPATCH
+}
+
+extern "C" int tp_gemm(int dtype, int a_mn, int b_mn, const void* A, long long lda, const void* B,
+                       long long ldb, void* out, long long ldo, int out_f32, int accumulate, int M,
+                       int N, int K, float alpha, const void* bias, const void* residual,
+                       long long ldr, int act, void* aux_out, int dact, const void* aux_in,
+                       long long ld_aux, int force_bn, int* err_flag, void* stream) {
+  return gemm_impl(dtype, a_mn, b_mn, A, lda, B, ldb, out, ldo, out_f32, accumulate, M, N, K, alpha,
+                   bias, residual, ldr, act, aux_out, dact, aux_in, ld_aux, force_bn, err_flag, stream,
+                   nullptr);
+}
+
+// All-gather -> GEMM: the same product as tp_gemm for A stored [M][K] whose rows
+// [s * rows_per_rank, (s + 1) * rows_per_rank) were written into this GPU's memory by rank s of a
+// tensor-parallel group (peer stores of the producing kernel, e.g. tp_layernorm_fwd_push).  The
+// kernel starts with the row blocks of rank `rank` and, before it loads rows of another rank s,
+// waits (bounded) until ag_flags[s] >= ag_epoch + *ag_epoch_base; it reads its own memory only.
+extern "C" int tp_gemm_ag(int dtype, int b_mn, const void* A, long long lda, const void* B,
+                          long long ldb, void* out, long long ldo, int M, int N, int K,
+                          const void* bias, int act, void* aux_out, int dact, const void* aux_in,
+                          long long ld_aux, const int* ag_flags, const int* ag_epoch_base, int ag_epoch,
+                          int rows_per_rank, int rank, int* err_flag, void* stream) {
+  tp::AgWait ag{ag_flags, ag_epoch_base, ag_epoch, rows_per_rank, rank};
+  return gemm_impl(dtype, 0, b_mn, A, lda, B, ldb, out, ldo, 0, 0, M, N, K, 1.0f, bias, nullptr, 0, act,
+                   aux_out, dact, aux_in, ld_aux, 0, err_flag, stream, ag_flags ? &ag : nullptr);
 }
 
 // Fused GEMM + tensor-parallel all-reduce (see the file comment).  `out_ptrs[r]` is the address
@@ -1431,7 +1691,10 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.num_m_tiles = (M + BM - 1) / BM;
-  p.num_tiles = p.num_m_tiles * ((N + BN - 1) / BN);
+  p.num_n_tiles = (N + BN - 1) / BN;
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  p.m_major = 0; p.m_first = 0;
+  p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   if (((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) > max_tiles) return kErrTooLarge;
   CUtensorMap tmA, tmB;
   if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16)) return kErrDriver;
@@ -1449,6 +1712,7 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
   ar.exchange = (g_pair_default && g_ar_exchange) ? 1 : 0;
+  ar.rows_per_rank = 0;
   ar.dbg = g_ar_debug;
   for (int i = 0; i < kMaxTp; ++i) {
     ar.stage[i] = i < tp ? stage_ptrs[i] : nullptr;
@@ -1470,6 +1734,70 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
                 : launch_gemm<__nv_bfloat16, BN, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
   return b_mn ? launch_gemm<__half, BN, false, true, false, true>(tmA, tmB, tmO, p, s, &ar)
               : launch_gemm<__half, BN, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
+}
+
+// Fused GEMM + tensor-parallel reduce-scatter over the rows (CTA-pair kernel, 256 x 128 tiles):
+// every rank computes its K shard of out = A * B^T (or A * B for b_mn) for all M rows; rank s ends
+// with rows [s * rows_per_rank, (s + 1) * rows_per_rank) of the sum, plus bias and residual, in
+// its own `out` (same row indices as the full matrix; other rows are not written).
+// rows_per_rank must be a multiple of 32; tiles are visited so that this rank's rows come last.
+// `stage_ptrs` / `flag_ptrs` are the staging and flag arrays of every rank as for tp_gemm_ar (two
+// staging halves, alternating with the call counter); epoch rules as for tp_gemm_ar.
+extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, const void* B,
+                          long long ldb, void* out, long long ldo, int M, int N, int K,
+                          const void* bias, const void* residual, long long ldr, int tp, int rank,
+                          int rows_per_rank, int epoch, const int* epoch_base, int max_tiles,
+                          void* const* stage_ptrs, int* const* flag_ptrs, int* err_flag, void* stream) {
+  using namespace tp;
+  if (M <= 0 || N <= 0 || K <= 0 || tp < 2 || tp > kMaxTp || rank < 0 || rank >= tp)
+    return kErrBadArgument;
+  if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 8) || rows_per_rank <= 0 || (rows_per_rank % 32))
+    return kErrBadArgument;
+  if (static_cast<long long>(rows_per_rank) * tp < M) return kErrBadArgument;
+  constexpr int BN = 128;
+  const bool bf16 = dtype == 1;
+  GemmParams p;
+  p.M = M; p.N = N; p.K = K;
+  p.num_m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
+  p.num_n_tiles = (N + BN - 1) / BN;
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  if (((M + kBM - 1) / kBM) * p.num_n_tiles > max_tiles) return kErrTooLarge;
+  // row blocks of the next rank first, this rank's own rows last
+  p.m_major = 1;
+  {
+    const long long first_after = static_cast<long long>(rank + 1) * rows_per_rank;
+    p.m_first = first_after >= M ? 0 : static_cast<int>((first_after + 2 * kBM - 1) / (2 * kBM)) % p.num_m_tiles;
+  }
+  p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
+  CUtensorMap tmA, tmB, tmO;
+  if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16)) return kErrDriver;
+  if (!(b_mn ? make_tmap_2d(&tmB, B, N, K, ldb, 64, kBK, bf16)
+             : make_tmap_2d(&tmB, B, K, N, ldb, kBK, BN / 2, bf16)))
+    return kErrDriver;
+  if (!make_tmap_out(&tmO, out, N, M, ldo, false, bf16)) return kErrDriver;
+  p.out = out; p.ldo = ldo;
+  p.bias = bias; p.residual = residual; p.ldr = ldr;
+  p.aux_out = nullptr; p.aux_in = nullptr; p.ld_aux = 0;
+  p.alpha = 1.0f; p.act = 0; p.dact = 0; p.accumulate = 0;
+  p.err = err_flag;
+  p.trace = nullptr;
+  p.prefetch = g_prefetch;
+  p.variant = 0;
+  ArParams ar;
+  ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
+  ar.exchange = 0; ar.rows_per_rank = rows_per_rank; ar.dbg = nullptr;
+  for (int i = 0; i < kMaxTp; ++i) {
+    ar.stage[i] = i < tp ? stage_ptrs[i] : nullptr;
+    ar.flag_a[i] = i < tp ? flag_ptrs[i] : nullptr;
+    ar.flag_b[i] = nullptr;
+    ar.out[i] = nullptr;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (bf16)
+    return b_mn ? launch_gemm_pair<__nv_bfloat16, BN, false, true, false, false, false, true>(tmA, tmB, tmO, p, s, &ar)
+                : launch_gemm_pair<__nv_bfloat16, BN, false, false, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
+  return b_mn ? launch_gemm_pair<__half, BN, false, true, false, false, false, true>(tmA, tmB, tmO, p, s, &ar)
+              : launch_gemm_pair<__half, BN, false, false, false, false, false, true>(tmA, tmB, tmO, p, s, &ar);
 }
 
 TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_gemm)
@@ -1504,7 +1832,10 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   GemmParams p;
   p.M = M; p.N = N; p.K = K;
   p.num_m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
-  p.num_tiles = p.num_m_tiles * ((N + bn - 1) / bn);
+  p.num_n_tiles = (N + bn - 1) / bn;
+  p.num_tiles = p.num_m_tiles * p.num_n_tiles;
+  p.m_major = 0; p.m_first = 0;
+  p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   p.out = out; p.ldo = ldo;
   p.bias = nullptr; p.residual = nullptr; p.ldr = 0;
   p.aux_out = nullptr; p.aux_in = nullptr; p.ld_aux = 0;

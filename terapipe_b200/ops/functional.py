@@ -35,7 +35,9 @@ def _stream() -> int:
 
 def status_word(device=None) -> torch.Tensor:
     """int32[1] on the device; kernels CAS their first time-out code into it."""
-    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    idx = None if device is None else torch.device(device).index
+    if idx is None:
+        idx = torch.cuda.current_device()
     if idx not in _status:
         _status[idx] = torch.zeros(1, dtype=torch.int32, device=f"cuda:{idx}")
     return _status[idx]

@@ -80,6 +80,14 @@ SIGNATURES = {
     "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, I, P, P],
     "tp_dp_reduce_adam": [I, I, I, I, P, P, P, P, P, P, P, L, L, P, F, F, F, F, F, F, P, P],
     "tp_set_wait_limit_ns": [L],
+    "tp_gemm_ag": [I, I, P, L, P, L, P, L, I, I, I, P, I, P, I, P, L, P, P, I, I, I, P, P],
+    "tp_gemm_rs": [I, I, P, L, P, L, P, L, I, I, I, P, P, L, I, I, I, I, P, I, P, P, P, P],
+    "tp_layernorm_fwd_push": [I, P, P, P, P, P, P, I, I, F, I, I, P, I, P, P, P],
+    "tp_layernorm_bwd_accum_push": [I, P, P, P, P, P, P, P, P, I, I, I, I, P, I, P, P, P],
+    "tp_layernorm_bwd_finish_assign": [P, I, I, P, P, P],
+    "tp_ag_push": [P, L, P, P, I, I, I, P, P, P],
+    "tp_group_barrier": [P, I, I, I, P, P, P],
+    "tp_peer_sum": [P, I, P, I, I, P],
     "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
     "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
 }

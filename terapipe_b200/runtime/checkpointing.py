@@ -42,7 +42,7 @@ def _gather_sharded_state(engine) -> None:
     buffers are complete again (collective over the data-parallel group)."""
     import torch.distributed as dist
     from .. import parallel as mpu
-    if engine.dp_sym is None:
+    if getattr(engine, "dp_sym", None) is None:
         return
     group = mpu.get_data_parallel_group()
     n = engine.layout.total

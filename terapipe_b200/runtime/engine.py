@@ -82,6 +82,12 @@ class _Layout:
 
 
 class StageEngine:
+    # Tensor-parallel communication: "nccl" = all-reduce after the GEMM (activations replicated),
+    # "fused" = GEMM + all-reduce in one kernel over peer memory (activations replicated),
+    # "sp" = sequence parallel: LayerNorm, residual stream and pipeline links on a token shard
+    # per rank, GEMM -> reduce-scatter and all-gather -> GEMM fused over peer memory.
+    TP_COMM_MODES = ("nccl", "fused", "sp")
+
     def __init__(self, config: TransformerConfig, batch_slices: Sequence[int],
                  seq_slices: Sequence[int], dtype=torch.float16, loss_scale=LOSS_SCALE_FACTOR,
                  lr=1e-10, seed=0, init="device", use_graph: Optional[bool] = None,
@@ -102,8 +108,16 @@ class StageEngine:
         self.is_first, self.is_last = self.pp_idx == 0, self.pp_idx == self.pp - 1
         self.layer_ids = self.topo.layers_of_stage(config.n_layers, self.pp_idx)
         self.n_layers = len(self.layer_ids)
+        if tp_comm not in self.TP_COMM_MODES:
+            raise ValueError(f"tp_comm must be one of {self.TP_COMM_MODES}")
         self.tp_comm = tp_comm if self.tp > 1 else "none"
         self.dp_comm = dp_comm if self.dp > 1 else "none"
+        self.sp = self.tp_comm == "sp"
+        if self.sp:
+            bad = [t * b for b in self.batch_slices for t in self.seq_slices if (t * b) % (32 * self.tp)]
+            if bad:
+                raise ValueError(f"tp_comm='sp' shards every token slice over {self.tp} ranks in "
+                                 f"blocks of 32 rows; slices of {bad} rows do not divide")
 
         H, Fw = config.embedding_dim, config.ffn_embedding_dim
         heads = config.num_attention_heads
@@ -149,7 +163,7 @@ class StageEngine:
         # A CUDA graph may hold this library's kernels only: captured NCCL point-to-point or
         # collective calls deadlocked on replay here, so a stage that calls NCCL runs eagerly.
         nccl_free = (self.pp == 1 and (self.dp == 1 or self.dp_comm == "fused")
-                     and (self.tp == 1 or self.tp_comm == "fused"))
+                     and (self.tp == 1 or self.tp_comm in ("fused", "sp")))
         self.use_graph = nccl_free if use_graph is None else (bool(use_graph) and nccl_free)
         self._graph = None
         # Recorded launch plans (runtime/launch_plan.py) for stages that cannot use a CUDA graph:
@@ -159,7 +173,7 @@ class StageEngine:
         want_plan = (os.environ.get("TERAPIPE_LAUNCH_PLAN", "0") == "1") if launch_plan is None \
             else bool(launch_plan)
         self._plan = None
-        if want_plan and not self.use_graph and (self.tp == 1 or self.tp_comm == "fused"):
+        if want_plan and not self.use_graph and (self.tp == 1 or self.tp_comm in ("fused", "sp")):
             from .launch_plan import RecordingLibrary, SegmentCache
             self.lib = RecordingLibrary(self.lib)
             self._plan = SegmentCache(self.lib, on_error=lambda rc, name: F.check(rc, name))
@@ -186,6 +200,11 @@ class StageEngine:
         self.launches_per_step = n_slices * self.n_layers * 16 + self.n_layers * 10 + 2
         self.launch_count = 0
         self._ar_calls_per_step = n_slices * self.n_layers * 4 + 1
+        # sequence parallel: all-gather pushes per step (2 per layer and slice forward; backward one
+        # per LayerNorm whose input gradient feeds another GEMM, plus the received output gradient)
+        self._ag_calls_per_step = n_slices * (2 * self.n_layers + self.n_layers + max(self.n_layers - 1, 0)
+                                              + (0 if self.is_last else 1)) + 1
+        self._ag_calls = 0
 
     # ------------------------------------------------------------------ parameters
     def param(self, layer: int, name: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -268,12 +287,13 @@ class StageEngine:
         self.tmax = tmax
         self.ar = None
         self._pool_off = {}
-        if self.tp_comm == "fused":
-            # matrices that receive all-reduced results live at the same offset of a
-            # peer-mapped pool on every tensor-parallel rank
+        if self.tp_comm in ("fused", "sp"):
+            # matrices that receive all-reduced (or, sequence parallel, all-gathered) results live
+            # at the same offset of a peer-mapped pool on every tensor-parallel rank
             from ..parallel.symm import FusedAllReduceContext
-            n_mats = 2 * self.n_layers
-            pool = n_mats * (rows * H * self.es + 256) + tmax * H * self.es + 4096
+            n_mats = (4 if self.sp else 2) * self.n_layers
+            pool = (n_mats * (rows * H * self.es + 256) + tmax * H * self.es
+                    + self.n_layers * 4 * H * 4 + 65536)
             self.ar = FusedAllReduceContext(mpu.get_model_parallel_group(), tmax, H, pool)
             self.ar_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
             self._ar_calls = 0
@@ -281,17 +301,34 @@ class StageEngine:
             # rank receives every partial tile); the default is reduce-scatter + all-gather
             self.lib.tp_gemm_ar_set_exchange(int(os.environ.get("TERAPIPE_AR_EXCHANGE", "0") == "1"))
 
-        def sym(name, nrows):
-            if self.ar is None:
+        if self.sp:
+            # flag words and counters of the sequence-parallel collectives (zero-filled pool)
+            self._ag_flags, self._off_ag_flags = self.ar.alloc((16,), torch.int32)
+            self._bar_flags, self._off_bar_flags = self.ar.alloc((16,), torch.int32)
+            self.ag_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
+            self.bar_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._push_counter = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._ag_flag_ptrs = self.ar.out_ptrs(self._off_ag_flags)
+            self._bar_flag_ptrs = self.ar.out_ptrs(self._off_bar_flags)
+            # per layer: folded LayerNorm gamma/beta gradient sums of this rank's token shard
+            self._ln_pack, self._off_ln_pack = self.ar.alloc((max(self.n_layers, 1), 4 * H), torch.float32)
+
+        def sym(name, nrows, pooled=True):
+            if self.ar is None or not pooled:
                 return torch.empty(nrows, H, dtype=dt, device=dev)
             t, off = self.ar.alloc((nrows, H), dt)
             self._pool_off[name] = off
             return t
 
-        self.X = [buf(H)] + [sym(f"X{l + 1}", rows) for l in range(self.n_layers)]
-        self.ln1 = [buf(H) for _ in range(self.n_layers)]
-        self.ln2 = [buf(H) for _ in range(self.n_layers)]
-        self.xmid = [sym(f"xmid{l}", rows) for l in range(self.n_layers)]
+        sp = self.sp
+        # replicated activations: the all-reduced layer outputs are pooled; sequence parallel: the
+        # all-gathered LayerNorm outputs and the gradients of the layer outputs are pooled instead
+        self.X = [buf(H)] + [sym(f"X{l + 1}", rows, not sp) for l in range(self.n_layers)]
+        if sp and self.n_layers:
+            self.X[-1].zero_()   # rows of other ranks' shards are never written; the loss sums all
+        self.ln1 = [sym(f"ln1_{l}", rows, sp) for l in range(self.n_layers)]
+        self.ln2 = [sym(f"ln2_{l}", rows, sp) for l in range(self.n_layers)]
+        self.xmid = [sym(f"xmid{l}", rows, not sp) for l in range(self.n_layers)]
         self.qkv = [buf(3 * Hl) for _ in range(self.n_layers)]
         self.ao = [buf(Hl) for _ in range(self.n_layers)]
         self.fa = [buf(Fl) for _ in range(self.n_layers)]
@@ -302,15 +339,15 @@ class StageEngine:
         self.delta = [torch.empty(self.B * self.h, self.L, dtype=torch.float32, device=dev)
                       for _ in range(self.n_layers)]
         # gradients, full length (see the module docstring)
-        self.dMid = [buf(H) for _ in range(self.n_layers)]
+        self.dMid = [sym(f"dMid{l}", rows, sp) for l in range(self.n_layers)]
         self.dFc = [buf(Fl) for _ in range(self.n_layers)]
         self.dQKV = [buf(3 * Hl) for _ in range(self.n_layers)]
         self.dAO = [buf(Hl) for _ in range(self.n_layers)]
-        self.dXo = [buf(H) for _ in range(self.n_layers)]   # d(layer output); the last one is
+        self.dXo = [sym(f"dXo{l}", rows, sp) for l in range(self.n_layers)]   # d(layer output); the last one is
         self.dY = self.dXo[-1] if self.n_layers else None    # received from the next stage
         self.dX0 = buf(H) if not self.is_first else None    # gradients sent to the previous stage
         self.dA = torch.empty(tmax, H, dtype=dt, device=dev)
-        self.dln = sym("dln", tmax)
+        self.dln = sym("dln", tmax, not sp)
         # LayerNorm parameter gradients: every backward launch adds its per-CTA partial sums
         # into persistent slots; one reduction per layer folds them after the last slice
         self.ln_parts = self.lib.tp_layernorm_bwd_parts(int(tmax))
@@ -362,8 +399,100 @@ class StageEngine:
         if st:
             F.check(st, "tp_gemm_ar")
 
+    # ------------------------------------------------------------------ sequence-parallel helpers
+    def _pool_ptrs(self, name, row):
+        """Addresses of row ``row`` of the pooled matrix ``name`` in every rank's memory."""
+        return self.ar.out_ptrs(self._pool_off[name] + row * self.H * self.es)
+
+    def _gemm_ag(self, a, lda, b, ldb, out, ldo, M, N, K, rpr, wait=True, b_mn=0, bias=None, act=0,
+                 aux_out=None, dact=0, aux_in=None, ld_aux=0):
+        """All-gather -> GEMM: A's rows were pushed into this rank's memory by the group (the
+        most recent push); rows of other ranks are awaited inside the kernel."""
+        st = self.lib.tp_gemm_ag(self.dt, b_mn, a, lda, b, ldb, out, ldo, M, N, K, bias, act, aux_out,
+                                 dact, aux_in, ld_aux,
+                                 self._ag_flags.data_ptr() if wait else None,
+                                 self.ag_epoch_base.data_ptr(), self._ag_calls, rpr, self.tp_idx,
+                                 self._status_ptr, self._stream)
+        if st:
+            F.check(st, "tp_gemm_ag")
+
+    def _gemm_rs(self, a, lda, b, ldb, out, ldo, M, N, K, rpr, b_mn=0, bias=None, residual=None, ldr=0):
+        """GEMM -> reduce-scatter: rows ``[tp_idx * rpr, (tp_idx + 1) * rpr)`` of the summed
+        product (+ bias + residual) land in ``out``; the other rows are not written."""
+        ar = self.ar
+        self._ar_calls += 1
+        st = self.lib.tp_gemm_rs(self.dt, b_mn, a, lda, b, ldb, out, ldo, M, N, K, bias, residual, ldr,
+                                 ar.tp, ar.rank, rpr, self._ar_calls, self.ar_epoch_base.data_ptr(),
+                                 ar.max_tiles, ar.stage_ptrs, ar.flag_a_ptrs, self._status_ptr,
+                                 self._stream)
+        if st:
+            F.check(st, "tp_gemm_rs")
+
+    def _ln_fwd_push(self, x, gamma, beta, dst_name, row, mean, rstd, rows):
+        self._ag_calls += 1
+        st = self.lib.tp_layernorm_fwd_push(self.dt, x, gamma, beta, self._pool_ptrs(dst_name, row), mean,
+                                            rstd, rows, self.H, 1e-5, self.tp, self.tp_idx,
+                                            self._ag_flag_ptrs, self._ag_calls,
+                                            self.ag_epoch_base.data_ptr(),
+                                            self._push_counter.data_ptr(), self._stream)
+        if st:
+            F.check(st, "tp_layernorm_fwd_push")
+
+    def _ln_bwd_push(self, dy, x, mean, rstd, gamma, dres, dst_name, row, slots, rows):
+        self._ag_calls += 1
+        st = self.lib.tp_layernorm_bwd_accum_push(self.dt, dy, x, mean, rstd, gamma, dres,
+                                                  self._pool_ptrs(dst_name, row), slots, rows, self.H,
+                                                  self.tp, self.tp_idx, self._ag_flag_ptrs,
+                                                  self._ag_calls, self.ag_epoch_base.data_ptr(),
+                                                  self._push_counter.data_ptr(), self._stream)
+        if st:
+            F.check(st, "tp_layernorm_bwd_accum_push")
+
+    def _forward_slice_sp(self, sl) -> None:
+        """Sequence-parallel forward of one token slice: this rank normalises and keeps the
+        residual stream of its ``T / tp`` rows only; LayerNorm outputs are pushed to every rank
+        (all-gather) for the column-parallel products, row-parallel products reduce-scatter."""
+        boff, b, c, t, r0 = sl
+        T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
+        lib, dt, s = self.lib, self.dt, self._stream
+        rpr = T // self.tp
+        m0 = r0 + self.tp_idx * rpr            # first row of this rank's shard
+        for l in range(self.n_layers):
+            st = self.stats[l].data_ptr()
+            self._ln_fwd_push(self.X[l].data_ptr() + m0 * H * es, self._p(l, "attn_ln.weight"),
+                              self._p(l, "attn_ln.bias"), f"ln1_{l}", m0, st + m0 * 4,
+                              st + (self.rows + m0) * 4, rpr)
+            qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
+            qkv = self.qkv[l].data_ptr() + r0 * 3 * Hl * es
+            self._gemm_ag(self.ln1[l].data_ptr() + r0 * H * es, H, self._p(l, "attn.in_proj.weight"), H,
+                          qkv, 3 * Hl, T, 3 * Hl, H, rpr, bias=self._p(l, "attn.in_proj.bias"))
+            ao = self.ao[l].data_ptr() + r0 * Hl * es
+            lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
+            rc = lib.tp_attn_fwd(dt, self.D, qkv_base, b, self.h, t, c, ao, Hl, lse, self.L,
+                                 self._status_ptr, s)
+            if rc:
+                F.check(rc, "tp_attn_fwd")
+            self._gemm_rs(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl,
+                          self.xmid[l].data_ptr() + r0 * H * es, H, T, H, Hl, rpr,
+                          bias=self._p(l, "attn.out_proj.bias"),
+                          residual=self.X[l].data_ptr() + r0 * H * es, ldr=H)
+            self._ln_fwd_push(self.xmid[l].data_ptr() + m0 * H * es, self._p(l, "fc_ln.weight"),
+                              self._p(l, "fc_ln.bias"), f"ln2_{l}", m0, st + (2 * self.rows + m0) * 4,
+                              st + (3 * self.rows + m0) * 4, rpr)
+            fa = self.fa[l].data_ptr() + r0 * Fl * es
+            fz = self.fz[l].data_ptr() + r0 * Fl * es if self.fz is not None else None
+            self._gemm_ag(self.ln2[l].data_ptr() + r0 * H * es, H, self._p(l, "fc1.weight"), H, fa, Fl,
+                          T, Fl, H, rpr, bias=self._p(l, "fc1.bias"), act=_ACT[self.act], aux_out=fz,
+                          ld_aux=Fl)
+            self._gemm_rs(fa, Fl, self._p(l, "fc2.weight"), Fl,
+                          self.X[l + 1].data_ptr() + r0 * H * es, H, T, H, Fl, rpr,
+                          bias=self._p(l, "fc2.bias"),
+                          residual=self.xmid[l].data_ptr() + r0 * H * es, ldr=H)
+
     # ------------------------------------------------------------------ forward of one slice
     def _forward_slice(self, sl) -> None:
+        if self.sp:
+            return self._forward_slice_sp(sl)
         boff, b, c, t, r0 = sl
         T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
         lib, dt, s = self.lib, self.dt, self._stream
@@ -417,6 +546,8 @@ class StageEngine:
     def _backward_slice(self, sl) -> None:
         """Data gradients of one token slice through every layer of the stage (last layer
         first).  Weight and bias gradients are left to :meth:`_weight_grads`."""
+        if self.sp:
+            return self._backward_slice_sp(sl)
         boff, b, c, t, r0 = sl
         T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
         lib, dt, s = self.lib, self.dt, self._stream
@@ -473,6 +604,77 @@ class StageEngine:
             lib.tp_layernorm_bwd_accum(dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
                                        self._p(l, "attn_ln.weight"), dmid, dnext, slots, T, H, s)
 
+    def _backward_slice_sp(self, sl) -> None:
+        """Sequence-parallel data gradients of one token slice (last layer first).  Data gradients
+        of column-parallel layers reduce-scatter onto this rank's rows; the LayerNorm backward
+        runs on those rows and pushes its result to every rank, where the data-gradient product of
+        the preceding row-parallel layer (and, after the last slice, the weight gradients) need
+        all rows."""
+        boff, b, c, t, r0 = sl
+        T, H, Hl, Fl, es = t * b, self.H, self.Hl, self.Fl, self.es
+        lib, dt, s = self.lib, self.dt, self._stream
+        rpr = T // self.tp
+        m0 = r0 + self.tp_idx * rpr
+        dln = self.dln.data_ptr()
+        dln_mine = dln + self.tp_idx * rpr * H * es
+        n = self.n_layers
+        if not self.is_last and n:
+            # the output gradient arrived from the next stage as this rank's shard: all-gather it
+            self._ag_calls += 1
+            off = self._pool_off[f"dXo{n - 1}"] + m0 * H * es
+            st = lib.tp_ag_push(self.dXo[n - 1].data_ptr() + m0 * H * es, rpr * H * es,
+                                self.ar.out_ptrs(off), self._ag_flag_ptrs, self.tp, self.tp_idx,
+                                self._ag_calls, self.ag_epoch_base.data_ptr(),
+                                self._push_counter.data_ptr(), s)
+            if st:
+                F.check(st, "tp_ag_push")
+        for l in reversed(range(n)):
+            st = self.stats[l].data_ptr()
+            fa = self.fa[l].data_ptr() + r0 * Fl * es
+            aux = (self.fz[l].data_ptr() + r0 * Fl * es) if self.fz is not None else fa
+            ao = self.ao[l].data_ptr() + r0 * Hl * es
+            dfc = self.dFc[l].data_ptr() + r0 * Fl * es
+            dqkv = self.dQKV[l].data_ptr() + r0 * 3 * Hl * es
+            dao = self.dAO[l].data_ptr() + r0 * Hl * es
+            slots = self.ln_slots[l].data_ptr()
+            # ---- FFN: d(fc1 out) from all rows of d(layer output); the seed gradient of the last
+            # stage is a constant every rank holds, everything else was pushed by the group
+            seeded = self.is_last and l == n - 1
+            self._gemm_ag(self.dXo[l].data_ptr() + r0 * H * es, H, self._p(l, "fc2.weight"), Fl, dfc, Fl,
+                          T, Fl, H, rpr, wait=not seeded, b_mn=1, dact=_ACT[self.act], aux_in=aux,
+                          ld_aux=Fl)
+            self._gemm_rs(dfc, Fl, self._p(l, "fc1.weight"), H, dln, H, T, H, Fl, rpr, b_mn=1)
+            self._ln_bwd_push(dln_mine, self.xmid[l].data_ptr() + m0 * H * es,
+                              st + (2 * self.rows + m0) * 4, st + (3 * self.rows + m0) * 4,
+                              self._p(l, "fc_ln.weight"), self.dXo[l].data_ptr() + m0 * H * es,
+                              f"dMid{l}", m0, slots + self.ln_parts * 2 * H * 4, rpr)
+            # ---- attention
+            self._gemm_ag(self.dMid[l].data_ptr() + r0 * H * es, H, self._p(l, "attn.out_proj.weight"),
+                          Hl, dao, Hl, T, Hl, H, rpr, b_mn=1)
+            qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
+            dao_base = self.dAO[l].data_ptr() + self.L * boff * Hl * es
+            lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
+            delta = self.delta[l].data_ptr() + boff * self.h * self.L * 4
+            rc = lib.tp_attn_bwd(dt, self.D, qkv_base, b, self.h, t, c, self.L, ao, Hl, dao_base, Hl,
+                                 lse, self.L, delta, dqkv, 3 * Hl, self._status_ptr, s)
+            if rc:
+                F.check(rc, "tp_attn_bwd")
+            self._gemm_rs(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, dln, H, T, H, 3 * Hl, rpr,
+                          b_mn=1)
+            x_mine = self.X[l].data_ptr() + m0 * H * es
+            dmid_mine = self.dMid[l].data_ptr() + m0 * H * es
+            if l > 0:
+                self._ln_bwd_push(dln_mine, x_mine, st + m0 * 4, st + (self.rows + m0) * 4,
+                                  self._p(l, "attn_ln.weight"), dmid_mine, f"dXo{l - 1}", m0, slots, rpr)
+            else:
+                # gradient of the stage input: only this rank's rows exist (they go to the same
+                # tensor-parallel rank of the previous stage, or nowhere on the first stage)
+                dnext = (self.dA.data_ptr() + self.tp_idx * rpr * H * es) if self.is_first \
+                    else self.dX0.data_ptr() + m0 * H * es
+                lib.tp_layernorm_bwd_accum(dt, dln_mine, x_mine, st + m0 * 4, st + (self.rows + m0) * 4,
+                                           self._p(l, "attn_ln.weight"), dmid_mine, dnext, slots, rpr,
+                                           H, s)
+
     def _weight_grads(self) -> None:
         """Weight and bias gradients of every layer over all ``L*B`` rows at once:
         ``dW += dY^T X`` with the token dimension as the (long) GEMM K dimension."""
@@ -494,10 +696,33 @@ class StageEngine:
                        H, 3 * Hl, H, R, a_mn=1, b_mn=1, out_f32=1, accumulate=1)
             lib.tp_colsum(dt, dqkv, 3 * Hl, R, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
             slots = self.ln_slots[l].data_ptr()
+            if self.sp:
+                # this rank's slots hold the sums over its token shards only: fold them into a
+                # peer-visible pack; the sums of all ranks are added after the barrier below
+                pack = self._ln_pack.data_ptr() + l * 4 * H * 4
+                lib.tp_layernorm_bwd_finish_assign(slots, self.ln_parts, H, pack, pack + H * 4, s)
+                lib.tp_layernorm_bwd_finish_assign(slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
+                                                   pack + 2 * H * 4, pack + 3 * H * 4, s)
+                continue
             lib.tp_layernorm_bwd_finish(slots, self.ln_parts, H, self._p(l, "attn_ln.weight", g),
                                         self._p(l, "attn_ln.bias", g), s)
             lib.tp_layernorm_bwd_finish(slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
                                         self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g), s)
+        if self.sp and self.n_layers:
+            self._group_barrier(2)
+            for l in range(self.n_layers):
+                off = self._off_ln_pack + l * 4 * H * 4
+                lib.tp_peer_sum(self._p(l, "attn_ln.weight", g), 2 * H, self.ar.out_ptrs(off), self.tp,
+                                self.tp_idx, s)
+                lib.tp_peer_sum(self._p(l, "fc_ln.weight", g), 2 * H, self.ar.out_ptrs(off + 2 * H * 4),
+                                self.tp, self.tp_idx, s)
+
+    def _group_barrier(self, index: int) -> None:
+        """Device-side barrier of the tensor-parallel group (``index`` 1 or 2 within a step)."""
+        st = self.lib.tp_group_barrier(self._bar_flag_ptrs, self.tp, self.tp_idx, index,
+                                       self.bar_epoch_base.data_ptr(), self._status_ptr, self._stream)
+        if st:
+            F.check(st, "tp_group_barrier")
 
     # ------------------------------------------------------------------ one iteration
     def _refresh_handles(self):
@@ -518,11 +743,11 @@ class StageEngine:
 
     def _run_graphed(self, key, fn, *args):
         ent = self._seg_graphs.get(key)
-        ar0 = getattr(self, "_ar_calls", 0)
+        ar0, ag0 = getattr(self, "_ar_calls", 0), self._ag_calls
         if ent is None:
             # first time: eager (kernel attributes get set, nothing may be captured before that)
             fn(*args)
-            self._seg_graphs[key] = [None, getattr(self, "_ar_calls", 0) - ar0]
+            self._seg_graphs[key] = [None, getattr(self, "_ar_calls", 0) - ar0, self._ag_calls - ag0]
             return
         if ent[0] is None:
             if self._cap_stream is None:
@@ -540,10 +765,13 @@ class StageEngine:
                     self._stream = outer
             if self.ar is not None:
                 self._ar_calls = ar0     # the captured launches did not run
+            self._ag_calls = ag0
             ent[0] = graph
         ent[0].replay()
+        # call indices baked into the graph stay in step with the host's counters
         if self.ar is not None:
-            self._ar_calls += ent[1]     # epochs baked into the graph stay in step with the host
+            self._ar_calls += ent[1]
+        self._ag_calls += ent[2]
 
     def _setup_streams(self):
         if self._streams_ready:
@@ -571,10 +799,21 @@ class StageEngine:
         self.recv_stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(self.recv_stream):
             for bi, si in order:
-                _, b, _, t, r0 = self.slices[bi][si]
-                works[(bi, si)] = dist.irecv(buf[r0:r0 + t * b], src, group=group)
+                lo, hi = self._link_rows(self.slices[bi][si])
+                works[(bi, si)] = dist.irecv(buf[lo:hi], src, group=group)
         torch.cuda.current_stream().wait_stream(self.recv_stream)
         return works
+
+    def _link_rows(self, sl):
+        """Row range of a token slice that crosses a pipeline link from this rank: all of it, or
+        (sequence parallel) this rank's shard, which goes to the same tensor-parallel rank of the
+        neighbouring stage."""
+        _, b, _, t, r0 = sl
+        T = t * b
+        if not self.sp:
+            return r0, r0 + T
+        rpr = T // self.tp
+        return r0 + self.tp_idx * rpr, r0 + (self.tp_idx + 1) * rpr
 
     def _forward_backward(self):
         pipelined = self.pp > 1
@@ -596,8 +835,8 @@ class StageEngine:
                 else:
                     self._segment(("forward", bi, si), self._forward_slice, sl)
                 if pipelined and not self.is_last:
-                    _, b, _, t, r0 = sl
-                    sends.append(dist.isend(self.X[self.n_layers][r0:r0 + t * b],
+                    lo, hi = self._link_rows(sl)
+                    sends.append(dist.isend(self.X[self.n_layers][lo:hi],
                                             mpu.get_pipeline_next_rank(), group=self._link_next))
         if self.is_last:
             self.loss_buf.copy_(self.X[self.n_layers].sum(dtype=torch.float32))
@@ -613,8 +852,8 @@ class StageEngine:
                 else:
                     self._segment(("backward", bi, si), self._backward_slice, sl)
                 if pipelined and not self.is_first:
-                    _, b, _, t, r0 = sl
-                    sends.append(dist.isend(self.dX0[r0:r0 + t * b], mpu.get_pipeline_prev_rank(),
+                    lo, hi = self._link_rows(sl)
+                    sends.append(dist.isend(self.dX0[lo:hi], mpu.get_pipeline_prev_rank(),
                                             group=self._link_prev))
         self._segment(("weight_grads",), self._weight_grads)
         for w in sends:
@@ -650,6 +889,14 @@ class StageEngine:
             self.lib.tp_advance_counter(self.ar_epoch_base.data_ptr(), self._ar_calls_per_step,
                                         self._stream)
             self._ar_calls = 0
+        if self.sp:
+            self.lib.tp_advance_counter(self.ag_epoch_base.data_ptr(), self._ag_calls_per_step,
+                                        self._stream)
+            self.lib.tp_advance_counter(self.bar_epoch_base.data_ptr(), 2, self._stream)
+            self._ag_calls = 0
+            # no rank may push this step's rows into a peer's buffers while that peer still reads
+            # last step's (its weight-gradient products come last)
+            self._group_barrier(1)
         if self.dp_sym is not None and update:
             # the fused reduction does not clear gradients (peers read them); clear them here,
             # after the previous reduction's end handshake and before this iteration adds to them
@@ -687,8 +934,15 @@ class StageEngine:
         return torch.cat(parts, dim=1)
 
     def loss(self) -> torch.Tensor:
-        """Device scalar: mean of the final output (valid on the last stage after a step)."""
-        return self.loss_buf / float(self.L * self.B * self.H)
+        """Device scalar: mean of the final output (valid on the last stage after a step).  Under
+        sequence parallelism every tensor-parallel rank holds the sum of its own rows; the ranks
+        add them up here (an NCCL all-reduce of one number: call it outside graph capture, on
+        every rank of the group)."""
+        total = self.loss_buf
+        if self.sp:
+            total = self.loss_buf.clone()
+            dist.all_reduce(total, group=mpu.get_model_parallel_group())
+        return total / float(self.L * self.B * self.H)
 
     def compute_grads(self) -> None:
         """Forward + backward without the optimizer; scaled grads stay in ``self.grad``."""

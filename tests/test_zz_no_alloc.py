@@ -58,20 +58,25 @@ def test_noalloc_layernorm_backward_matches_regular_entry_point():
         # allocation-free entry point: outputs allocated up front, nothing allocated by the call
         dx = torch.empty_like(x)
         dg, db = torch.ones(H, device="cuda"), torch.ones(H, device="cuda")
-        torch.cuda.synchronize()
-        before = torch.cuda.memory_allocated()
-        free_before = torch.cuda.mem_get_info()[0]
-        st = fn(0, dy.data_ptr(), x.data_ptr(), mean.data_ptr(), rstd.data_ptr(), g.data_ptr(),
+        args = (0, dy.data_ptr(), x.data_ptr(), mean.data_ptr(), rstd.data_ptr(), g.data_ptr(),
                 dres.data_ptr(), dx.data_ptr(), dg.data_ptr(), db.data_ptr(), rows, H, stream)
-        torch.cuda.synchronize()
-        assert st == 0, (call, st)
-        assert torch.cuda.memory_allocated() == before
-        if call > 0:
-            # after the first call (which resolves the array's address once) the device's free
-            # memory is untouched: no cudaMalloc inside the library either
-            assert torch.cuda.mem_get_info()[0] == free_before
-        assert _rel(dx, dx_ref) < 3e-3
-        assert _rel(dg, dg_ref) < 2e-3 and _rel(db, db_ref) < 2e-3
+        for repeat in range(2):      # two calls in a row share the built-in array
+            dg.fill_(1.0)
+            db.fill_(1.0)
+            dx.zero_()
+            torch.cuda.synchronize()
+            before = torch.cuda.memory_allocated()
+            free_before = torch.cuda.mem_get_info()[0]
+            st = fn(*args)
+            torch.cuda.synchronize()
+            assert st == 0, (call, repeat, st)
+            assert torch.cuda.memory_allocated() == before
+            if repeat == 1:
+                # the kernels are loaded and the array's address is resolved by now: the device's
+                # free memory must not move, i.e. no cudaMalloc inside the library either
+                assert torch.cuda.mem_get_info()[0] == free_before
+            assert _rel(dx, dx_ref) < 3e-3
+            assert _rel(dg, dg_ref) < 2e-3 and _rel(db, db_ref) < 2e-3
 
 
 def test_noalloc_rejects_rows_wider_than_the_built_in_array():

@@ -1166,9 +1166,29 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int owner = min(row0 / ar.rows_per_rank, ar.tp - 1);
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
         const long long tile_elems = kBM * BN;
-        if (row0 < p.M && owner == ar.rank) {
+        const bool mine = row0 < p.M && owner == ar.rank;
+        // Hand this warp's part of the block to the publishing warp (which keeps at most two
+        // blocks outstanding).  A warp that owns its rows has nothing to publish and says so
+        // BEFORE it waits for its peers: their publishing warps wait for all eight epilogue warps
+        // too, so waiting first would deadlock two ranks on a block that holds rows of both.
+        auto pub_arrive = [&]() {
+          if (it >= 2) {
+            unsigned spins = 0;
+            unsigned long long t0 = 0;
+            while (*pub_done < it - 1 && !*abort_flag) {
+              if ((++spins & 0xFF) == 0) {
+                const unsigned long long now = globaltimer_ns();
+                if (t0 == 0) t0 = now;
+                else if (now - t0 > g_wait_limit_ns) { report_timeout(wctx, kErrWaitEpilogue); break; }
+              }
+            }
+          }
+          mbar_arrive(&pub_full[it & 1]);
+        };
+        if (mine) {
           // rows of this rank: the other ranks' partials join the accumulator in the epilogue
           int got = 1;
+          if (lane == 0) pub_arrive();
           if (lane == 0) {
             for (int src = 0; src < ar.tp && got; ++src)
               if (src != ar.rank)
@@ -1219,19 +1239,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncwarp();
         if (lane == 0) {
           mbar_arrive_cluster(mapa_u32(smem_u32(&tempty[acc]), 0));
-          // hand the block to the publishing warp; it keeps at most two blocks outstanding
-          if (it >= 2) {
-            unsigned spins = 0;
-            unsigned long long t0 = 0;
-            while (*pub_done < it - 1 && !*abort_flag) {
-              if ((++spins & 0xFF) == 0) {
-                const unsigned long long now = globaltimer_ns();
-                if (t0 == 0) t0 = now;
-                else if (now - t0 > g_wait_limit_ns) { report_timeout(wctx, kErrWaitEpilogue); break; }
-              }
-            }
-          }
-          mbar_arrive(&pub_full[it & 1]);
+          if (!mine) pub_arrive();
         }
         continue;
       }

@@ -903,7 +903,8 @@ class StageEngine:
             self.grad.zero_()
         self._forward_backward()
         if update:
-            if self.dp == 1 or self.dp_sym is not None:
+            if self._seg_graphs is not None and (self.dp == 1 or self.dp_sym is not None):
+                # (a recorded launch plan only sees calls made through self.lib: not this one)
                 self._segment(("update",), self._reduce_and_update)
             else:
                 self._reduce_and_update()

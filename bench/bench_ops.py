@@ -1,9 +1,9 @@
 """Micro-benchmarks of the sm_100a kernels at the GPT-3 layer shapes (CUDA-event timing).
 
-    python -m terapipe_b200.ops.bench_ops --case gemm  [--hidden 2048] [--tokens 1024]
-    python -m terapipe_b200.ops.bench_ops --case attn  [--ctx 1920] [--slice 128]
-    python -m terapipe_b200.ops.bench_ops --case norm
-    python -m terapipe_b200.ops.bench_ops --case adam
+    python bench/bench_ops.py --case gemm  [--hidden 2048] [--tokens 1024]
+    python bench/bench_ops.py --case attn  [--ctx 1920] [--slice 128]
+    python bench/bench_ops.py --case norm
+    python bench/bench_ops.py --case adam
 
 ``--once`` runs each kernel a few times without timing (a small, self-terminating workload
 for profiler captures).  Between timed kernels a 256 MB buffer is rewritten to flush the L2
@@ -12,10 +12,14 @@ when ``--flush`` is given; otherwise launches run back to back (warm L2).
 from __future__ import annotations
 
 import argparse
+import os
+import sys
 
 import torch
 
-from . import functional as F
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from terapipe_b200.ops import functional as F  # noqa: E402
 
 
 def _timeit(fn, n=20, warm=3, flush=None):

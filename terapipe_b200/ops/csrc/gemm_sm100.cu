@@ -41,10 +41,14 @@ struct GemmParams {
   int M, N, K;
   int num_m_tiles, num_tiles;
   // CTA-pair kernel: tile order.  m_major = 0: consecutive tiles walk down a column of the output
-  // (tile -> m = tile % num_m_tiles); m_major = 1: they walk along a row block, and the row
-  // blocks are visited starting at m_first and wrapping around (used to put the row blocks whose
-  // operands or results live on this rank first or last).
-  int num_n_tiles, m_major, m_first;
+  // (tile -> m = tile % num_m_tiles), so the CTAs of a wave share few B tiles.  m_major = 1: the
+  // columns are taken in groups of order_group; inside a group the row blocks are split in two
+  // phases: first the `order_split` row blocks starting at m_first (wrapping around) for every
+  // column of the group, then the remaining row blocks for every column, row block fastest in
+  // both.  order_first_only = 1 applies the split to the first group only.  The all-gather
+  // variant puts the row blocks whose operands are local first; the reduce-scatter variant puts
+  // the row blocks this rank owns last, a whole phase after the peers produced their share.
+  int num_n_tiles, m_major, m_first, order_split, order_group, order_first_only;
   // All-gather wait (CTA-pair kernel, A stored [M][K]): rows [s * ag_rows, (s + 1) * ag_rows) of A
   // were written into this GPU's memory by rank s; before loading rows of another rank the
   // producer waits until ag_flags[s] >= ag_epoch + *ag_epoch_base.  ag_flags == nullptr: no wait.
@@ -398,13 +402,27 @@ __device__ __forceinline__ void add_partials(uint32_t (&r)[32], const T* part, l
 
 // Output-tile coordinates of the CTA-pair kernel (see GemmParams::m_major).
 __device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int& m_idx, int& n_idx) {
-  if (p.m_major) {
-    n_idx = tile % p.num_n_tiles;
-    m_idx = (tile / p.num_n_tiles + p.m_first) % p.num_m_tiles;
-  } else {
+  if (!p.m_major) {
     m_idx = tile % p.num_m_tiles;
     n_idx = tile / p.num_m_tiles;
+    return;
   }
+  const int per_group = p.num_m_tiles * p.order_group;
+  const int g = tile / per_group, r = tile % per_group;
+  const int cols = min(p.order_group, p.num_n_tiles - g * p.order_group);
+  int j;
+  if (p.order_first_only && g > 0) {
+    j = r % p.num_m_tiles;
+    n_idx = g * p.order_group + r / p.num_m_tiles;
+  } else if (r < p.order_split * cols) {
+    j = r % p.order_split;
+    n_idx = g * p.order_group + r / p.order_split;
+  } else {
+    const int r2 = r - p.order_split * cols, cnt = p.num_m_tiles - p.order_split;
+    j = p.order_split + r2 % cnt;
+    n_idx = g * p.order_group + r2 / cnt;
+  }
+  m_idx = (j + p.m_first) % p.num_m_tiles;
 }
 
 // Epilogue of one warp's 32 rows over `nc` 32-column chunks of an accumulator at TMEM address
@@ -1622,12 +1640,20 @@ static int gemm_impl(int dtype, int a_mn, int b_mn, const void* A, long long lda
   p.num_m_tiles = (M + BM - 1) / BM;
   p.num_n_tiles = (N + BN - 1) / BN;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.m_major = 0; p.m_first = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   if (ag) {
-    // row blocks of this rank first: their operands are local, the others are still arriving
-    p.m_major = 1;
-    p.m_first = static_cast<int>((static_cast<long long>(ag->rank) * ag->rows_per_rank) / BM) % p.num_m_tiles;
+    // the first wave of tiles takes row blocks of this rank only: their operands are local
+    // while the peers' rows are still arriving; later tiles use the ordinary order
+    const int own_tiles = (ag->rows_per_rank + BM - 1) / BM;
+    if (own_tiles < p.num_m_tiles) {
+      p.m_major = 1;
+      p.m_first = static_cast<int>((static_cast<long long>(ag->rank) * ag->rows_per_rank) / BM) % p.num_m_tiles;
+      p.order_split = own_tiles;
+      p.order_group = (max_pairs() + own_tiles - 1) / own_tiles;
+      if (p.order_group > p.num_n_tiles) p.order_group = p.num_n_tiles;
+      p.order_first_only = 1;
+    }
     p.ag_flags = ag->flags; p.ag_epoch_base = ag->epoch_base; p.ag_epoch = ag->epoch;
     p.ag_rows = ag->rows_per_rank; p.ag_rank = ag->rank;
   }
@@ -1701,7 +1727,7 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.num_m_tiles = (M + BM - 1) / BM;
   p.num_n_tiles = (N + BN - 1) / BN;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.m_major = 0; p.m_first = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   if (((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) > max_tiles) return kErrTooLarge;
   CUtensorMap tmA, tmB;
@@ -1770,11 +1796,21 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
   p.num_n_tiles = (N + BN - 1) / BN;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
   if (((M + kBM - 1) / kBM) * p.num_n_tiles > max_tiles) return kErrTooLarge;
-  // row blocks of the next rank first, this rank's own rows last
-  p.m_major = 1;
+  // Column groups of about one wave of remote row blocks; inside a group the row blocks of the
+  // other ranks first (starting after this rank's rows), this rank's own row blocks last.
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
   {
     const long long first_after = static_cast<long long>(rank + 1) * rows_per_rank;
-    p.m_first = first_after >= M ? 0 : static_cast<int>((first_after + 2 * kBM - 1) / (2 * kBM)) % p.num_m_tiles;
+    const long long my_end = first_after < M ? first_after : M;
+    const long long my_begin = static_cast<long long>(rank) * rows_per_rank;
+    int own_tiles = my_begin >= M ? 0 : static_cast<int>((my_end + 2 * kBM - 1) / (2 * kBM) - my_begin / (2 * kBM));
+    if (own_tiles > 0 && own_tiles < p.num_m_tiles) {
+      p.m_major = 1;
+      p.m_first = first_after >= M ? 0 : static_cast<int>((first_after + 2 * kBM - 1) / (2 * kBM)) % p.num_m_tiles;
+      p.order_split = p.num_m_tiles - own_tiles;
+      p.order_group = (max_pairs() + p.order_split - 1) / p.order_split;
+      if (p.order_group > p.num_n_tiles) p.order_group = p.num_n_tiles;
+    }
   }
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   CUtensorMap tmA, tmB, tmO;
@@ -1842,7 +1878,7 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   p.num_m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
   p.num_n_tiles = (N + bn - 1) / bn;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.m_major = 0; p.m_first = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   p.out = out; p.ldo = ldo;
   p.bias = nullptr; p.residual = nullptr; p.ldr = 0;

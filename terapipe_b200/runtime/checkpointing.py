@@ -45,15 +45,12 @@ def _gather_sharded_state(engine) -> None:
     if getattr(engine, "dp_sym", None) is None:
         return
     group = mpu.get_data_parallel_group()
-    n = engine.layout.total
-    chunk = ((n + engine.dp - 1) // engine.dp + 3) // 4 * 4
     for buf in (engine.master, engine.exp_avg, engine.exp_avg_sq):
-        padded = torch.zeros(chunk * engine.dp, dtype=buf.dtype, device=buf.device)
-        mine = buf[engine._dp_begin:engine._dp_end]
-        own = torch.zeros(chunk, dtype=buf.dtype, device=buf.device)
-        own[:mine.numel()] = mine
-        dist.all_gather_into_tensor(padded, own, group=group)
-        buf.copy_(padded[:n])
+        own = torch.zeros_like(buf)
+        for _, _, b, e in engine._dp_ranges:
+            own[b:e] = buf[b:e]
+        dist.all_reduce(own, group=group)      # every element has exactly one owner
+        buf.copy_(own)
 
 
 def save_checkpoint(engine, directory: str) -> str:

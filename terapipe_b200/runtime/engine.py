@@ -113,6 +113,10 @@ class StageEngine:
         self.tp_comm = tp_comm if self.tp > 1 else "none"
         self.dp_comm = dp_comm if self.dp > 1 else "none"
         self.sp = self.tp_comm == "sp"
+        # overlap the data-parallel reduction with the weight-gradient products (TERAPIPE_DP_OVERLAP=0
+        # runs it after them, for comparison)
+        self.dp_overlap = os.environ.get("TERAPIPE_DP_OVERLAP", "1") != "0"
+        self._dp_overlap, self._dp_works = False, None
         if self.sp:
             bad = [t * b for b in self.batch_slices for t in self.seq_slices if (t * b) % (32 * self.tp)]
             if bad:
@@ -146,9 +150,19 @@ class StageEngine:
             self.model = self.dp_sym.view(self._dp_off_model, (n,), dtype)
             self.grad = self.dp_sym.view(self._dp_off_grad, (n,), torch.float32)
             self.dp_epoch_base = torch.zeros(1, dtype=torch.int32, device=dev)
-            chunk = ((n + self.dp - 1) // self.dp + 3) // 4 * 4
-            self._dp_begin = min(n, self.dp_idx * chunk)
-            self._dp_end = min(n, self._dp_begin + chunk)
+            # Ownership of the fused reduction + sharded Adam: within the flat range of every
+            # layer, replica r owns the r-th chunk.  (lo, hi, begin, end) per layer.
+            self._dp_ranges = []
+            for l in range(self.n_layers):
+                lo = self.layout.offsets[l][PARAM_ORDER[0]]
+                hi = self.layout.offsets[l + 1][PARAM_ORDER[0]] if l + 1 < self.n_layers else n
+                chunk = ((hi - lo + self.dp - 1) // self.dp + 3) // 4 * 4
+                b = min(hi, lo + self.dp_idx * chunk)
+                self._dp_ranges.append((lo, hi, b, min(hi, b + chunk)))
+            self._dp_ptrs = (self.dp_sym.ptr_array(self._dp_off_grad),
+                             self.dp_sym.ptr_array(self._dp_off_model), self.dp_sym.ptr_array(0))
+            self._dp_calls = 0
+            self._dp_stream = None
         else:
             self.model = torch.zeros(n, dtype=dtype, device=dev)
             self.grad = torch.zeros(n, dtype=torch.float32, device=dev)
@@ -680,7 +694,17 @@ class StageEngine:
         ``dW += dY^T X`` with the token dimension as the (long) GEMM K dimension."""
         R, H, Hl, Fl = self.rows, self.H, self.Hl, self.Fl
         lib, dt, s, g = self.lib, self.dt, self._stream, self.grad
+        # Data-parallel reduction overlapped with these products: as soon as the gradients of a
+        # layer are complete (layers are visited last to first), its reduction - and with the fused
+        # kernel its Adam update and parameter push - starts on a side stream (NCCL: on NCCL's own
+        # stream) underneath the next layer's four long-K GEMMs.
+        overlap = self._dp_overlap and not self.sp
+        works = []
+        if overlap and self.dp_sym is not None:
+            self._dp_begin_update()
         for l in reversed(range(self.n_layers)):
+            if l != self.n_layers - 1 and overlap:
+                self._dp_layer_done(l + 1, works)
             dxo, dmid = self.dXo[l].data_ptr(), self.dMid[l].data_ptr()
             dfc, dqkv = self.dFc[l].data_ptr(), self.dQKV[l].data_ptr()
             self._gemm(dxo, H, self.fa[l].data_ptr(), Fl, self._p(l, "fc2.weight", g), Fl, H, Fl, R,
@@ -708,6 +732,12 @@ class StageEngine:
                                         self._p(l, "attn_ln.bias", g), s)
             lib.tp_layernorm_bwd_finish(slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
                                         self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g), s)
+        if overlap and self.n_layers:
+            self._dp_layer_done(0, works)
+            if self.dp_sym is not None:
+                torch.cuda.current_stream().wait_stream(self._dp_stream)
+            else:
+                self._dp_works = works
         if self.sp and self.n_layers:
             self._group_barrier(2)
             for l in range(self.n_layers):
@@ -855,28 +885,68 @@ class StageEngine:
                     lo, hi = self._link_rows(sl)
                     sends.append(dist.isend(self.dX0[lo:hi], mpu.get_pipeline_prev_rank(),
                                             group=self._link_prev))
-        self._segment(("weight_grads",), self._weight_grads)
+        if self.dp > 1 and self.dp_sym is None:
+            self._weight_grads()           # starts NCCL all-reduces: not for a captured segment
+        else:
+            self._segment(("weight_grads",), self._weight_grads)
         for w in sends:
             w.wait()
 
+    # ------------------------------------------------------------------ data-parallel update
+    def _dp_begin_update(self):
+        """Fused path, once per step before the first layer's reduction: advance Adam's bias
+        correction and the call counter of the reduction kernel's flags."""
+        F.adam_tick(self.adam_state)
+        self.lib.tp_advance_counter(self.dp_epoch_base.data_ptr(), self.n_layers, self._stream)
+        self._dp_calls = 0
+        if self._dp_stream is None:
+            self._dp_stream = torch.cuda.Stream()
+
+    def _dp_layer_update(self, l, stream_handle):
+        """Fused reduction of layer ``l``: peer-load every replica's gradients of the chunk this
+        replica owns, Adam on that chunk, peer-store the new 16-bit parameters into every
+        replica; then clear the layer's gradients (the kernel's closing handshake guarantees that
+        no replica still reads them)."""
+        lo, hi, b, e = self._dp_ranges[l]
+        self._dp_calls += 1
+        gp, mp_, fp = self._dp_ptrs
+        st = self.lib.tp_dp_reduce_adam(
+            self.dt, self.dp, self.dp_sym.rank, self._dp_calls, self.dp_epoch_base.data_ptr(), gp, mp_, fp,
+            self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(), b, e,
+            self.adam_state.data_ptr(), self.lr, 0.9, 0.999, 1e-8, 0.0,
+            1.0 / (self.loss_scale * self.dp), self._status_ptr, stream_handle)
+        if st:
+            F.check(st, "tp_dp_reduce_adam")
+        self.grad[lo:hi].zero_()
+
+    def _dp_layer_done(self, l, works):
+        """The gradients of layer ``l`` are complete on the current stream: start reducing them."""
+        if self.dp_sym is not None:
+            side = self._dp_stream
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                self._dp_layer_update(l, side.cuda_stream)
+        else:
+            lo = self.layout.offsets[l][PARAM_ORDER[0]]
+            hi = self.layout.offsets[l + 1][PARAM_ORDER[0]] if l + 1 < self.n_layers else self.layout.total
+            works.append(dist.all_reduce(self.grad[lo:hi], group=mpu.get_data_parallel_group(),
+                                         async_op=True))
+
     def _reduce_and_update(self):
         if self.dp_sym is not None:
-            # one kernel: peer-load every replica's gradients for the owned chunk, Adam on that
-            # chunk, peer-store the new 16-bit parameters into every replica
-            F.adam_tick(self.adam_state)
-            self.lib.tp_advance_counter(self.dp_epoch_base.data_ptr(), 1, self._stream)
-            sym = self.dp_sym
-            st = self.lib.tp_dp_reduce_adam(
-                self.dt, self.dp, sym.rank, 0, self.dp_epoch_base.data_ptr(),
-                sym.ptr_array(self._dp_off_grad), sym.ptr_array(self._dp_off_model), sym.ptr_array(0),
-                self.master.data_ptr(), self.exp_avg.data_ptr(), self.exp_avg_sq.data_ptr(),
-                self._dp_begin, self._dp_end, self.adam_state.data_ptr(), self.lr, 0.9, 0.999, 1e-8,
-                0.0, 1.0 / (self.loss_scale * self.dp), self._status_ptr, self._stream)
-            if st:
-                F.check(st, "tp_dp_reduce_adam")
+            if self._dp_overlap and not self.sp:
+                return                     # done layer by layer underneath the weight gradients
+            self._dp_begin_update()
+            for l in reversed(range(self.n_layers)):
+                self._dp_layer_update(l, self._stream)
             return
         if self.dp > 1:
-            dist.all_reduce(self.grad, group=mpu.get_data_parallel_group())
+            if self._dp_works is not None:
+                for w in self._dp_works:   # per-layer all-reduces started under the weight gradients
+                    w.wait()
+                self._dp_works = None
+            else:
+                dist.all_reduce(self.grad, group=mpu.get_data_parallel_group())
         F.adam_tick(self.adam_state)
         F.fused_adam(self.grad, self.master, self.exp_avg, self.exp_avg_sq, self.model,
                      self.adam_state, lr=self.lr, grad_scale=1.0 / (self.loss_scale * self.dp))
@@ -897,12 +967,10 @@ class StageEngine:
             # no rank may push this step's rows into a peer's buffers while that peer still reads
             # last step's (its weight-gradient products come last)
             self._group_barrier(1)
-        if self.dp_sym is not None and update:
-            # the fused reduction does not clear gradients (peers read them); clear them here,
-            # after the previous reduction's end handshake and before this iteration adds to them
-            self.grad.zero_()
+        self._dp_overlap = bool(update and self.dp > 1 and self.dp_overlap)
+        self._dp_works = None
         self._forward_backward()
-        if update:
+        if update and not (self.dp_sym is not None and self._dp_overlap and not self.sp):
             if self._seg_graphs is not None and (self.dp == 1 or self.dp_sym is not None):
                 # (a recorded launch plan only sees calls made through self.lib: not this one)
                 self._segment(("update",), self._reduce_and_update)

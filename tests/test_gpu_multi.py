@@ -228,3 +228,57 @@ def test_two_gpu_fused_modes_match_nccl_at_gpt3_1b_width():
             assert abs(l - l0) < 2e-3, mode
             rel = ((g - g0).norm() / g0.norm()).item()
             assert rel < 2e-2, (mode, rel)
+
+
+def _dp_ckpt_worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from terapipe_b200 import parallel as mpu
+    from terapipe_b200.models import TransformerConfig
+    from terapipe_b200.runtime import checkpointing as ck
+    from terapipe_b200.runtime.engine import StageEngine
+    mpu.initialize_model_parallel(1, 1, verbose=False)
+    cfg = TransformerConfig(batch_size=2, seq_len=128, n_layers=2, embedding_dim=256,
+                            num_attention_heads=4, n_devices=world)
+
+    def data(step):
+        g = torch.Generator().manual_seed(100 + 10 * rank + step)
+        return torch.randn(cfg.seq_len, cfg.batch_size, cfg.embedding_dim, generator=g)
+
+    eng = StageEngine(cfg, [2], [64, 64], init="device", use_graph=False, lr=1e-3, dp_comm="fused")
+    for step in range(3):
+        eng.set_input(data(step))
+        eng.step()
+    torch.cuda.synchronize()
+    ck.save_checkpoint(eng, os.path.join(out_dir, "ckpt"))
+    fresh = StageEngine(cfg, [2], [64, 64], init="device", use_graph=False, lr=1e-3, dp_comm="fused", seed=9)
+    ck.load_checkpoint(fresh, os.path.join(out_dir, "ckpt"))
+    same_model = torch.equal(fresh.model, eng.model)
+    for e in (eng, fresh):
+        e.set_input(data(3))
+        e.step()
+    torch.cuda.synchronize()
+    eng.check_status()
+    torch.save({"same_model": same_model, "same_next": torch.equal(fresh.model, eng.model),
+                "moved": (eng.model.float() - eng.model.float().mean()).abs().max().item()},
+               os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_checkpoint_roundtrip_with_fused_data_parallel_update():
+    """With the sharded (fused) data-parallel update every replica owns a chunk of master weights
+    and moments; a checkpoint must still restore all of them on every replica."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from dist_utils import free_port
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_dp_ckpt_worker, args=(2, free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    for r in res:
+        assert r["same_model"] and r["same_next"] and r["moved"] > 0

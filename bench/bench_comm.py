@@ -193,6 +193,22 @@ def bench_column_parallel(c: Ctx, name, N):
                              b.data_ptr(), 0, None, 0, None, 0, c.ag_flags.data_ptr(), None, c.ag_calls,
                              rpr, rank, c.status.data_ptr(), c.stream()), "tp_gemm_ag")
 
+    side = torch.cuda.Stream()
+    local_dst = c.ln_sym[m0:m0 + rpr]
+
+    def copied():
+        # LayerNorm writes its shard locally; copy engines carry it to the peers on a side stream
+        # while the GEMM already works on this rank's own row blocks
+        c.ag_calls += 1
+        F.layernorm_fwd(x[m0:m0 + rpr], gamma, beta, local_dst, mean[m0:m0 + rpr], rstd[m0:m0 + rpr])
+        side.wait_stream(torch.cuda.current_stream())
+        check(lib.tp_ag_copy(local_dst.data_ptr(), rpr * H * 2, dst_ptrs, c.ag_flag_ptrs, tp, rank,
+                             c.ag_calls, None, side.cuda_stream), "tp_ag_copy")
+        check(lib.tp_gemm_ag(0, 0, c.ln_sym.data_ptr(), H, w.data_ptr(), H, y.data_ptr(), N, T, N, H,
+                             b.data_ptr(), 0, None, 0, None, 0, c.ag_flags.data_ptr(), None, c.ag_calls,
+                             rpr, rank, c.status.data_ptr(), c.stream()), "tp_gemm_ag")
+        torch.cuda.current_stream().wait_stream(side)
+
     def gathered():
         F.layernorm_fwd(x[m0:m0 + rpr], gamma, beta, ln_shard, mean[m0:m0 + rpr], rstd[m0:m0 + rpr])
         dist.all_gather_into_tensor(ln_full, ln_shard)
@@ -206,7 +222,13 @@ def bench_column_parallel(c: Ctx, name, N):
     gathered()
     torch.cuda.synchronize()
     err = ((y.float() - y_ref.float()).norm() / y_ref.float().norm()).item()
-    ms = {"push_ag_gemm": _max_ms(pushed, tp), "ln_gemm_no_comm": _max_ms(local_only, tp),
+    y.zero_()
+    copied()
+    torch.cuda.synchronize()
+    err_copy = ((y.float() - y_ref.float()).norm() / y_ref.float().norm()).item()
+    err = max(err, err_copy)
+    ms = {"copy_ag_gemm": _max_ms(copied, tp), "push_ag_gemm": _max_ms(pushed, tp),
+          "ln_gemm_no_comm": _max_ms(local_only, tp),
           "ln_nccl_ag_gemm": _max_ms(gathered, tp)}
     flops = 2.0 * T * N * H
     wire = (tp - 1) * rpr * H * 2                  # this rank's shard to every peer

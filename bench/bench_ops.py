@@ -108,21 +108,6 @@ def case_gemm_trace(a):
         w = torch.randn(N, K, device=dev, dtype=dt) * 0.02
         out = torch.empty(M, N, device=dev, dtype=dt)
         for bn in (128, 256):
-            for variant in (7, 8):  # TMEM load latency probes
-                for _ in range(3):
-                    tr = F.gemm_pair_trace(x, w, out, bn, variant)
-                torch.cuda.synchronize()
-                tr = tr.cpu().double()
-                print(f"  [TMEM probe {variant}] {name} 256x{bn}: first chunk load+wait {float(tr[:, 16].median()):6.0f} "
-                      f"read {float(tr[:, 17].median()):6.0f}; later chunks (sum) load+wait {float(tr[:, 18].median()):6.0f} "
-                      f"read {float(tr[:, 19].median()):6.0f}; tiles {float(tr[0::2, 8].median()):.0f}")
-            for variant in (1, 2, 3, 4, 5, 6):  # truncated epilogues, see GemmParams::variant
-                for _ in range(3):
-                    tr = F.gemm_pair_trace(x, w, out, bn, variant)
-                torch.cuda.synchronize()
-                tr = tr.cpu().double()
-                print(f"  [epilogue variant {variant}] {name} 256x{bn}: accumulator ready -> epilogue done "
-                      f"{float((tr[:, 12] - tr[:, 10]).median()):7.0f}, -> exit {float((tr[:, 13] - tr[:, 10]).median()):7.0f}")
             for _ in range(3):
                 tr = F.gemm_pair_trace(x, w, out, bn)
             if a.flush_buf is not None:

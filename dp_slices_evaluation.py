@@ -26,7 +26,7 @@ def main():
     parser.add_argument("--dp-results", type=str, default="dp_results.json")
     parser.add_argument("--n-layers", type=int, default=None)
     parser.add_argument("--memory-limit", type=float, default=None)
-    parser.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
+    parser.add_argument("--tp-comm", default="fused", choices=["nccl", "fused", "sp"])
     args = parser.parse_args()
     cli.resolve_ranks(args)
     out_path = os.path.join("dp_evaluation_results", f"dp_eval-{args.model_name}-{args.index}.json")

@@ -192,7 +192,7 @@ def main():
     parser.add_argument("--mixed-precision", action="store_true", default=False)
     parser.add_argument("--verify", type=str, default=None, choices=["save", "load"])
     parser.add_argument("--verify-path", type=str, default="verify_data")
-    parser.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
+    parser.add_argument("--tp-comm", default="fused", choices=["nccl", "fused", "sp"])
     args = parser.parse_args()
     cli.resolve_ranks(args)
     if args.verify:

@@ -352,6 +352,38 @@ extern "C" int tp_ag_push(const void* src, long long bytes, void* const* dst_ptr
   return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }
 
+namespace tp {
+__global__ void ag_signal_kernel(const PeerPtrs pp) {
+  const int r = threadIdx.x;
+  if (r < pp.n && r != pp.rank) {
+    const int epoch = pp.epoch + (pp.epoch_base ? *pp.epoch_base : 0);
+    __threadfence_system();
+    st_release_sys_i(pp.flags[r] + pp.rank, epoch);
+  }
+}
+}  // namespace tp
+
+// All-gather by copy engine: `bytes` at `src` (this rank's shard, already in its final place in
+// the local buffer) are copied to dst_ptrs[r] for every other rank r with one cudaMemcpyAsync per
+// peer, then a one-warp kernel raises flag_ptrs[r][rank] = epoch + *epoch_base at every peer.  No SM
+// time is spent on the transfer, so it can run on a side stream underneath the consumer
+// (tp_gemm_ag), which starts with the row blocks of its own rank.
+extern "C" int tp_ag_copy(const void* src, long long bytes, void* const* dst_ptrs, int* const* flag_ptrs,
+                          int n, int rank, int epoch, const int* epoch_base, void* stream) {
+  if (bytes <= 0 || !dst_ptrs || !flag_ptrs) return kErrBadArgument;
+  PeerPtrs pp;
+  if (!make_peer_ptrs(&pp, dst_ptrs, flag_ptrs, n, rank, epoch, epoch_base, nullptr, nullptr))
+    return kErrBadArgument;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  for (int r = 0; r < n; ++r) {
+    if (r == rank) continue;
+    if (cudaMemcpyAsync(dst_ptrs[r], src, static_cast<size_t>(bytes), cudaMemcpyDefault, s) != cudaSuccess)
+      return kErrDriver;
+  }
+  ag_signal_kernel<<<1, 32, 0, s>>>(pp);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+}
+
 // Device-side barrier of a tensor-parallel group between steps: flag_ptrs[r] is rank r's barrier
 // flag array (n ints), epoch + *epoch_base must grow from call to call.  A wait that runs out
 // writes kErrWaitPeer to *err.

@@ -71,8 +71,6 @@ struct GemmParams {
   long long* trace;  // optional per-CTA phase stamps (trace builds of the kernel only)
   int prefetch;      // CTA-pair kernel: operand tiles are prefetched into L2 this many k-steps
                      // ahead of the loads that fill the ring (0 = off)
-  int variant;       // trace builds only: 1 = epilogue reads TMEM and drops the values, 2 = stops
-                     // after the shared-memory writes, 3 = stops after the proxy fence
 };
 
 constexpr int kMaxTp = 8;
@@ -85,7 +83,6 @@ struct ArParams {
   int exchange;                  // CTA-pair kernel: every rank receives every partial tile and
                                  // reduces it itself (one NVLink hop instead of two)
   int rows_per_rank;             // reduce-scatter kernel: rank s owns rows [s * rows_per_rank, ...)
-  long long* dbg;                // optional: 8 globaltimer stamps per CTA (see tp_gemm_ar_set_debug)
   void* stage[kMaxTp];           // per rank: [2 halves][tp sources][max_tiles][128][BN] 16-bit partials
                                  // (the second half is used by exchange mode only)
   int* flag_a[kMaxTp];           // per rank: [max_tiles][kMaxTp] partial-arrived flags
@@ -188,12 +185,10 @@ template <typename T, bool OUT_F32, bool TRACE = false>
 __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtensorMap* tmO,
                                                EpiStage& es, uint32_t (&r)[32], long long row,
                                                bool row_ok, int n, int row0, int lane,
-                                               uint32_t t_next, long long* cyc = nullptr) {
+                                               uint32_t t_next, long long* cyc = nullptr,
+                                               const T* part = nullptr, long long part_stride = 0,
+                                               int n_src = 0, int self = 0) {
   const long long t_0 = TRACE ? clock_ordered() : 0;
-  if (TRACE && p.variant == 1) {
-    asm volatile("" ::"r"(r[0]), "r"(r[31]) : "memory");
-    return;
-  }
   // Issue every global load of this 32-column chunk before any dependent math or store,
   // so the chunk pays one memory latency instead of one per 8-column group.
   bool gok[4];
@@ -220,6 +215,17 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtens
                   ? __ldcg(reinterpret_cast<const uint4*>(static_cast<const T*>(p.aux_in) + row * p.ld_aux + n + g * 8))
                   : zero4;
   }
+  // Reduce-scatter: the other ranks' 16-bit partials of this chunk (thread = row, 64 contiguous
+  // bytes per source in this rank's staging buffer); the first source is fetched here with the
+  // other operands, further ones (groups of more than two ranks) in a loop below.
+  uint4 pa[4];
+  int src_a = -1;
+  if (part) {
+    src_a = self == 0 ? 1 : 0;
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      pa[g] = __ldcg(reinterpret_cast<const uint4*>(part + src_a * part_stride + g * 8));
+  }
   // A tile store reads its source a good thousand cycles after it was issued, so the buffers
   // rotate: four 2 KB buffers for 16-bit output, two 4 KB buffers for fp32.  The buffer about
   // to be overwritten was the source of the store issued kBufs chunks ago.
@@ -241,35 +247,36 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtens
   // empty asm keeps the copies above ahead of the load that overwrites their source.
   asm volatile("" ::: "memory");
   if (t_next) tmem_ld_32x32(t_next, r);
-  if (TRACE && p.variant >= 4 && p.variant <= 6) {
-    // attribution probes: 4 = conversions only, 5 = shared-memory stores only, 6 = both through
-    // explicit st.shared instructions
-    if (p.variant == 4) {
-      uint32_t x = 0;
-#pragma unroll
-      for (int j = 0; j < 16; ++j) x ^= Elem<T>::pack2(v[2 * j], v[2 * j + 1]);
-      if (x == 0x12345u) cyc[4] += 1;
-    } else if (p.variant == 5) {
-#pragma unroll
-      for (int g = 0; g < 4; ++g)
-        *reinterpret_cast<float4*>(sb + lane * 64 + ((g ^ ((lane >> 1) & 3)) << 4)) =
-            make_float4(v[4 * g], v[4 * g + 1], v[4 * g + 2], v[4 * g + 3]);
-    } else {
-      const uint32_t base = smem_u32(sb) + lane * 64;
-#pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const uint32_t a0 = Elem<T>::pack2(v[g * 8 + 0], v[g * 8 + 1]), a1 = Elem<T>::pack2(v[g * 8 + 2], v[g * 8 + 3]);
-        const uint32_t a2 = Elem<T>::pack2(v[g * 8 + 4], v[g * 8 + 5]), a3 = Elem<T>::pack2(v[g * 8 + 6], v[g * 8 + 7]);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(base + ((g ^ ((lane >> 1) & 3)) << 4)),
-                     "r"(a0), "r"(a1), "r"(a2), "r"(a3)
-                     : "memory");
-      }
-    }
-    return;
-  }
   if (p.alpha != 1.0f) {
 #pragma unroll
     for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+  }
+  if (part) {
+#pragma unroll
+    for (int g = 0; g < 4; ++g) {
+      const uint32_t aw[4] = {pa[g].x, pa[g].y, pa[g].z, pa[g].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = Elem<T>::unpack2(aw[j]);
+        v[g * 8 + 2 * j] += fa.x;
+        v[g * 8 + 2 * j + 1] += fa.y;
+      }
+    }
+#pragma unroll 1
+    for (int q = src_a + 1; q < n_src; ++q) {  // groups of more than two ranks
+      if (q == self) continue;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const uint4 u = __ldcg(reinterpret_cast<const uint4*>(part + q * part_stride + g * 8));
+        const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = Elem<T>::unpack2(w[j]);
+          v[g * 8 + 2 * j] += f.x;
+          v[g * 8 + 2 * j + 1] += f.y;
+        }
+      }
+    }
   }
   if (p.bias) {
 #pragma unroll
@@ -351,10 +358,8 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtens
     }
   }
   const long long t_2 = TRACE ? clock_ordered() : 0;
-  if (TRACE && p.variant == 2) return;
   fence_proxy_async();
   __syncwarp();
-  if (TRACE && p.variant == 3) return;
   if (lane == 0) {
     if (OUT_F32 && p.accumulate) tma_reduce_add_2d(tmO, sb, n, row0);
     else tma_store_2d(tmO, sb, n, row0);
@@ -365,38 +370,6 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtens
     cyc[0] += t_1 - t_0;        // loads issued, staging buffer free
     cyc[1] += t_2 - t_1;        // math and shared-memory writes
     cyc[2] += clock_ordered() - t_2;  // proxy fence, tile store issued
-  }
-}
-
-// Reduce-scatter: add the 16-bit partial results that the other ranks stored in this rank's
-// staging buffer to the fp32 accumulators of one 32-column chunk (thread = row).  `part` points at
-// this thread's 32 values (64 contiguous bytes) in source 0's copy of the chunk; the copies of
-// the sources are `stride` elements apart; source `self` is the accumulator itself.
-template <typename T>
-__device__ __forceinline__ void add_partials(uint32_t (&r)[32], const T* part, long long stride,
-                                             int n_src, int self) {
-  const uint4 zero4 = make_uint4(0, 0, 0, 0);
-#pragma unroll 1
-  for (int s0 = 0; s0 < n_src; s0 += 2) {
-    const bool ua = s0 != self, ub = (s0 + 1 < n_src) && (s0 + 1 != self);
-    uint4 a[4], b[4];
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      a[g] = ua ? __ldcg(reinterpret_cast<const uint4*>(part + s0 * stride + g * 8)) : zero4;
-      b[g] = ub ? __ldcg(reinterpret_cast<const uint4*>(part + (s0 + 1) * stride + g * 8)) : zero4;
-    }
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      const uint32_t aw[4] = {a[g].x, a[g].y, a[g].z, a[g].w};
-      const uint32_t bw[4] = {b[g].x, b[g].y, b[g].z, b[g].w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 fa = Elem<T>::unpack2(aw[j]);
-        const float2 fb = Elem<T>::unpack2(bw[j]);
-        r[g * 8 + 2 * j] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j]) + (fa.x + fb.x));
-        r[g * 8 + 2 * j + 1] = __float_as_uint(__uint_as_float(r[g * 8 + 2 * j + 1]) + (fa.y + fb.y));
-      }
-    }
   }
 }
 
@@ -440,41 +413,14 @@ __device__ __forceinline__ void epilogue_rows(const GemmParams& p, const CUtenso
   const bool row_ok = row < p.M;
   uint32_t r[32];
   __syncwarp();
-  if (TRACE && p.variant >= 7) {
-    // latency probe: load one chunk (7: one 32-column load, 8: two 16-column loads), wait, read
-    // every register; cycles of load + wait and of the reads, first chunk and later chunks apart
-#pragma unroll 1
-    for (int c = c_first; c < nc; c += c_step) {
-      const long long t0 = clock_ordered();
-      if (p.variant == 7) {
-        tmem_ld_32x32(t_acc + c * 32, r);
-      } else {
-        uint32_t lo[16], hi[16];
-        tmem_ld_32x16(t_acc + c * 32, lo);
-        tmem_ld_32x16(t_acc + c * 32 + 16, hi);
-#pragma unroll
-        for (int j = 0; j < 16; ++j) { r[j] = lo[j]; r[j + 16] = hi[j]; }
-      }
-      tmem_ld_wait();
-      const long long t1 = clock_ordered();
-      uint32_t x = 0, y;
-#pragma unroll
-      for (int j = 0; j < 32; ++j) x ^= r[j];
-      asm volatile("mov.b32 %0, %1;" : "=r"(y) : "r"(x) : "memory");
-      const long long t2 = clock_ordered();
-      cyc[c == c_first ? 0 : 2] += t1 - t0;
-      cyc[c == c_first ? 1 : 3] += t2 - t1 + (y == 0x12345u ? 1 : 0);
-    }
-    return;
-  }
   if (c_first >= nc) return;
   tmem_ld_32x32(t_acc + c_first * 32, r);
 #pragma unroll 1
   for (int c = c_first; c < nc; c += c_step) {
     tmem_ld_wait();
-    if (part) add_partials<T>(r, part + c * 4096, part_stride, n_src, self);
     epilogue_chunk<T, OUT_F32, TRACE>(p, tmO, es, r, row, row_ok, n0 + c * 32, row0, lane,
-                                      c + c_step < nc ? t_acc + (c + c_step) * 32 : 0u, cyc);
+                                      c + c_step < nc ? t_acc + (c + c_step) * 32 : 0u, cyc,
+                                      part ? part + c * 4096 : nullptr, part_stride, n_src, self);
   }
 }
 
@@ -768,7 +714,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
   auto kern = gemm_kernel<T, BN, A_MN, B_MN, OUT_F32, AR, MT>;
   ArParams ar;
   if (arp) ar = *arp;
-  else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; ar.dbg = nullptr; }
+  else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; }
   static bool configured = false;
   if (!configured) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes) !=
@@ -974,8 +920,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const uint32_t cta = cluster_ctarank();   // 0 = leader
   long long* tr = TRACE ? p.trace + static_cast<long long>(blockIdx.x) * kTraceSlots : nullptr;
-  long long* dbg = (AR && ar.dbg) ? ar.dbg + static_cast<long long>(blockIdx.x) * 8 : nullptr;
-  if (AR && dbg && threadIdx.x == 0) dbg[0] = static_cast<long long>(globaltimer_ns());
   if (TRACE && threadIdx.x == 0) tr[0] = clock64();
   const int pair = blockIdx.x >> 1;
   const int npairs = gridDim.x >> 1;
@@ -1144,7 +1088,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         umma_commit_pair(&tfull[acc], 3);
       }
       if (TRACE) { tr[5] = stall_full; tr[6] = stall_acc; tr[7] = clock64(); tr[8] = it; }
-      if (AR && dbg) dbg[7] = static_cast<long long>(globaltimer_ns());
     }
   } else if (warp < 10) {
     const int quarter = warp & 3;      // TMEM lane quarter this warp may access
@@ -1153,8 +1096,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     int it = 0;
     bool ok = true;
     // AR: index (into this rank's owned tiles) of the next one this CTA reduces
-    long long pub_ns = 0;
-    int n_early = 0;
     int next_owned = (AR && !ar.exchange) ? static_cast<int>(blockIdx.x) : 0;
     const int n_owned = !AR ? 0
                         : ar.exchange ? (p.num_tiles - pair + npairs - 1) / npairs
@@ -1320,14 +1261,12 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // release store is cumulative over the writes ordered before it by the barrier
         asm volatile("bar.sync 2, 256;" ::: "memory");
         if (threadIdx.x == 64 && in_range) {
-          const unsigned long long t_p = dbg ? globaltimer_ns() : 0;
           if (ar.exchange) {
             for (int dst = 0; dst < ar.tp; ++dst)
               st_release_sys(ar.flag_a[dst] + static_cast<long long>(ar_tile) * kMaxTp + ar.rank, ar_epoch);
           } else {
             st_release_sys(ar.flag_a[owner] + static_cast<long long>(ar_tile) * kMaxTp + ar.rank, ar_epoch);
           }
-          if (dbg) pub_ns += static_cast<long long>(globaltimer_ns() - t_p);
         }
         // Phase B between tiles: while the tensor core works on the next tile, the epilogue
         // warps look (once, without waiting) whether a tile this CTA is to reduce has arrived
@@ -1361,7 +1300,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                 st_release_sys(ar.flag_b[threadIdx.x - 64] + otile, ar_epoch);
             }
             next_owned += ar.exchange ? 1 : static_cast<int>(gridDim.x);
-            ++n_early;
           }
         }
         continue;
@@ -1383,11 +1321,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     epi_drain(lane);  // the staging buffers must outlive the stores that read them
     if (AR && threadIdx.x == 64) {
       *s_next = next_owned;
-      if (dbg) {
-        dbg[1] = static_cast<long long>(globaltimer_ns());
-        dbg[4] = n_early;
-        dbg[5] = pub_ns;
-      }
     }
   }
 
@@ -1451,7 +1384,6 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (s_ok) ar_reduce_tile<T, BN>(p, ar, tile, num_m128, threadIdx.x, nthreads, true, stage_half);
         __syncthreads();
       }
-      if (dbg && threadIdx.x == 0) dbg[2] = static_cast<long long>(globaltimer_ns());
     } else {
       const int n_owned = (num_ar_tiles - ar.rank + ar.tp - 1) / ar.tp;
       for (int j = *s_next; j < n_owned; j += gridDim.x) {
@@ -1468,13 +1400,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         __syncthreads();
         if (s_ok && threadIdx.x < ar.tp) st_release_sys(ar.flag_b[threadIdx.x] + tile, ar_epoch);
       }
-      if (dbg && threadIdx.x == 0) dbg[2] = static_cast<long long>(globaltimer_ns());
       // phase C: every tile of the output must have arrived in this rank's memory
       for (int tile = blockIdx.x * nthreads + threadIdx.x; tile < num_ar_tiles; tile += gridDim.x * nthreads)
         wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
     }
     __syncthreads();
-    if (dbg && threadIdx.x == 0) dbg[3] = static_cast<long long>(globaltimer_ns());
   }
 
   // teardown: nobody leaves (or frees TMEM) while the peer may still read this CTA's shared
@@ -1515,7 +1445,7 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   }
   ArParams ar;
   if (arp) ar = *arp;
-  else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; ar.dbg = nullptr; }
+  else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; }
   const int pairs = p.num_tiles < max_pairs() ? p.num_tiles : max_pairs();
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs, 1, 1);
@@ -1550,7 +1480,6 @@ static int dispatch_layout_pair(int a_mn, int b_mn, int out_f32, const CUtensorM
 static bool g_pair_default = true;
 static int g_prefetch = 0;             // L2 prefetch distance of the CTA-pair kernel, in k-steps
 static bool g_ar_exchange = false;     // one-hop exchange instead of reduce-scatter + all-gather
-static long long* g_ar_debug = nullptr;
 
 // Measured model of one launch, in kilo-cycles: waves x (main loop of one tile, proportional to
 // K, + epilogue where it does not overlap the next tile) + exposed epilogue of the last tile.
@@ -1664,7 +1593,6 @@ static int gemm_impl(int dtype, int a_mn, int b_mn, const void* A, long long lda
   p.err = err_flag;
   p.trace = nullptr;
   p.prefetch = g_prefetch;
-  p.variant = 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
 #define TP_DISPATCH(T)                                                                   \
   (pair ? (BN == 256 ? dispatch_layout_pair<T, 256>(a_mn, b_mn, out_f32, tmA, tmB, tmO, p, s)  \
@@ -1742,12 +1670,10 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.err = err_flag;
   p.trace = nullptr;
   p.prefetch = g_prefetch;
-  p.variant = 0;
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
   ar.exchange = (g_pair_default && g_ar_exchange) ? 1 : 0;
   ar.rows_per_rank = 0;
-  ar.dbg = g_ar_debug;
   for (int i = 0; i < kMaxTp; ++i) {
     ar.stage[i] = i < tp ? stage_ptrs[i] : nullptr;
     ar.flag_a[i] = i < tp ? flag_a_ptrs[i] : nullptr;
@@ -1796,8 +1722,8 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
   p.num_n_tiles = (N + BN - 1) / BN;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
   if (((M + kBM - 1) / kBM) * p.num_n_tiles > max_tiles) return kErrTooLarge;
-  // Column groups of about one wave of remote row blocks; inside a group the row blocks of the
-  // other ranks first (starting after this rank's rows), this rank's own row blocks last.
+  // The row blocks of the other ranks first (starting after this rank's rows), this rank's own
+  // row blocks last.
   p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
   {
     const long long first_after = static_cast<long long>(rank + 1) * rows_per_rank;
@@ -1808,8 +1734,10 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
       p.m_major = 1;
       p.m_first = first_after >= M ? 0 : static_cast<int>((first_after + 2 * kBM - 1) / (2 * kBM)) % p.num_m_tiles;
       p.order_split = p.num_m_tiles - own_tiles;
-      p.order_group = (max_pairs() + p.order_split - 1) / p.order_split;
-      if (p.order_group > p.num_n_tiles) p.order_group = p.num_n_tiles;
+      // one group: every row block of the other ranks before any of this rank's, so that a
+      // partial is always consumed at least a wave after the peer produced it (column groups
+      // of one wave measured slower: the last group's two phases share a wave)
+      p.order_group = p.num_n_tiles;
     }
   }
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
@@ -1826,10 +1754,9 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
   p.err = err_flag;
   p.trace = nullptr;
   p.prefetch = g_prefetch;
-  p.variant = 0;
   ArParams ar;
   ar.tp = tp; ar.rank = rank; ar.epoch = epoch; ar.epoch_base = epoch_base; ar.max_tiles = max_tiles;
-  ar.exchange = 0; ar.rows_per_rank = rows_per_rank; ar.dbg = nullptr;
+  ar.exchange = 0; ar.rows_per_rank = rows_per_rank;
   for (int i = 0; i < kMaxTp; ++i) {
     ar.stage[i] = i < tp ? stage_ptrs[i] : nullptr;
     ar.flag_a[i] = i < tp ? flag_ptrs[i] : nullptr;
@@ -1864,7 +1791,7 @@ __global__ void advance_counter_kernel(int* counter, int inc) { *counter += inc;
 //   the leader CTA of each pair only.
 extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B, long long ldb,
                              void* out, long long ldo, int M, int N, int K, long long* trace,
-                             int variant, int* err_flag, void* stream) {
+                             int* err_flag, void* stream) {
   using namespace tp;
   if (M <= 0 || N <= 0 || K <= 0 || (bn != 128 && bn != 256) || !trace) return kErrBadArgument;
   if ((N % 8) || (lda % 8) || (ldb % 8) || (ldo % 8)) return kErrBadArgument;
@@ -1887,7 +1814,6 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   p.err = err_flag;
   p.trace = trace;
   p.prefetch = g_prefetch;
-  p.variant = variant;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   return bn == 256 ? launch_gemm_pair<__half, 256, false, false, false, true>(tmA, tmB, tmO, p, s)
                    : launch_gemm_pair<__half, 128, false, false, false, true>(tmA, tmB, tmO, p, s);
@@ -1898,13 +1824,6 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
 // reduce-scatter to an owner rank, then all-gather (two hops).  On two B200s the one-hop form
 // measured slower (86 vs 72 us for 1024 x 5120 x 2560).
 extern "C" void tp_gemm_ar_set_exchange(int enabled) { tp::g_ar_exchange = enabled != 0; }
-
-// Timing probe of the fused all-reduce (CTA-pair kernel): `buf` is a device array of 8 int64 per
-// CTA (296 CTAs at most) or null to switch the probe off.  Slots, in globaltimer nanoseconds:
-// 0 kernel entry, 1 all own tiles sent and published, 2 all assigned reductions done, 3 all
-// results arrived (exit), 4 reductions done between tiles, 5 ns spent in the release stores that
-// publish tiles, 7 last MMA issued (leader CTA of each pair).
-extern "C" void tp_gemm_ar_set_debug(long long* buf) { tp::g_ar_debug = buf; }
 
 // L2 prefetch distance (in 64-element k-steps) of the CTA-pair kernel's producer; 0 switches it off.
 extern "C" void tp_gemm_set_prefetch(int k_steps) { tp::g_prefetch = k_steps < 0 ? 0 : k_steps; }

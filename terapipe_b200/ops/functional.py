@@ -84,12 +84,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, *, a_mn=False, b_m
 GEMM_TRACE_SLOTS = 24
 
 
-def gemm_pair_trace(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 256,
-                    variant: int = 0) -> torch.Tensor:
+def gemm_pair_trace(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int = 256) -> torch.Tensor:
     """Run the CTA-pair GEMM (fp16, ``out = a @ b.T``) in its tracing build and return the
     per-CTA phase stamps, an int64 tensor ``[n_ctas, 24]`` of SM clock cycles (slot meanings
-    are listed at ``tp_gemm_trace`` in ``csrc/gemm_sm100.cu``).  ``variant`` 1-3 truncate the
-    epilogue (the output is then not written) to attribute its cost."""
+    are listed at ``tp_gemm_trace`` in ``csrc/gemm_sm100.cu``)."""
     M, N = out.shape
     K = a.shape[1]
     assert a.dtype == torch.float16 and b.dtype == torch.float16 and out.dtype == torch.float16
@@ -98,7 +96,7 @@ def gemm_pair_trace(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, bn: int
     n_ctas = 2 * min(tiles, sms // 2)
     trace = torch.zeros(n_ctas, GEMM_TRACE_SLOTS, dtype=torch.int64, device=a.device)
     st = cuda_lib().tp_gemm_trace(int(bn), a.data_ptr(), a.stride(0), b.data_ptr(), b.stride(0),
-                                  out.data_ptr(), out.stride(0), M, N, K, trace.data_ptr(), int(variant),
+                                  out.data_ptr(), out.stride(0), M, N, K, trace.data_ptr(),
                                   status_word(a.device).data_ptr(), _stream())
     check(st, "tp_gemm_trace")
     return trace

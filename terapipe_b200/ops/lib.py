@@ -75,9 +75,8 @@ SIGNATURES = {
     "tp_gemm_set_pair_default": [I],
     "tp_gemm_set_prefetch": [I],
     "tp_gemm_ar_set_exchange": [I],
-    "tp_gemm_ar_set_debug": [P],
     "tp_link_probe": [P, L, I, P],
-    "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, I, P, P],
+    "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, P, P],
     "tp_dp_reduce_adam": [I, I, I, I, P, P, P, P, P, P, P, L, L, P, F, F, F, F, F, F, P, P],
     "tp_set_wait_limit_ns": [L],
     "tp_gemm_ag": [I, I, P, L, P, L, P, L, I, I, I, P, I, P, I, P, L, P, P, I, I, I, P, P],
@@ -86,6 +85,7 @@ SIGNATURES = {
     "tp_layernorm_bwd_accum_push": [I, P, P, P, P, P, P, P, P, I, I, I, I, P, I, P, P, P],
     "tp_layernorm_bwd_finish_assign": [P, I, I, P, P, P],
     "tp_ag_push": [P, L, P, P, I, I, I, P, P, P],
+    "tp_ag_copy": [P, L, P, P, I, I, I, P, P],
     "tp_group_barrier": [P, I, I, I, P, P, P],
     "tp_peer_sum": [P, I, P, I, I, P],
     "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],

@@ -219,6 +219,8 @@ class StageEngine:
         self._ag_calls_per_step = n_slices * (2 * self.n_layers + self.n_layers + max(self.n_layers - 1, 0)
                                               + (0 if self.is_last else 1)) + 1
         self._ag_calls = 0
+        self._ag_stream, self._ag_pending = None, False
+        self._ag_in_kernel = os.environ.get("TERAPIPE_AG_PUSH", "0") == "1"
 
     # ------------------------------------------------------------------ parameters
     def param(self, layer: int, name: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -442,7 +444,39 @@ class StageEngine:
         if st:
             F.check(st, "tp_gemm_rs")
 
+    def _ag_async(self, name, row, rows):
+        """All-gather of rows ``[row, row + rows)`` of the pooled matrix ``name`` (just written
+        locally on the current stream): copy-engine copies to every peer plus a flag, on a side
+        stream, so that the consumer (``_gemm_ag``, which starts with this rank's own row blocks)
+        runs meanwhile.  ``TERAPIPE_AG_PUSH=1`` selects the variant in which the producing
+        LayerNorm kernel stores to the peers itself."""
+        self._ag_calls += 1
+        if self._ag_stream is None:
+            self._ag_stream = torch.cuda.Stream()
+        side = self._ag_stream
+        side.wait_stream(torch.cuda.current_stream())
+        off = self._pool_off[name] + row * self.H * self.es
+        local = self.ar.buf.local_ptr + off
+        st = self.lib.tp_ag_copy(local, rows * self.H * self.es, self.ar.out_ptrs(off), self._ag_flag_ptrs,
+                                 self.tp, self.tp_idx, self._ag_calls, self.ag_epoch_base.data_ptr(),
+                                 side.cuda_stream)
+        if st:
+            F.check(st, "tp_ag_copy")
+        self._ag_pending = True
+
+    def _ag_join(self):
+        """The side stream's copies become part of the current stream's order again (end of a
+        slice; required before a captured segment closes)."""
+        if self._ag_pending:
+            torch.cuda.current_stream().wait_stream(self._ag_stream)
+            self._ag_pending = False
+
     def _ln_fwd_push(self, x, gamma, beta, dst_name, row, mean, rstd, rows):
+        if not self._ag_in_kernel:
+            dst = self.ar.buf.local_ptr + self._pool_off[dst_name] + row * self.H * self.es
+            self.lib.tp_layernorm_fwd(self.dt, x, gamma, beta, dst, mean, rstd, rows, self.H, 1e-5,
+                                      self._stream)
+            return self._ag_async(dst_name, row, rows)
         self._ag_calls += 1
         st = self.lib.tp_layernorm_fwd_push(self.dt, x, gamma, beta, self._pool_ptrs(dst_name, row), mean,
                                             rstd, rows, self.H, 1e-5, self.tp, self.tp_idx,
@@ -453,6 +487,11 @@ class StageEngine:
             F.check(st, "tp_layernorm_fwd_push")
 
     def _ln_bwd_push(self, dy, x, mean, rstd, gamma, dres, dst_name, row, slots, rows):
+        if not self._ag_in_kernel:
+            dst = self.ar.buf.local_ptr + self._pool_off[dst_name] + row * self.H * self.es
+            self.lib.tp_layernorm_bwd_accum(self.dt, dy, x, mean, rstd, gamma, dres, dst, slots, rows,
+                                            self.H, self._stream)
+            return self._ag_async(dst_name, row, rows)
         self._ag_calls += 1
         st = self.lib.tp_layernorm_bwd_accum_push(self.dt, dy, x, mean, rstd, gamma, dres,
                                                   self._pool_ptrs(dst_name, row), slots, rows, self.H,
@@ -502,6 +541,7 @@ class StageEngine:
                           self.X[l + 1].data_ptr() + r0 * H * es, H, T, H, Fl, rpr,
                           bias=self._p(l, "fc2.bias"),
                           residual=self.xmid[l].data_ptr() + r0 * H * es, ldr=H)
+        self._ag_join()
 
     # ------------------------------------------------------------------ forward of one slice
     def _forward_slice(self, sl) -> None:
@@ -634,14 +674,7 @@ class StageEngine:
         n = self.n_layers
         if not self.is_last and n:
             # the output gradient arrived from the next stage as this rank's shard: all-gather it
-            self._ag_calls += 1
-            off = self._pool_off[f"dXo{n - 1}"] + m0 * H * es
-            st = lib.tp_ag_push(self.dXo[n - 1].data_ptr() + m0 * H * es, rpr * H * es,
-                                self.ar.out_ptrs(off), self._ag_flag_ptrs, self.tp, self.tp_idx,
-                                self._ag_calls, self.ag_epoch_base.data_ptr(),
-                                self._push_counter.data_ptr(), s)
-            if st:
-                F.check(st, "tp_ag_push")
+            self._ag_async(f"dXo{n - 1}", m0, rpr)
         for l in reversed(range(n)):
             st = self.stats[l].data_ptr()
             fa = self.fa[l].data_ptr() + r0 * Fl * es
@@ -688,6 +721,7 @@ class StageEngine:
                 lib.tp_layernorm_bwd_accum(dt, dln_mine, x_mine, st + m0 * 4, st + (self.rows + m0) * 4,
                                            self._p(l, "attn_ln.weight"), dmid_mine, dnext, slots, rpr,
                                            H, s)
+        self._ag_join()
 
     def _weight_grads(self) -> None:
         """Weight and bias gradients of every layer over all ``L*B`` rows at once:

@@ -41,7 +41,7 @@ class NCCLTransformerRunner:
                  data_parallel_size: int, model_parallel_size: int, pipeline_parallel_size: int,
                  rank: int, local_rank: int, mixed_precision: bool = False, use_mpi: bool = False,
                  init_process_group: bool = False, checkpoint_gradients: bool = False,
-                 engine: str = "auto", dtype=torch.float16, tp_comm: str = "nccl",
+                 engine: str = "auto", dtype=torch.float16, tp_comm: str = "fused",
                  use_graph=None, init: str = "device"):
         self.config = config
         self.batch_slices, self.seq_slices = list(batch_slices), list(seq_slices)
@@ -89,8 +89,15 @@ class NCCLTransformerRunner:
         impl = self.impl
         if not impl.is_first:
             return None
-        g = torch.Generator().manual_seed(977 + 7919 * impl.dp_idx + self._step)
         c = self.config
+        seed = 977 + 7919 * impl.dp_idx + self._step
+        if torch.cuda.is_available() and self.engine_kind == "b200":
+            # drawn on the device, as the reference does (test_transformer_terapipe.py:181-189):
+            # the timed step must not contain host random-number generation or a pageable copy
+            g = torch.Generator(device=impl.device).manual_seed(seed)
+            return torch.randn(c.seq_len, c.batch_size, c.embedding_dim, generator=g,
+                               device=impl.device, dtype=impl.dtype)
+        g = torch.Generator().manual_seed(seed)
         return torch.randn(c.seq_len, c.batch_size, c.embedding_dim, generator=g)
 
     def step(self):

@@ -122,7 +122,7 @@ def main():
     parser.add_argument("--flush-every", type=int, default=100)
     parser.add_argument("--max-points", type=int, default=None)
     parser.add_argument("--out-dir", type=str, default="performance_model_data")
-    parser.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
+    parser.add_argument("--tp-comm", default="fused", choices=["nccl", "fused", "sp"])
     args = parser.parse_args()
     cli.resolve_ranks(args)
     if args.world_size > 1:

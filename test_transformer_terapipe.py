@@ -35,7 +35,7 @@ def main():
     parser.add_argument("--verbose", action="store_true", default=False)
     parser.add_argument("--checkpoint-gradients", action="store_true", default=False)
     parser.add_argument("--memory-limit", type=float, default=None)
-    parser.add_argument("--tp-comm", default="nccl", choices=["nccl", "fused"])
+    parser.add_argument("--tp-comm", default="fused", choices=["nccl", "fused", "sp"])
     args = parser.parse_args()
     cli.resolve_ranks(args)
     as_ints = lambda s: cli.parse_comma_delimited_arg(s, int)  # noqa: E731

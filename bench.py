@@ -89,6 +89,8 @@ def parse_args():
     ap.add_argument("--launch-plan", action="store_true",
                     help="stages that run eagerly replay recorded launch lists (see runtime/launch_plan.py)")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--checkpoint-gradients", action="store_true",
+                    help="reference arm: recompute the attention core in backward (this library always does)")
     ap.add_argument("--blocks", default="auto",
                     help="'auto' (the blocks of this GPU count), 'none', or a comma list of block names")
     ap.add_argument("--block-timeout", type=float, default=None,
@@ -439,7 +441,8 @@ def main():
 
     main_spec = dict(model=args.model, n_layers=args.n_layers, batch=args.batch, tp=args.tp,
                      pp=args.pp if args.pp is not None else world // args.tp,
-                     seq_slices=args.seq_slices, batch_slices=args.batch_slices)
+                     seq_slices=args.seq_slices, batch_slices=args.batch_slices,
+                     checkpoint_gradients=args.checkpoint_gradients)
     deadline.arm(2 * limit, "main")
     blk = arm.measure(main_spec, args.steps, warmup, main=True)
     deadline.disarm()

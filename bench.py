@@ -26,9 +26,9 @@ the timed region.
 ``--impl reference`` runs the unmodified reference (installed under ``baseline/_ref``) through
 its own ``NCCLTransformerRunner.step`` on the same models, layouts and slices, block by block.
 
-Every block runs under a host-side deadline: if it is still running after ``--block-timeout``
-seconds, rank 0 prints the line with what has been measured so far (the block is marked
-``timed_out``) and every rank leaves with status 0, so one stuck block cannot lose the others.
+The further blocks run in child processes (one per rank, with a process group of their own) under
+``--block-timeout`` seconds each: a block that fails or hangs is reported in its own entry
+(``error`` / ``timed_out``) and cannot lose the numbers measured before it.
 """
 from __future__ import annotations
 
@@ -93,6 +93,7 @@ def parse_args():
                     help="reference arm: recompute the attention core in backward (this library always does)")
     ap.add_argument("--blocks", default="auto",
                     help="'auto' (the blocks of this GPU count), 'none', or a comma list of block names")
+    ap.add_argument("--child-block", default=None, help=argparse.SUPPRESS)
     ap.add_argument("--block-timeout", type=float, default=None,
                     help="seconds a single block may take (default 420 ours, 900 reference)")
     return ap.parse_args()
@@ -412,6 +413,8 @@ def make_arm(args):
 
 def main():
     args = parse_args()
+    if args.child_block:
+        return child_main(args)
     rank, world, local = dist_env()
     assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
     warmup = max(args.warmup, 3)
@@ -467,29 +470,60 @@ def main():
         names = []
     else:
         names = [n for n in args.blocks.split(",") if n]
-    for name in names:
-        deadline.arm(limit, name)
+    # Every further block runs in child processes, one per rank, that form a process group of
+    # their own: a block that faults, runs out of memory or hangs ends with its children and
+    # costs only its own entry, never the numbers measured before it.
+    arm.finish()                       # the parent's process group and device memory are released
+    gc.collect()
+    try:
+        import torch
+        torch.cuda.empty_cache()
+    except Exception:  # noqa: BLE001
+        pass
+    base_port = int(os.environ.get("MASTER_PORT", "29500"))
+    for i, name in enumerate(names):
+        if name != "tp_block" and HEADLINE_BLOCKS[name]["tp"] * HEADLINE_BLOCKS[name]["pp"] != world:
+            out[name] = {"skipped": "needs %d GPUs" % (HEADLINE_BLOCKS[name]["tp"] * HEADLINE_BLOCKS[name]["pp"])}
+            continue
+        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(base_port + 101 + 7 * i),
+                   RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local))
+        cmd = [sys.executable, os.path.abspath(__file__), "--child-block", name] + sys.argv[1:]
         try:
-            if name == "tp_block":
-                spec = dict(TP_BLOCK, tp=world)
-                out[name] = arm.tp_block(spec, min(args.steps, spec["steps"]), warmup)
-            else:
-                spec = dict(HEADLINE_BLOCKS[name])
-                if spec["tp"] * spec["pp"] != world:
-                    out[name] = {"skipped": f"needs {spec['tp'] * spec['pp']} GPUs"}
-                    continue
-                out[name] = arm.measure(spec, min(args.steps, spec["steps"]), warmup)
-        except Exception as e:  # noqa: BLE001
-            # The other ranks may be inside a collective of this block: report what exists and
-            # leave; their own deadlines end them.  (Rank 0 prints; any other rank just leaves
-            # and rank 0's deadline prints the line.)
-            out[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
-            emit()
-            sys.stdout.flush()
-            os._exit(0)
-        finally:
-            deadline.disarm()
+            res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                                 timeout=limit)
+            entry = None
+            for line in res.stdout.splitlines():
+                if line.startswith("{"):
+                    entry = json.loads(line)
+            if entry is None:
+                tail = (res.stderr or "").strip().splitlines()[-3:]
+                entry = {"error": f"child exited with status {res.returncode}", "stderr_tail": tail}
+        except subprocess.TimeoutExpired:
+            entry = {"timed_out": True, "limit_s": limit}
+        if rank == 0:
+            out[name] = entry
     emit()
+
+
+def child_main(args):
+    """One further block in a process group of its own (see main); rank 0 prints the block."""
+    rank, world, local = dist_env()
+    warmup = max(args.warmup, 3)
+    arm = make_arm(args)
+    why = arm.setup(rank, world, local)
+    if why is not None:
+        if rank == 0:
+            print(json.dumps({"unavailable": why}), flush=True)
+        return
+    name = args.child_block
+    if name == "tp_block":
+        spec = dict(TP_BLOCK, tp=world)
+        entry = arm.tp_block(spec, min(args.steps, spec["steps"]), warmup)
+    else:
+        spec = dict(HEADLINE_BLOCKS[name])
+        entry = arm.measure(spec, min(args.steps, spec["steps"]), warmup)
+    if rank == 0:
+        print(json.dumps(entry), flush=True)
     arm.finish()
 
 

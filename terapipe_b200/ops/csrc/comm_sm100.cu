@@ -98,6 +98,7 @@ __device__ __forceinline__ bool spin_until(const int* p, int target, int* err, i
   unsigned spins = 0;
   while (ld_acquire_sys_i(p) < target) {
     if ((++spins & 0x3F) == 0) {
+      if (err && *reinterpret_cast<volatile int*>(err) != 0) return false;  // already out of step
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > g_wait_limit_ns) {

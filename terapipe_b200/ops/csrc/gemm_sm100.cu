@@ -48,7 +48,10 @@ struct GemmParams {
   // both.  order_first_only = 1 applies the split to the first group only.  The all-gather
   // variant puts the row blocks whose operands are local first; the reduce-scatter variant puts
   // the row blocks this rank owns last, a whole phase after the peers produced their share.
-  int num_n_tiles, m_major, m_first, order_split, order_group, order_first_only;
+  // order_pipelined = 1 interleaves the phases of successive groups (A0 A1 B0 A2 B1 ... B_last):
+  // a group's second phase then runs one first phase after its own, while its B tiles are still
+  // in L2.
+  int num_n_tiles, m_major, m_first, order_split, order_group, order_first_only, order_pipelined;
   // All-gather wait (CTA-pair kernel, A stored [M][K]): rows [s * ag_rows, (s + 1) * ag_rows) of A
   // were written into this GPU's memory by rank s; before loading rows of another rank the
   // producer waits until ag_flags[s] >= ag_epoch + *ag_epoch_base.  ag_flags == nullptr: no wait.
@@ -105,6 +108,9 @@ __device__ __forceinline__ bool wait_flag(const int* p, int target, const WaitCt
   while (ld_acquire_sys(p) < target) {
     if ((++spins & 0x3F) == 0) {
       if (*w.abort_smem) return false;
+      // an earlier wait of this step already ran out (here or in an earlier kernel): the peers
+      // are out of step for good, so do not spend another wait limit on every later flag
+      if (w.err_global && *reinterpret_cast<volatile int*>(w.err_global) != 0) return false;
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > g_wait_limit_ns) {
@@ -378,6 +384,30 @@ __device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, 
   if (!p.m_major) {
     m_idx = tile % p.num_m_tiles;
     n_idx = tile / p.num_m_tiles;
+    return;
+  }
+  if (p.order_pipelined) {
+    const int G = p.order_group, split = p.order_split, rest = p.num_m_tiles - split;
+    const int ng = (p.num_n_tiles + G - 1) / G;
+    int t = tile, phase = -1, g = 0;
+    const int c0 = min(G, p.num_n_tiles);
+    if (t < split * c0) {
+      phase = 0;
+    } else {
+      t -= split * c0;
+      for (int k = 1; k < ng; ++k) {
+        const int ck = min(G, p.num_n_tiles - k * G);
+        if (t < split * ck) { phase = 0; g = k; break; }
+        t -= split * ck;
+        if (t < rest * G) { phase = 1; g = k - 1; break; }
+        t -= rest * G;
+      }
+      if (phase < 0) { phase = 1; g = ng - 1; }
+    }
+    int j;
+    if (phase == 0) { j = t % split; n_idx = g * G + t / split; }
+    else { j = split + t % rest; n_idx = g * G + t / rest; }
+    m_idx = (j + p.m_first) % p.num_m_tiles;
     return;
   }
   const int per_group = p.num_m_tiles * p.order_group;
@@ -1569,7 +1599,7 @@ static int gemm_impl(int dtype, int a_mn, int b_mn, const void* A, long long lda
   p.num_m_tiles = (M + BM - 1) / BM;
   p.num_n_tiles = (N + BN - 1) / BN;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0; p.order_pipelined = 0;
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   if (ag) {
     // the first wave of tiles takes row blocks of this rank only: their operands are local
@@ -1655,7 +1685,7 @@ extern "C" int tp_gemm_ar(int dtype, int b_mn, const void* A, long long lda, con
   p.num_m_tiles = (M + BM - 1) / BM;
   p.num_n_tiles = (N + BN - 1) / BN;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0; p.order_pipelined = 0;
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   if (((M + kBM - 1) / kBM) * ((N + BN - 1) / BN) > max_tiles) return kErrTooLarge;
   CUtensorMap tmA, tmB;
@@ -1724,7 +1754,7 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
   if (((M + kBM - 1) / kBM) * p.num_n_tiles > max_tiles) return kErrTooLarge;
   // The row blocks of the other ranks first (starting after this rank's rows), this rank's own
   // row blocks last.
-  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0; p.order_pipelined = 0;
   {
     const long long first_after = static_cast<long long>(rank + 1) * rows_per_rank;
     const long long my_end = first_after < M ? first_after : M;
@@ -1738,6 +1768,19 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
       // partial is always consumed at least a wave after the peer produced it (column groups
       // of one wave measured slower: the last group's two phases share a wave)
       p.order_group = p.num_n_tiles;
+      // A large weight shard (it does not stay in L2 between the two phases) is walked in column
+      // groups with the phases of successive groups interleaved; the group is sized so that
+      // about 10 us of other tiles lie between a partial's production and its use.
+      if (static_cast<long long>(N) * K * 2 > (48ll << 20)) {
+        const float tile_us = 0.0046f * static_cast<float>(K);
+        int g = static_cast<int>(max_pairs() * 10.0f / (tile_us * p.order_split)) + 1;
+        if (g < 2) g = 2;
+        if (g < p.num_n_tiles) {
+          const int ng = (p.num_n_tiles + g - 1) / g;
+          p.order_group = (p.num_n_tiles + ng - 1) / ng;
+          p.order_pipelined = 1;
+        }
+      }
     }
   }
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
@@ -1805,7 +1848,7 @@ extern "C" int tp_gemm_trace(int bn, const void* A, long long lda, const void* B
   p.num_m_tiles = (M + 2 * kBM - 1) / (2 * kBM);
   p.num_n_tiles = (N + bn - 1) / bn;
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
-  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0;
+  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0; p.order_pipelined = 0;
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   p.out = out; p.ldo = ldo;
   p.bias = nullptr; p.residual = nullptr; p.ldr = 0;

@@ -40,13 +40,14 @@ def format_json(r):
 class TerapipeLatencyModel:
     """One layer, one slice: the slice of ``seqlen`` tokens attends to ``ctx`` cached rows."""
 
-    def __init__(self, model_name, batch_size, seqlen, ctx, mixed_precision=True, tp_comm="nccl"):
+    def __init__(self, model_name, batch_size, seqlen, ctx, mixed_precision=True, tp_comm="fused", reps=4):
+        self.reps = reps
         from terapipe_b200.runtime.engine import StageEngine
         cfg = TransformerConfig.from_predefined_model(model_name, batch_size=batch_size, n_layers=1)
         cfg.seq_len = ctx + seqlen
         slices = ([ctx] if ctx else []) + [seqlen]
         self.engine = StageEngine(cfg, [batch_size], slices, init="device", use_graph=False,
-                                  tp_comm=tp_comm)
+                                  tp_comm=tp_comm, segment_graphs=False)
         self.engine.set_input(torch.randn(cfg.seq_len, batch_size, cfg.embedding_dim))
         self.target = self.engine.slices[0][-1]
 
@@ -56,25 +57,38 @@ class TerapipeLatencyModel:
         if e.ar is not None:
             e.lib.tp_advance_counter(e.ar_epoch_base.data_ptr(), e._ar_calls_per_step, e._stream)
             e._ar_calls = 0
-        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        if getattr(e, "sp", False):
+            raise ValueError("the latency table is measured with tp_comm 'fused' or 'nccl'")
+        # Steady state, not launch-bound: inside a training step the launches of a slice are
+        # replayed from a CUDA graph, so the device never waits for the host.  Here every timed
+        # phase is repeated `reps` times behind a short device-side sleep that lets the host
+        # queue all launches first; the events then measure back-to-back kernel time.
+        reps = self.reps
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
         t0 = time.time()
+        torch.cuda._sleep(400_000 * reps)
         ev[0].record()
-        e._forward_slice(self.target)
+        for _ in range(reps):
+            e._forward_slice(self.target)
         ev[1].record()
-        py_fwd = time.time() - t0
+        py_fwd = (time.time() - t0) / reps
         t0 = time.time()
-        e._backward_slice(self.target)
+        torch.cuda._sleep(600_000 * reps)
         ev[2].record()
-        py_bwd = time.time() - t0
+        for _ in range(reps):
+            e._backward_slice(self.target)
+        ev[3].record()
+        py_bwd = (time.time() - t0) / reps
         # weight gradients run once per iteration over all rows, not per slice: they are timed
         # apart and reported per token so the planner can add them as a per-layer constant
         e._weight_grads()
-        ev[3].record()
-        e._reduce_and_update()
         ev[4].record()
+        e._reduce_and_update()
+        ev[5].record()
         torch.cuda.synchronize()
-        return (py_fwd, ev[0].elapsed_time(ev[1]) / 1e3, py_bwd, ev[1].elapsed_time(ev[2]) / 1e3,
-                ev[3].elapsed_time(ev[4]) / 1e3, ev[2].elapsed_time(ev[3]) / 1e3 / e.rows)
+        return (py_fwd, ev[0].elapsed_time(ev[1]) / 1e3 / reps, py_bwd,
+                ev[2].elapsed_time(ev[3]) / 1e3 / reps, ev[4].elapsed_time(ev[5]) / 1e3,
+                ev[3].elapsed_time(ev[4]) / 1e3 / e.rows)
 
     def run(self, n_steps=10, warmup_steps=5):
         # the prefix rows must hold valid keys/values: run the context slice once
@@ -156,6 +170,7 @@ def main():
         try:
             m = TerapipeLatencyModel(args.model, b, s, c, tp_comm=args.tp_comm)
             table[f"{b}_{s}_{c}"] = m.run(args.n_steps, args.warmup_steps)
+            m.engine.close()      # unmaps the peer buffers of this point (collective)
             del m
         except torch.cuda.OutOfMemoryError:
             flush()

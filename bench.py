@@ -55,6 +55,10 @@ METRIC = "training throughput (tokens/s), GPT-3-shaped decoder, fwd+bwd+Adam per
 # Extra blocks by GPU count.  `steps` caps the timed steps of the block (warm-up is always >= 3).
 HEADLINE_BLOCKS = {
     "headline": dict(model="gpt3-13b", batch=8, tp=2, pp=4, seq_slices=16, batch_slices=1, steps=5),
+    # the same layout with the batch / token slices chosen by the dynamic program over the B200
+    # latency tables (both arms read the same committed schedule)
+    "headline_planned": dict(model="gpt3-13b", batch=8, tp=2, pp=4, schedule="dp_results.kernel_model.json",
+                             seq_slices=16, batch_slices=1, steps=5),
     "headline_tp8": dict(model="gpt3-175b", n_layers=8, batch=2, tp=8, pp=1, seq_slices=8,
                          batch_slices=1, steps=5),
     "headline_44b": dict(model="gpt3-44b", batch=4, tp=4, pp=2, seq_slices=8, batch_slices=1,
@@ -220,6 +224,14 @@ def slices_for(spec, seq_len, args=None):
                      e.get("pipeline_length") == spec["pp"] and e.get("batch_size") == spec["batch"]]
             sched = match[0] if match else sched[args.schedule_index]
         return list(sched["batch_slices"]), list(sched["input_slices"])
+    if spec.get("schedule"):
+        # the entry the slice planner wrote for this model and layout (a committed dp_results file)
+        with open(os.path.join(ROOT, spec["schedule"])) as f:
+            for e in json.load(f):
+                if (e.get("model_name") == spec["model"] and e.get("model_parallel_size") == spec["tp"]
+                        and e.get("pipeline_length") == spec["pp"] and e.get("batch_size") == spec["batch"]):
+                    return list(e["batch_slices"]), list(e["input_slices"])
+        raise ValueError(f"no schedule for {spec['model']} in {spec['schedule']}")
     if "seq_slice_list" in spec:
         return list(spec["batch_slice_list"]), list(spec["seq_slice_list"])
     return (uniform_slice(spec["batch"], spec.get("batch_slices", 1)),

@@ -248,3 +248,23 @@ def test_module_style_helpers_exist_and_build_a_stage():
     y = pipelined(torch.randn(config.seq_len, 2, config.embedding_dim))
     tpipe.loss_func(y).backward()
     assert all(p.grad is not None for p in pipelined.parameters())
+
+
+def test_assign_cache_backward_leaves_the_incoming_gradient_untouched():
+    """Autograd may hand backward a tensor the caller still owns (``grad_outputs``): the KV-append
+    op must build the earlier cache's gradient in a new tensor."""
+    import torch
+    from terapipe_b200.models.layers import assign_cache_
+    cache = torch.zeros(2, 6, 3, requires_grad=True)
+    value = torch.randn(2, 2, 3, requires_grad=True)
+    idx = (slice(None), slice(2, 4))
+    out = assign_cache_(cache, value, idx)
+    g = torch.randn(2, 6, 3)
+    g_before = g.clone()
+    g_cache, g_value = torch.autograd.grad(out, [cache, value], grad_outputs=g)
+    assert torch.equal(g, g_before)
+    assert torch.equal(g_value, g_before[idx])
+    assert torch.equal(g_cache[idx], torch.zeros(2, 2, 3))
+    keep = torch.ones(6, dtype=torch.bool)
+    keep[2:4] = False
+    assert torch.equal(g_cache[:, keep], g_before[:, keep])

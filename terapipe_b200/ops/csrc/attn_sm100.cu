@@ -156,6 +156,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // set-up done; from here on the predecessor's results are read
   const uint32_t tmem = sh->tmem_slot;
   const uint32_t tO = tmem + 128;   // S[0] at 0, S[1] at 64, O at 128
 
@@ -331,6 +332,7 @@ __global__ void attn_delta_kernel(const T* __restrict__ o, long long ld_o, const
                                   long long delta_stride, int c, int t, int b, int h, int D) {
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
+  pdl_wait();
   if (warp >= t * b * h) return;
   const int hi = warp % h;
   const int bi = (warp / h) % b;
@@ -435,6 +437,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  pdl_wait();  // set-up done; from here on the predecessor's results are read
   const uint32_t tmem = sh->tmem_slot;
   // columns: S[0] 0, S[1] 64, dP[0] 128, dP[1] 192, Acc1 256, Acc2 256 + D
   const uint32_t tA1 = tmem + 256, tA2 = tmem + 256 + D;
@@ -676,8 +679,9 @@ static int attn_fwd_launch(const void* qkv, const AttnParams& p, bool bf16, cuda
   static bool cfg = false;
   if (!cfg) { if (!set_smem(kern, fwd_smem<D>())) return kErrLaunch; cfg = true; }
   dim3 grid((p.t + 127) / 128, p.b * p.h);
-  kern<<<grid, kAttnThreads, fwd_smem<D>(), s>>>(tmQ, tmKV, p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+  return launch_pdl(kern, grid, dim3(kAttnThreads), fwd_smem<D>(), s, 1, tmQ, tmKV, p) == cudaSuccess
+             ? kOk
+             : kErrLaunch;
 }
 
 template <typename T, int D>
@@ -694,9 +698,9 @@ static int attn_bwd_launch(const void* qkv, const void* o, const void* do_full, 
     const int threads = 256;
     const int blocks = static_cast<int>((warps * 32 + threads - 1) / threads);
     const T* do_slice = static_cast<const T*>(do_full) + static_cast<long long>(p.c) * p.b * ld_do;
-    attn_delta_kernel<T><<<blocks, threads, 0, s>>>(static_cast<const T*>(o), p.ld_o, do_slice,
-                                                    ld_do, p.delta, p.lse_stride, p.c, p.t, p.b,
-                                                    p.h, D);
+    if (launch_pdl(attn_delta_kernel<T>, dim3(blocks), dim3(threads), 0, s, 1, static_cast<const T*>(o),
+                   p.ld_o, do_slice, ld_do, p.delta, p.lse_stride, p.c, p.t, p.b, p.h, D) != cudaSuccess)
+      return kErrLaunch;
   }
   auto k0 = attn_bwd_kernel<T, D, 0>;
   auto k1 = attn_bwd_kernel<T, D, 1>;
@@ -706,9 +710,13 @@ static int attn_bwd_launch(const void* qkv, const void* o, const void* do_full, 
     cfg = true;
   }
   dim3 grid((p.t + 127) / 128, p.b * p.h);
-  k0<<<grid, kBwdThreads, bwd_smem<D, 0>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
-  k1<<<grid, kBwdThreads, bwd_smem<D, 1>(), s>>>(tm128, tm64, tmdO128, tmdO64, p);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+  if (launch_pdl(k0, grid, dim3(kBwdThreads), bwd_smem<D, 0>(), s, 1, tm128, tm64, tmdO128, tmdO64, p) !=
+      cudaSuccess)
+    return kErrLaunch;
+  return launch_pdl(k1, grid, dim3(kBwdThreads), bwd_smem<D, 1>(), s, 1, tm128, tm64, tmdO128, tmdO64, p) ==
+                 cudaSuccess
+             ? kOk
+             : kErrLaunch;
 }
 
 }  // namespace tp

@@ -6,6 +6,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
+
+#include <utility>
 
 namespace tp {
 
@@ -94,6 +97,45 @@ inline bool make_tmap_out(CUtensorMap* out, const void* base, uint64_t cols, uin
     return false;
   }
   return true;
+}
+
+// Launch with programmatic stream serialization (see pdl_wait in ptx.cuh).  The kernel must call
+// pdl_wait() in every thread before its first access to global data.  tp_set_pdl(0) (or the
+// environment variable TERAPIPE_PDL=0 at first use) turns the attribute off.
+inline int& pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* e = getenv("TERAPIPE_PDL");
+    enabled = (e && e[0] == '0') ? 0 : 1;
+  }
+  return enabled;
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, int cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[2];
+  int n = 0;
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  if (pdl_enabled()) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
 }
 
 inline int num_sms() {

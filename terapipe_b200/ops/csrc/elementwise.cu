@@ -112,6 +112,7 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
   __shared__ float red[2 * G::kRowsPerCta * WPR + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int grp = warp / WPR, wr = warp % WPR;
+  pdl_wait();
   const long long row = static_cast<long long>(blockIdx.x) * G::kRowsPerCta + grp;
   const bool row_ok = row < rows;
   float v[NV][8];
@@ -183,6 +184,7 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   for (int i = 0; i < NV; ++i)
 #pragma unroll
     for (int j = 0; j < 8; ++j) { pg[i][j] = 0.0f; pb[i][j] = 0.0f; }
+  pdl_wait();
   int parity = 0;
   for (long long base = static_cast<long long>(blockIdx.x) * G::kRowsPerCta; base < rows;
        base += static_cast<long long>(gridDim.x) * G::kRowsPerCta, parity ^= 1) {
@@ -458,10 +460,10 @@ static int layernorm_fwd_launch(int dtype, const void* x, const void* gamma, con
   int nv, wpr;
   if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
 #define LN_FWD(T, NV, WPR)                                                                       \
-  layernorm_fwd_kernel<T, NV, WPR>                                                               \
-      <<<(rows + LnGeom<WPR>::kRowsPerCta - 1) / LnGeom<WPR>::kRowsPerCta, LnGeom<WPR>::kThreads, \
-         0, s>>>(static_cast<const T*>(x), static_cast<const T*>(gamma),                         \
-                 static_cast<const T*>(beta), pd, mean, rstd, rows, H, eps)
+  launch_pdl(layernorm_fwd_kernel<T, NV, WPR>,                                                   \
+             dim3((rows + LnGeom<WPR>::kRowsPerCta - 1) / LnGeom<WPR>::kRowsPerCta),             \
+             dim3(LnGeom<WPR>::kThreads), 0, s, 1, static_cast<const T*>(x),                     \
+             static_cast<const T*>(gamma), static_cast<const T*>(beta), pd, mean, rstd, rows, H, eps)
   if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_FWD) }
   else { TP_LN_DISPATCH(__half, LN_FWD) }
 #undef LN_FWD
@@ -525,10 +527,10 @@ static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const 
   {                                                                                             \
     auto kern = layernorm_bwd_kernel<T, NV, WPR>;                                               \
     if (smem > 48 * 1024) ln_allow_smem(kern);                                                  \
-    kern<<<parts, LnGeom<WPR>::kThreads, smem, s>>>(                                            \
-        static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                        \
-        static_cast<const T*>(gamma), static_cast<const T*>(dres), pd, scratch,                  \
-        rows, H, mode);                                                                         \
+    launch_pdl(kern, dim3(parts), dim3(LnGeom<WPR>::kThreads), smem, s, 1,                      \
+               static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                 \
+               static_cast<const T*>(gamma), static_cast<const T*>(dres), pd, scratch,           \
+               rows, H, mode);                                                                  \
   }
   if (dtype == 1) { TP_LN_DISPATCH(__nv_bfloat16, LN_BWD) }
   else { TP_LN_DISPATCH(__half, LN_BWD) }
@@ -679,4 +681,11 @@ extern "C" int tp_layernorm_bwd_noalloc(int dtype, const void* dy, const void* x
   // mode 0 writes every slot it later reads, so stale contents of the shared array are harmless
   return layernorm_bwd_launch(dtype, dy, x, mean, rstd, gamma, dres, single_dst(dx), dgamma, dbeta,
                               scratch_of_device[dev], rows, H, 0, static_cast<cudaStream_t>(stream));
+}
+
+// Programmatic dependent launch of the GEMM, attention and LayerNorm kernels (on by default;
+// TERAPIPE_PDL=0 in the environment or tp_set_pdl(0) turns it off, e.g. to compare timings).
+extern "C" int tp_set_pdl(int enabled) {
+  tp::pdl_enabled() = enabled ? 1 : 0;
+  return kOk;
 }

@@ -503,6 +503,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_wait();  // set-up done; from here on the predecessor's results are read
 
   const int num_kb = (p.K + kBK - 1) / kBK;
   const int ar_epoch = AR ? (ar.epoch + (ar.epoch_base ? *ar.epoch_base : 0)) : 0;
@@ -753,8 +754,10 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB, const CUt
     configured = true;
   }
   int grid = p.num_tiles < num_sms() ? p.num_tiles : num_sms();
-  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, tmO, p, ar);
-  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
+  return launch_pdl(kern, dim3(grid), dim3(kGemmThreads), Cfg::kSmemBytes, stream, 1, tmA, tmB, tmO, p, ar) ==
+                 cudaSuccess
+             ? kOk
+             : kErrLaunch;
 }
 
 template <typename T, int BN, int MT = 1>
@@ -979,6 +982,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
   __syncthreads();
   cluster_sync_all();  // both CTAs' barriers are initialised before any remote arrival
+  pdl_wait();          // set-up done; from here on the predecessor's results are read
   // The producer warp starts loading at once; the other five warps meet again after the TMEM
   // allocation (named barrier 1, 288 threads).
   uint32_t tmem_base = 0;
@@ -1477,19 +1481,10 @@ static int launch_gemm_pair(const CUtensorMap& tmA, const CUtensorMap& tmB, cons
   if (arp) ar = *arp;
   else { ar.tp = 0; ar.exchange = 0; ar.rows_per_rank = 0; }
   const int pairs = p.num_tiles < max_pairs() ? p.num_tiles : max_pairs();
-  cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(2 * pairs, 1, 1);
-  cfg.blockDim = dim3(kPairThreads + (RS ? 32 : 0), 1, 1);  // RS: one more warp publishes blocks
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
-  cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return cudaLaunchKernelEx(&cfg, kern, tmA, tmB, tmO, p, ar) == cudaSuccess ? kOk : kErrLaunch;
+  return launch_pdl(kern, dim3(2 * pairs), dim3(kPairThreads + (RS ? 32 : 0)), Cfg::kSmemBytes, stream, 2,
+                    tmA, tmB, tmO, p, ar) == cudaSuccess
+             ? kOk
+             : kErrLaunch;
 }
 
 template <typename T, int BN>

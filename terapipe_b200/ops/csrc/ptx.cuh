@@ -31,6 +31,18 @@ __device__ __forceinline__ unsigned long long globaltimer_ns() {
   return t;
 }
 
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization
+// attribute (see launch_pdl in common.cuh) may begin while its predecessor in the stream still
+// runs: its CTAs are placed as SMs free up and execute their set-up (barrier initialisation,
+// TMEM allocation, tensor-map prefetch).  pdl_wait() blocks until the predecessor has completed
+// and its memory operations are visible; every thread calls it before it touches global data.
+// The trigger directly after it lets the successor do the same with this kernel, and no
+// earlier, so at most two kernels overlap.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ bool elect_one() {
   uint32_t pred = 0;
   asm volatile(

@@ -79,6 +79,7 @@ SIGNATURES = {
     "tp_gemm_trace": [I, P, L, P, L, P, L, I, I, I, P, P, P],
     "tp_dp_reduce_adam": [I, I, I, I, P, P, P, P, P, P, P, L, L, P, F, F, F, F, F, F, P, P],
     "tp_set_wait_limit_ns": [L],
+    "tp_set_pdl": [I],
     "tp_gemm_ag": [I, I, P, L, P, L, P, L, I, I, I, P, I, P, I, P, L, P, P, I, I, I, P, P],
     "tp_gemm_rs": [I, I, P, L, P, L, P, L, I, I, I, P, P, L, I, I, I, I, P, I, P, P, P, P],
     "tp_layernorm_fwd_push": [I, P, P, P, P, P, P, I, I, F, I, I, P, I, P, P, P],

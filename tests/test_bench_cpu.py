@@ -1,0 +1,55 @@
+"""bench.py without a GPU: the block table, the slice schedules and the shared config keys."""
+import importlib.util
+import inspect
+import os
+import sys
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(ROOT, "bench.py"))
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules["bench_module"] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def test_blocks_name_valid_models_layouts_and_slices():
+    from terapipe_b200.models import MODEL_CONFIGS
+    bench = _bench()
+    blocks = dict(bench.HEADLINE_BLOCKS, tp_block=dict(bench.TP_BLOCK, tp=2))
+    assert {"headline", "headline_44b", "headline_tp8"} <= set(bench.HEADLINE_BLOCKS)
+    for name, spec in blocks.items():
+        n_layers, hidden, seq_len, heads = MODEL_CONFIGS[spec["model"]]
+        n_layers = spec.get("n_layers") or n_layers
+        assert heads % spec["tp"] == 0 and n_layers % spec["pp"] == 0, name
+        if name != "tp_block":
+            assert spec["tp"] * spec["pp"] == 8, name
+        bs, ss = bench.slices_for(spec, seq_len)
+        assert sum(bs) == spec["batch"] and sum(ss) == seq_len, name
+        # the sequence-parallel mode shards every slice in blocks of 32 rows per rank
+        assert all((b * t) % (32 * spec["tp"]) == 0 for b in bs for t in ss), name
+
+
+def test_headline_matches_the_named_configs():
+    bench = _bench()
+    h = bench.HEADLINE_BLOCKS
+    assert (h["headline"]["model"], h["headline"]["tp"], h["headline"]["pp"], h["headline"]["batch"]) == \
+        ("gpt3-13b", 2, 4, 8)
+    assert (h["headline_44b"]["model"], h["headline_44b"]["tp"], h["headline_44b"]["pp"],
+            h["headline_44b"]["batch"]) == ("gpt3-44b", 4, 2, 4)
+    assert (h["headline_tp8"]["model"], h["headline_tp8"]["n_layers"], h["headline_tp8"]["tp"],
+            h["headline_tp8"]["batch"], h["headline_tp8"]["seq_slices"]) == ("gpt3-175b", 8, 8, 2, 8)
+
+
+def test_both_arms_fill_the_same_config_keys():
+    bench = _bench()
+    keys = set(bench.config_dict())
+    sys.path.insert(0, ROOT)
+    from baseline import reference_arm
+    src_ref = inspect.getsource(reference_arm.ReferenceArm.measure)
+    src_ours = inspect.getsource(bench.OursArm.measure)
+    for k in keys:
+        assert f"{k}=" in src_ref, f"reference arm does not fill config key {k}"
+        assert f"{k}=" in src_ours, f"our arm does not fill config key {k}"

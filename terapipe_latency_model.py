@@ -106,11 +106,12 @@ class TerapipeLatencyModel:
         return out
 
 
-def scan_points(model, batch_size, step_gap, scan_grid):
+def scan_points(model, batch_size, step_gap, scan_grid, batches=None):
     _, _, L, _ = MODEL_CONFIGS[model]
     nb, ns, nc = scan_grid
-    batches = sorted({max(1, round(batch_size * (i + 1) / nb)) for i in range(nb)}) \
-        if batch_size > 8 else list(range(1, batch_size + 1))
+    if batches is None:
+        batches = sorted({max(1, round(batch_size * (i + 1) / nb)) for i in range(nb)}) \
+            if batch_size > 8 else list(range(1, batch_size + 1))
     seqs = sorted({max(step_gap, (L * (i + 1) // ns) // step_gap * step_gap) for i in range(ns)})
     ctxs = sorted({(L * (i + 1) // nc) // step_gap * step_gap for i in range(nc)})
     pts = {(b, s, c) for b in batches for s in seqs for c in ctxs if s + c <= L}
@@ -135,6 +136,8 @@ def main():
     parser.add_argument("--scan-grid", type=str, default="4,8,4")
     parser.add_argument("--flush-every", type=int, default=100)
     parser.add_argument("--max-points", type=int, default=None)
+    parser.add_argument("--batches", type=str, default=None,
+                        help="comma list of batch sizes to scan instead of the default set")
     parser.add_argument("--out-dir", type=str, default="performance_model_data")
     parser.add_argument("--tp-comm", default="fused", choices=["nccl", "fused", "sp"])
     args = parser.parse_args()
@@ -149,7 +152,8 @@ def main():
     path = os.path.join(args.out_dir, f"latency_model.{args.model}.mp_{args.model_parallel_size}.json")
     table = json.load(open(path)) if os.path.exists(path) else {}
     grid = tuple(int(v) for v in args.scan_grid.split(","))
-    todo = [p for p in scan_points(args.model, batch, args.step_gap, grid)
+    only = [int(v) for v in args.batches.split(",")] if args.batches else None
+    todo = [p for p in scan_points(args.model, batch, args.step_gap, grid, only)
             if "_".join(map(str, p)) not in table]
     # cheapest first, so that an out-of-memory point comes last (three alternative cost orders)
     keyfn = [lambda p: p[0] * p[1] * (p[1] + p[2]), lambda p: p[0] * (p[1] + p[2]),

@@ -282,3 +282,70 @@ def test_checkpoint_roundtrip_with_fused_data_parallel_update():
         res = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
     for r in res:
         assert r["same_model"] and r["same_next"] and r["moved"] > 0
+
+
+def _jitter_worker(rank, world, port, out_dir):
+    import random
+    import time
+    import torch.distributed as dist
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    from terapipe_b200 import parallel as mpu
+    from terapipe_b200.models import TransformerConfig
+    from terapipe_b200.runtime.engine import StageEngine
+    mpu.initialize_model_parallel(world, 1, verbose=False)
+    cfg = TransformerConfig(batch_size=4, seq_len=256, n_layers=2, embedding_dim=512,
+                            num_attention_heads=8, n_devices=world)
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn(cfg.seq_len, cfg.batch_size, cfg.embedding_dim, generator=g)
+    out = {}
+    for mode in ("fused", "sp"):
+        grads = []
+        for jitter in (False, True):
+            eng = StageEngine(cfg, [4], [64, 64, 128], init="device", use_graph=False, tp_comm=mode,
+                              segment_graphs=False)
+            if jitter:
+                # every rank delays its launches by its own random amounts: flags and epochs of
+                # the fused kernels must not depend on the ranks arriving together
+                rnd = random.Random(1000 + rank)
+                fwd, bwd = eng._forward_slice, eng._backward_slice
+
+                def slow_fwd(sl, fwd=fwd):
+                    time.sleep(rnd.random() * 0.004)
+                    fwd(sl)
+
+                def slow_bwd(sl, bwd=bwd):
+                    time.sleep(rnd.random() * 0.004)
+                    bwd(sl)
+
+                eng._forward_slice, eng._backward_slice = slow_fwd, slow_bwd
+            eng.set_input(x)
+            for _ in range(2):
+                eng.compute_grads()
+            torch.cuda.synchronize()
+            eng.check_status()
+            grads.append(eng.grad.clone())
+            dist.barrier()
+            eng._forward_slice = eng._backward_slice = None
+            eng.close()
+        out[mode] = bool(torch.equal(grads[0], grads[1]))
+    torch.save(out, os.path.join(out_dir, f"rank{rank}.pt"))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_fused_kernels_are_insensitive_to_launch_jitter():
+    """Random per-rank host delays before every slice (up to 4 ms, far more than a kernel) leave
+    the gradients of the fused tensor-parallel modes bit-identical."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    import torch.multiprocessing as mp
+    from dist_utils import free_port
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_jitter_worker, args=(2, free_port(), d), nprocs=2, join=True)
+        res = [torch.load(os.path.join(d, f"rank{r}.pt")) for r in range(2)]
+    for r in res:
+        assert r["fused"] and r["sp"], r

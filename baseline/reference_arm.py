@@ -42,16 +42,27 @@ class _NumpyCompat:
         return self._np.array(obj, *args, **kwargs)
 
 
+class _Grads(list):
+    """What ``torch.autograd.grad`` returns to the reference in this process: a list, because the
+    driver concatenates ``[dy] + all_grads[n:]`` (test_transformer_terapipe.py:156-166), which
+    also adds to a tuple from the left, because the reference's recompute function returns
+    ``(None, None) + grads`` (checkpoint.py:43).  Torch of the reference's era returned a tuple
+    and its driver code predates the list concatenation failing; both call shapes must work."""
+
+    def __radd__(self, other):
+        if isinstance(other, tuple):
+            return other + tuple(self)
+        return list(other) + list(self)
+
+
 def _autograd_grad_returns_list(torch) -> None:
-    """The reference's backward loop concatenates ``[dy] + all_grads[n:]``
-    (test_transformer_terapipe.py:156-166), which needs ``torch.autograd.grad`` to hand back a
-    list; current torch returns a tuple.  In this process only, wrap it to return a list."""
+    """See :class:`_Grads`.  In this process only, wrap ``torch.autograd.grad``."""
     original = torch.autograd.grad
     if getattr(original, "_returns_list", False):
         return
 
     def grad(*args, **kwargs):
-        return list(original(*args, **kwargs))
+        return _Grads(original(*args, **kwargs))
 
     grad._returns_list = True
     torch.autograd.grad = grad

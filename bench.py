@@ -497,7 +497,10 @@ def main():
         if name != "tp_block" and HEADLINE_BLOCKS[name]["tp"] * HEADLINE_BLOCKS[name]["pp"] != world:
             out[name] = {"skipped": "needs %d GPUs" % (HEADLINE_BLOCKS[name]["tp"] * HEADLINE_BLOCKS[name]["pp"])}
             continue
-        env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(base_port + 101 + 7 * i),
+        # torchrun's agent variables must not reach the children: with TORCHELASTIC_USE_AGENT_STORE
+        # set, rank 0 would look for the agent's store on the new port instead of opening one
+        env = {k: v for k, v in os.environ.items() if not k.startswith(("TORCHELASTIC_", "TORCH_NCCL_ASYNC"))}
+        env.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(base_port + 101 + 7 * i),
                    RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local))
         cmd = [sys.executable, os.path.abspath(__file__), "--child-block", name] + sys.argv[1:]
         try:

@@ -98,6 +98,8 @@ def parse_args():
     ap.add_argument("--blocks", default="auto",
                     help="'auto' (the blocks of this GPU count), 'none', or a comma list of block names")
     ap.add_argument("--child-block", default=None, help=argparse.SUPPRESS)
+    ap.add_argument("--total-budget", type=float, default=1500.0,
+                    help="seconds after which no further block is started")
     ap.add_argument("--block-timeout", type=float, default=None,
                     help="seconds a single block may take (default 420 ours, 900 reference)")
     return ap.parse_args()
@@ -425,6 +427,7 @@ def make_arm(args):
 
 def main():
     args = parse_args()
+    t_start = time.time()
     if args.child_block:
         return child_main(args)
     rank, world, local = dist_env()
@@ -494,6 +497,10 @@ def main():
         pass
     base_port = int(os.environ.get("MASTER_PORT", "29500"))
     for i, name in enumerate(names):
+        remaining = args.total_budget - (time.time() - t_start)
+        if remaining < 60:
+            out[name] = {"skipped": f"time budget of {args.total_budget:.0f} s for the whole run is used up"}
+            continue
         if name != "tp_block" and HEADLINE_BLOCKS[name]["tp"] * HEADLINE_BLOCKS[name]["pp"] != world:
             out[name] = {"skipped": "needs %d GPUs" % (HEADLINE_BLOCKS[name]["tp"] * HEADLINE_BLOCKS[name]["pp"])}
             continue
@@ -505,7 +512,7 @@ def main():
         cmd = [sys.executable, os.path.abspath(__file__), "--child-block", name] + sys.argv[1:]
         try:
             res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
-                                 timeout=limit)
+                                 timeout=min(limit, remaining + 120))
             entry = None
             for line in res.stdout.splitlines():
                 if line.startswith("{"):

@@ -520,8 +520,10 @@ def main():
             if entry is None:
                 tail = (res.stderr or "").strip().splitlines()[-3:]
                 entry = {"error": f"child exited with status {res.returncode}", "stderr_tail": tail}
-        except subprocess.TimeoutExpired:
-            entry = {"timed_out": True, "limit_s": limit}
+        except subprocess.TimeoutExpired as e:
+            err = e.stderr.decode(errors="replace") if isinstance(e.stderr, bytes) else (e.stderr or "")
+            entry = {"timed_out": True, "limit_s": limit,
+                     "stderr_tail": [ln[:200] for ln in err.strip().splitlines()[-12:]]}
         if rank == 0:
             out[name] = entry
     emit()
@@ -529,6 +531,10 @@ def main():
 
 def child_main(args):
     """One further block in a process group of its own (see main); rank 0 prints the block."""
+    import faulthandler
+    limit = args.block_timeout or (420.0 if args.impl == "ours" else 900.0)
+    # a block that hangs leaves the Python stack of every thread in its stderr before it is ended
+    faulthandler.dump_traceback_later(max(30.0, 0.85 * limit), exit=False)
     rank, world, local = dist_env()
     warmup = max(args.warmup, 3)
     arm = make_arm(args)

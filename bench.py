@@ -388,6 +388,7 @@ class OursArm:
         if "sp" in getattr(StageEngine, "TP_COMM_MODES", ()):
             modes.append("sp")
         for mode in modes:
+            print(f"[tp_block] rank {self.rank}: mode {mode}", file=sys.stderr, flush=True)
             block, grads = self.measure(spec, steps, warmup, tp_comm=mode, keep_grads=True)
             entry = {"ms_per_step": block["ms_per_step"], "tokens_per_s": block["value"],
                      "e2e_ms_per_step": block["e2e"]["ms_per_step"] if block["e2e"] else None,

@@ -410,7 +410,7 @@ extern "C" int tp_peer_sum(float* out, int n, void* const* src_ptrs, int n_ranks
 }
 
 // Limit of every bounded device-side wait of this library (mbarrier, peer flags), on the current
-// device; the default is 2 s.  Call it with no kernel of the library in flight.
+// device; the default is 5 s.  Call it with no kernel of the library in flight.
 TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_comm)
 extern "C" int tp_set_wait_limit_ns_gemm(unsigned long long ns);
 extern "C" int tp_set_wait_limit_ns_attn(unsigned long long ns);

@@ -683,8 +683,8 @@ extern "C" int tp_layernorm_bwd_noalloc(int dtype, const void* dy, const void* x
                               scratch_of_device[dev], rows, H, 0, static_cast<cudaStream_t>(stream));
 }
 
-// Programmatic dependent launch of the GEMM, attention and LayerNorm kernels (on by default;
-// TERAPIPE_PDL=0 in the environment or tp_set_pdl(0) turns it off, e.g. to compare timings).
+// Programmatic dependent launch of the GEMM, attention and LayerNorm kernels (off by default;
+// TERAPIPE_PDL=1 in the environment or tp_set_pdl(1) turns it on).
 extern "C" int tp_set_pdl(int enabled) {
   tp::pdl_enabled() = enabled ? 1 : 0;
   return kOk;

@@ -110,7 +110,10 @@ __device__ __forceinline__ bool wait_flag(const int* p, int target, const WaitCt
       if (*w.abort_smem) return false;
       // an earlier wait of this step already ran out (here or in an earlier kernel): the peers
       // are out of step for good, so do not spend another wait limit on every later flag
-      if (w.err_global && *reinterpret_cast<volatile int*>(w.err_global) != 0) return false;
+      if (w.err_global && *reinterpret_cast<volatile int*>(w.err_global) != 0) {
+        *w.abort_smem = code;  // the CTA's own barrier waits end at once as well
+        return false;
+      }
       const unsigned long long now = globaltimer_ns();
       if (t0 == 0) t0 = now;
       else if (now - t0 > g_wait_limit_ns) {

@@ -12,10 +12,10 @@
 
 namespace tp {
 
-// Limit of every device-side wait, in nanoseconds (default 2 s).  The variable exists once per
+// Limit of every device-side wait, in nanoseconds (default 5 s).  The variable exists once per
 // translation unit; tp_set_wait_limit_ns() (comm_sm100.cu) sets all of them on the current
 // device, which lets a test make a wait run out within milliseconds.
-static __device__ unsigned long long g_wait_limit_ns = 2000000000ull;
+static __device__ unsigned long long g_wait_limit_ns = 5000000000ull;
 #define TP_DEFINE_WAIT_LIMIT_SETTER(fn_name)                                               \
   extern "C" int fn_name(unsigned long long ns) {                                           \
     return cudaMemcpyToSymbol(tp::g_wait_limit_ns, &ns, sizeof(ns)) == cudaSuccess ? 0 : -2; \

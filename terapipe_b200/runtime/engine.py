@@ -220,6 +220,7 @@ class StageEngine:
                                               + (0 if self.is_last else 1)) + 1
         self._ag_calls = 0
         self._ag_stream, self._ag_pending = None, False
+        self._first_step_synced = False
         self._ag_in_kernel = os.environ.get("TERAPIPE_AG_PUSH", "0") == "1"
 
     # ------------------------------------------------------------------ parameters
@@ -986,6 +987,16 @@ class StageEngine:
                      self.adam_state, lr=self.lr, grad_scale=1.0 / (self.loss_scale * self.dp))
 
     def _iteration(self, update=True):
+        if not self._first_step_synced:
+            # Kernels that wait for a peer on the device are bounded by the wait limit; the first
+            # step follows minutes of set-up whose length differs between ranks (weight
+            # initialisation, module loading), so the ranks of the groups meet on the host first.
+            self._first_step_synced = True
+            if (self.ar is not None or self.dp_sym is not None) and dist.is_initialized():
+                torch.cuda.synchronize()
+                for group in (mpu.get_model_parallel_group(), mpu.get_data_parallel_group()):
+                    if group is not None and dist.get_world_size(group) > 1:
+                        dist.barrier(group=group)
         self._refresh_handles()
         if self.ar is not None:
             # call indices restart at 1 every iteration; the device counter supplies the rest, so

@@ -74,6 +74,16 @@ def _fit_context_model(rows, targets, holdout=0.25, seed=42):
     n_test = int(len(y) * holdout) if len(y) >= 8 else 0
     test, train = idx[:n_test], idx[n_test:]
     coef, *_ = np.linalg.lstsq(A[train], y[train], rcond=None)
+    if (coef[1:] < 0).any():
+        # More context can only cost time (the attention core reads more keys).  On a B200 the
+        # context term of a slice is small against run-to-run noise, and an unconstrained fit
+        # then returns negative slopes that make long contexts look cheap: fit with
+        # non-negative coefficients instead.
+        try:
+            from scipy.optimize import nnls
+            coef, _ = nnls(A[train], np.maximum(y[train], 0.0))
+        except Exception:  # noqa: BLE001 - no scipy: clip
+            coef = np.maximum(coef, 0.0)
     if n_test:
         resid = y[test] - A[test] @ coef
         denom = ((y[test] - y[test].mean()) ** 2).sum()
@@ -116,6 +126,11 @@ def fit_latency_tables(latency_table: Dict[Tuple[int, int, int], dict],
             hole = ~np.isfinite(t0)
             hole[0, :] = False
             hole[:, 0] = False
+            # batch sizes without any measurement stay infeasible: the surface is not trusted
+            # outside the measured range (it made unmeasured small batches look free)
+            for b in range(t0.shape[0]):
+                if np.isfinite(t0[b]).sum() < 2:
+                    hole[b, :] = False
             t0[hole] = surf[hole]
     rows, targets = [], []
     for (b, s, c), t in latency_table.items():

@@ -163,3 +163,24 @@ def test_auto_schedule_for_a_layout():
     bs, ss, latency = auto_schedule("gpt3-1b", 8, 1, 8)
     assert sum(bs) == 8 and sum(ss) == 2048 and 0.02 < latency < 0.06
     assert len(set(bs)) == 1                      # equal batch slices (the engine's requirement)
+
+
+def test_fit_keeps_unmeasured_batches_infeasible_and_context_terms_non_negative():
+    """A coarse, noisy table (batches 2 and 4 only; the context term drowned in noise) must not
+    make an unmeasured batch size look free, nor long contexts cheaper than short ones."""
+    import numpy as np
+    from terapipe_b200.planner.latency_model import fit_latency_tables
+    rng = np.random.RandomState(0)
+    table = {}
+    for b in (2, 4):
+        for s in range(64, 513, 64):
+            base = 1e-4 + 2e-7 * b * s
+            table[(b, s, 0)] = {"forward_mean": base, "backward_mean": 2 * base, "update_mean": 1e-3}
+            for c in (128, 256):
+                if s + c <= 512:
+                    noisy = base * (1 + 0.05 * rng.randn())       # noise larger than the context effect
+                    table[(b, s, c)] = {"forward_mean": noisy, "backward_mean": 2 * noisy, "update_mean": 1e-3}
+    model = fit_latency_tables(table, None, batch_size=4, seqlen=512, layers_per_stage=2, step_gap=64)
+    assert np.isinf(model.no_content_performance[1]).all() and np.isinf(model.no_content_performance[3]).all()
+    assert np.isfinite(model.no_content_performance[2, 1:]).all() and np.isfinite(model.no_content_performance[4, 1:]).all()
+    assert (np.asarray(model.context_coef)[1:] >= 0).all()

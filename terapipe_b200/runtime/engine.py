@@ -42,7 +42,7 @@ import torch.distributed as dist
 from .. import parallel as mpu
 from ..models import TransformerConfig
 from ..ops import functional as F
-from ..ops.lib import cuda_lib
+from ..ops.lib import KernelError, cuda_lib
 
 LOSS_SCALE_FACTOR = 128.0
 _ACT = {"none": 0, "relu": 1, "gelu": 2}
@@ -1082,8 +1082,23 @@ class StageEngine:
     def _capture(self):
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            self._iteration()
+        try:
+            with torch.cuda.graph(graph):
+                self._iteration()
+        except (RuntimeError, KernelError) as e:
+            # The whole step could not be captured (seen with a 48-layer stage of GPT3-44B width:
+            # a launch inside the capture failed although the same step had just run eagerly).
+            # Fall back to one graph per launch-only segment, which captures far smaller pieces.
+            import warnings
+            warnings.warn(f"whole-step CUDA graph capture failed ({type(e).__name__}: {str(e)[:120]}); "
+                          "using per-segment graphs instead")
+            torch.cuda.synchronize()
+            self.use_graph = False
+            self._graph = None
+            self._ag_pending = False
+            if self._plan is None and self._seg_graphs is None:
+                self._seg_graphs = {}
+            return
         self._graph = graph
 
     def check_status(self):

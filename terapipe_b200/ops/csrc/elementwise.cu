@@ -500,8 +500,13 @@ extern "C" int tp_layernorm_bwd_parts(int rows) {
 }
 
 namespace tp {
+// Opt the kernel in to more than 48 KB of shared memory, once per instantiation (the first,
+// eager launch; never inside a stream capture).
 template <typename K> static void ln_allow_smem(K kern) {
+  static bool done = false;
+  if (done) return;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
+  done = true;
 }
 
 static int ln_parts(int rows, int wpr) {
@@ -526,7 +531,7 @@ static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const 
 #define LN_BWD(T, NV, WPR)                                                                      \
   {                                                                                             \
     auto kern = layernorm_bwd_kernel<T, NV, WPR>;                                               \
-    if (smem > 48 * 1024) ln_allow_smem(kern);                                                  \
+    if (smem > 40 * 1024) ln_allow_smem(kern); /* dynamic + static must stay under 48 KB */    \
     launch_pdl(kern, dim3(parts), dim3(LnGeom<WPR>::kThreads), smem, s, 1,                      \
                static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                 \
                static_cast<const T*>(gamma), static_cast<const T*>(dres), pd, scratch,           \

@@ -395,6 +395,13 @@ class StageEngine:
         if st:
             F.check(st, "tp_gemm")
 
+    def _ln(self, fn_name, *args):
+        """An entry point of the library whose status must be zero (LayerNorm, column sums, ...);
+        a rejected or failed launch raises."""
+        st = getattr(self.lib, fn_name)(*args)
+        if st:
+            F.check(st, fn_name)
+
     def _p(self, layer, name, buf=None):
         base = (self.model if buf is None else buf)
         return base.data_ptr() + self.layout.offsets[layer][name] * base.element_size()
@@ -475,7 +482,7 @@ class StageEngine:
     def _ln_fwd_push(self, x, gamma, beta, dst_name, row, mean, rstd, rows):
         if not self._ag_in_kernel:
             dst = self.ar.buf.local_ptr + self._pool_off[dst_name] + row * self.H * self.es
-            self.lib.tp_layernorm_fwd(self.dt, x, gamma, beta, dst, mean, rstd, rows, self.H, 1e-5,
+            self._ln("tp_layernorm_fwd", self.dt, x, gamma, beta, dst, mean, rstd, rows, self.H, 1e-5,
                                       self._stream)
             return self._ag_async(dst_name, row, rows)
         self._ag_calls += 1
@@ -490,7 +497,7 @@ class StageEngine:
     def _ln_bwd_push(self, dy, x, mean, rstd, gamma, dres, dst_name, row, slots, rows):
         if not self._ag_in_kernel:
             dst = self.ar.buf.local_ptr + self._pool_off[dst_name] + row * self.H * self.es
-            self.lib.tp_layernorm_bwd_accum(self.dt, dy, x, mean, rstd, gamma, dres, dst, slots, rows,
+            self._ln("tp_layernorm_bwd_accum", self.dt, dy, x, mean, rstd, gamma, dres, dst, slots, rows,
                                             self.H, self._stream)
             return self._ag_async(dst_name, row, rows)
         self._ag_calls += 1
@@ -556,7 +563,7 @@ class StageEngine:
             x = self.X[l].data_ptr() + r0 * H * es
             ln1 = self.ln1[l].data_ptr() + r0 * H * es
             st = self.stats[l].data_ptr()
-            lib.tp_layernorm_fwd(dt, x, self._p(l, "attn_ln.weight"), self._p(l, "attn_ln.bias"), ln1,
+            self._ln("tp_layernorm_fwd", dt, x, self._p(l, "attn_ln.weight"), self._p(l, "attn_ln.bias"), ln1,
                                  st + r0 * 4, st + (self.rows + r0) * 4, T, H, 1e-5, s)
             qkv_base = self.qkv[l].data_ptr() + self.L * boff * 3 * Hl * es
             qkv = self.qkv[l].data_ptr() + r0 * 3 * Hl * es
@@ -579,7 +586,7 @@ class StageEngine:
                 if self.tp > 1:
                     self._all_reduce_rows(self.xmid[l], r0, T)
             ln2 = self.ln2[l].data_ptr() + r0 * H * es
-            lib.tp_layernorm_fwd(dt, xmid, self._p(l, "fc_ln.weight"), self._p(l, "fc_ln.bias"), ln2,
+            self._ln("tp_layernorm_fwd", dt, xmid, self._p(l, "fc_ln.weight"), self._p(l, "fc_ln.bias"), ln2,
                                  st + (2 * self.rows + r0) * 4, st + (3 * self.rows + r0) * 4, T, H,
                                  1e-5, s)
             fa = self.fa[l].data_ptr() + r0 * Fl * es
@@ -630,7 +637,7 @@ class StageEngine:
                 if self.tp > 1:
                     self._all_reduce_rows(self.dln, 0, T)
             slots = self.ln_slots[l].data_ptr()
-            lib.tp_layernorm_bwd_accum(dt, dln, xmid, st + (2 * self.rows + r0) * 4,
+            self._ln("tp_layernorm_bwd_accum", dt, dln, xmid, st + (2 * self.rows + r0) * 4,
                                        st + (3 * self.rows + r0) * 4, self._p(l, "fc_ln.weight"), dcur,
                                        dmid, slots + self.ln_parts * 2 * H * 4, T, H, s)
             # ---- attention
@@ -656,7 +663,7 @@ class StageEngine:
                 dnext = self.dA.data_ptr()
             else:
                 dnext = self.dX0.data_ptr() + r0 * H * es
-            lib.tp_layernorm_bwd_accum(dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
+            self._ln("tp_layernorm_bwd_accum", dt, dln, x, st + r0 * 4, st + (self.rows + r0) * 4,
                                        self._p(l, "attn_ln.weight"), dmid, dnext, slots, T, H, s)
 
     def _backward_slice_sp(self, sl) -> None:
@@ -719,7 +726,7 @@ class StageEngine:
                 # tensor-parallel rank of the previous stage, or nowhere on the first stage)
                 dnext = (self.dA.data_ptr() + self.tp_idx * rpr * H * es) if self.is_first \
                     else self.dX0.data_ptr() + m0 * H * es
-                lib.tp_layernorm_bwd_accum(dt, dln_mine, x_mine, st + m0 * 4, st + (self.rows + m0) * 4,
+                self._ln("tp_layernorm_bwd_accum", dt, dln_mine, x_mine, st + m0 * 4, st + (self.rows + m0) * 4,
                                            self._p(l, "attn_ln.weight"), dmid_mine, dnext, slots, rpr,
                                            H, s)
         self._ag_join()
@@ -744,28 +751,28 @@ class StageEngine:
             dfc, dqkv = self.dFc[l].data_ptr(), self.dQKV[l].data_ptr()
             self._gemm(dxo, H, self.fa[l].data_ptr(), Fl, self._p(l, "fc2.weight", g), Fl, H, Fl, R,
                        a_mn=1, b_mn=1, out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dxo, H, R, H, self._p(l, "fc2.bias", g), s)
+            self._ln("tp_colsum", dt, dxo, H, R, H, self._p(l, "fc2.bias", g), s)
             self._gemm(dfc, Fl, self.ln2[l].data_ptr(), H, self._p(l, "fc1.weight", g), H, Fl, H, R,
                        a_mn=1, b_mn=1, out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dfc, Fl, R, Fl, self._p(l, "fc1.bias", g), s)
+            self._ln("tp_colsum", dt, dfc, Fl, R, Fl, self._p(l, "fc1.bias", g), s)
             self._gemm(dmid, H, self.ao[l].data_ptr(), Hl, self._p(l, "attn.out_proj.weight", g), Hl,
                        H, Hl, R, a_mn=1, b_mn=1, out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dmid, H, R, H, self._p(l, "attn.out_proj.bias", g), s)
+            self._ln("tp_colsum", dt, dmid, H, R, H, self._p(l, "attn.out_proj.bias", g), s)
             self._gemm(dqkv, 3 * Hl, self.ln1[l].data_ptr(), H, self._p(l, "attn.in_proj.weight", g),
                        H, 3 * Hl, H, R, a_mn=1, b_mn=1, out_f32=1, accumulate=1)
-            lib.tp_colsum(dt, dqkv, 3 * Hl, R, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
+            self._ln("tp_colsum", dt, dqkv, 3 * Hl, R, 3 * Hl, self._p(l, "attn.in_proj.bias", g), s)
             slots = self.ln_slots[l].data_ptr()
             if self.sp:
                 # this rank's slots hold the sums over its token shards only: fold them into a
                 # peer-visible pack; the sums of all ranks are added after the barrier below
                 pack = self._ln_pack.data_ptr() + l * 4 * H * 4
-                lib.tp_layernorm_bwd_finish_assign(slots, self.ln_parts, H, pack, pack + H * 4, s)
-                lib.tp_layernorm_bwd_finish_assign(slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
+                self._ln("tp_layernorm_bwd_finish_assign", slots, self.ln_parts, H, pack, pack + H * 4, s)
+                self._ln("tp_layernorm_bwd_finish_assign", slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
                                                    pack + 2 * H * 4, pack + 3 * H * 4, s)
                 continue
-            lib.tp_layernorm_bwd_finish(slots, self.ln_parts, H, self._p(l, "attn_ln.weight", g),
+            self._ln("tp_layernorm_bwd_finish", slots, self.ln_parts, H, self._p(l, "attn_ln.weight", g),
                                         self._p(l, "attn_ln.bias", g), s)
-            lib.tp_layernorm_bwd_finish(slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
+            self._ln("tp_layernorm_bwd_finish", slots + self.ln_parts * 2 * H * 4, self.ln_parts, H,
                                         self._p(l, "fc_ln.weight", g), self._p(l, "fc_ln.bias", g), s)
         if overlap and self.n_layers:
             self._dp_layer_done(0, works)
@@ -777,9 +784,9 @@ class StageEngine:
             self._group_barrier(2)
             for l in range(self.n_layers):
                 off = self._off_ln_pack + l * 4 * H * 4
-                lib.tp_peer_sum(self._p(l, "attn_ln.weight", g), 2 * H, self.ar.out_ptrs(off), self.tp,
+                self._ln("tp_peer_sum", self._p(l, "attn_ln.weight", g), 2 * H, self.ar.out_ptrs(off), self.tp,
                                 self.tp_idx, s)
-                lib.tp_peer_sum(self._p(l, "fc_ln.weight", g), 2 * H, self.ar.out_ptrs(off + 2 * H * 4),
+                self._ln("tp_peer_sum", self._p(l, "fc_ln.weight", g), 2 * H, self.ar.out_ptrs(off + 2 * H * 4),
                                 self.tp, self.tp_idx, s)
 
     def _group_barrier(self, index: int) -> None:

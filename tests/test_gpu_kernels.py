@@ -88,7 +88,7 @@ def test_gemm_activation_epilogues(act):
     F.check_device_status()
 
 
-@pytest.mark.parametrize("H", [256, 2048, 5120, 12288])
+@pytest.mark.parametrize("H", [256, 2048, 5120, 6144, 12288])  # 6144: 48 KB of dynamic shared memory + static
 def test_layernorm_fwd_bwd(H):
     from terapipe_b200.ops import functional as F
     torch.manual_seed(4)

@@ -503,10 +503,15 @@ namespace tp {
 // Opt the kernel in to more than 48 KB of shared memory, once per instantiation (the first,
 // eager launch; never inside a stream capture).
 template <typename K> static void ln_allow_smem(K kern) {
-  static bool done = false;
-  if (done) return;
+  // (instantiations of one element type share the function-pointer type K, so the kernels
+  // already handled are remembered by address)
+  static const void* seen[64];
+  static int n_seen = 0;
+  const void* key = reinterpret_cast<const void*>(kern);
+  for (int i = 0; i < n_seen; ++i)
+    if (seen[i] == key) return;
   cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
-  done = true;
+  if (n_seen < 64) seen[n_seen++] = key;
 }
 
 static int ln_parts(int rows, int wpr) {

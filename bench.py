@@ -57,7 +57,7 @@ HEADLINE_BLOCKS = {
     "headline": dict(model="gpt3-13b", batch=8, tp=2, pp=4, seq_slices=16, batch_slices=1, steps=5),
     # the same layout with the batch / token slices chosen by the dynamic program over the B200
     # latency tables (both arms read the same committed schedule)
-    "headline_planned": dict(model="gpt3-13b", batch=8, tp=2, pp=4, schedule="dp_results.kernel_model.json",
+    "headline_planned": dict(model="gpt3-13b", batch=8, tp=2, pp=4, schedule="dp_results.json",
                              seq_slices=16, batch_slices=1, steps=5),
     "headline_tp8": dict(model="gpt3-175b", n_layers=8, batch=2, tp=8, pp=1, seq_slices=8,
                          batch_slices=1, steps=5),

@@ -102,7 +102,8 @@ inline bool make_tmap_out(CUtensorMap* out, const void* base, uint64_t cols, uin
 // Launch with programmatic stream serialization (see pdl_wait in ptx.cuh).  The kernel must call
 // pdl_wait() in every thread before its first access to global data.  The attribute is off
 // unless tp_set_pdl(1) was called or the environment variable TERAPIPE_PDL=1 is set at first use
-// (it measured no gain on a power-capped step, see the design notes).
+// (it measured no gain on a step that runs at the power cap: time saved in gaps came back as a
+// lower clock).
 inline int& pdl_enabled() {
   static int enabled = -1;
   if (enabled < 0) {

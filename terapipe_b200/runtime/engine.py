@@ -219,6 +219,12 @@ class StageEngine:
         self._ag_calls_per_step = n_slices * (2 * self.n_layers + self.n_layers + max(self.n_layers - 1, 0)
                                               + (0 if self.is_last else 1)) + 1
         self._ag_calls = 0
+        if self.sp:
+            # one flag kernel per all-gather, two group barriers, the sums of the LayerNorm
+            # gradients over the group and the three counter updates of a step
+            self.launches_per_step += (self._ag_calls_per_step - 1) + 2 + 2 * self.n_layers + 3
+        elif self.tp_comm == "fused":
+            self.launches_per_step += 1      # the epoch counter update
         self._ag_stream, self._ag_pending = None, False
         self._first_step_synced = False
         self._ag_in_kernel = os.environ.get("TERAPIPE_AG_PUSH", "0") == "1"

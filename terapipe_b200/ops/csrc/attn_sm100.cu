@@ -723,23 +723,25 @@ static int attn_bwd_launch(const void* qkv, const void* o, const void* do_full, 
 
 using namespace tp;
 
-static AttnParams base_params(int D, int b, int h, int t, int c, int* err) {
+// `scale` multiplies q.k before the softmax; <= 0 selects D^-0.5.  A caller whose heads are narrower
+// than the kernel's D (zero-padded columns) passes the scale of the real width.
+static AttnParams base_params(int D, float scale, int b, int h, int t, int c, int* err) {
   AttnParams p;
   memset(&p, 0, sizeof(p));
   p.t = t; p.c = c; p.b = b; p.h = h;
-  p.scale = 1.0f / sqrtf(static_cast<float>(D));
+  p.scale = scale > 0.0f ? scale : 1.0f / sqrtf(static_cast<float>(D));
   p.scale2 = p.scale * 1.4426950408889634f;
   p.err = err;
   return p;
 }
 
 // qkv: base of the full-length [L][b][h][3][D] buffer; rows [0, c+t) must be valid.
-extern "C" int tp_attn_fwd(int dtype, int D, const void* qkv, int b, int h, int t, int c, void* o,
-                           long long ld_o, float* lse2, long long lse_stride, int* err,
-                           void* stream) {
+extern "C" int tp_attn_fwd_scaled(int dtype, int D, float scale, const void* qkv, int b, int h, int t,
+                                  int c, void* o, long long ld_o, float* lse2, long long lse_stride,
+                                  int* err, void* stream) {
   if ((D != 64 && D != 128) || t <= 0 || c < 0 || b <= 0 || h <= 0) return kErrBadArgument;
   if (ld_o % 8) return kErrBadArgument;
-  AttnParams p = base_params(D, b, h, t, c, err);
+  AttnParams p = base_params(D, scale, b, h, t, c, err);
   p.o = o; p.ld_o = ld_o; p.lse2 = lse2; p.lse_stride = lse_stride;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool bf16 = dtype == 1;
@@ -749,6 +751,12 @@ extern "C" int tp_attn_fwd(int dtype, int D, const void* qkv, int b, int h, int 
               : attn_fwd_launch<__half, 64>(qkv, p, false, s);
 }
 
+extern "C" int tp_attn_fwd(int dtype, int D, const void* qkv, int b, int h, int t, int c, void* o,
+                           long long ld_o, float* lse2, long long lse_stride, int* err,
+                           void* stream) {
+  return tp_attn_fwd_scaled(dtype, D, 0.0f, qkv, b, h, t, c, o, ld_o, lse2, lse_stride, err, stream);
+}
+
 // Backward of the slice [c, c+t).  The slices after it must already have been processed:
 //   o        this slice's attention output, [t*b][ld_o]
 //   do_full  full-length gradient of the attention output, [L*b][ld_do]; rows [c*b, q_end*b)
@@ -756,14 +764,15 @@ extern "C" int tp_attn_fwd(int dtype, int D, const void* qkv, int b, int h, int 
 //   lse2, delta   fp32 [b*h][lse_stride], indexed by absolute position; delta rows [c, c+t) are
 //            written here, rows [c+t, q_end) were written by the calls for the later slices
 //   dqkv     this slice's [t*b][ld_dqkv] output (same column order as qkv)
-extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int t, int c, int q_end,
-                           const void* o, long long ld_o, const void* do_full, long long ld_do,
-                           const float* lse2, long long lse_stride, float* delta, void* dqkv,
-                           long long ld_dqkv, int* err, void* stream) {
+extern "C" int tp_attn_bwd_scaled(int dtype, int D, float scale, const void* qkv, int b, int h, int t,
+                                  int c, int q_end, const void* o, long long ld_o, const void* do_full,
+                                  long long ld_do, const float* lse2, long long lse_stride,
+                                  float* delta, void* dqkv, long long ld_dqkv, int* err,
+                                  void* stream) {
   if ((D != 64 && D != 128) || t <= 0 || c < 0 || b <= 0 || h <= 0 || q_end < c + t)
     return kErrBadArgument;
   if (ld_o % 8 || ld_do % 8 || ld_dqkv % 8) return kErrBadArgument;
-  AttnParams p = base_params(D, b, h, t, c, err);
+  AttnParams p = base_params(D, scale, b, h, t, c, err);
   p.o = const_cast<void*>(o); p.ld_o = ld_o;
   p.lse2 = const_cast<float*>(lse2); p.lse_stride = lse_stride;
   p.delta = delta; p.q_end = q_end; p.dqkv = dqkv; p.ld_dqkv = ld_dqkv;
@@ -773,6 +782,14 @@ extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int 
                             : attn_bwd_launch<__half, 128>(qkv, o, do_full, ld_do, p, false, s);
   return bf16 ? attn_bwd_launch<__nv_bfloat16, 64>(qkv, o, do_full, ld_do, p, true, s)
               : attn_bwd_launch<__half, 64>(qkv, o, do_full, ld_do, p, false, s);
+}
+
+extern "C" int tp_attn_bwd(int dtype, int D, const void* qkv, int b, int h, int t, int c, int q_end,
+                           const void* o, long long ld_o, const void* do_full, long long ld_do,
+                           const float* lse2, long long lse_stride, float* delta, void* dqkv,
+                           long long ld_dqkv, int* err, void* stream) {
+  return tp_attn_bwd_scaled(dtype, D, 0.0f, qkv, b, h, t, c, q_end, o, ld_o, do_full, ld_do, lse2,
+                            lse_stride, delta, dqkv, ld_dqkv, err, stream);
 }
 
 TP_DEFINE_WAIT_LIMIT_SETTER(tp_set_wait_limit_ns_attn)

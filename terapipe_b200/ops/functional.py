@@ -157,22 +157,24 @@ def fill(t, value: float):
     return t
 
 
-def attn_fwd(qkv, b: int, h: int, D: int, t: int, c: int, o, lse2):
+def attn_fwd(qkv, b: int, h: int, D: int, t: int, c: int, o, lse2, scale: float = 0.0):
     """Slice-causal attention forward.
 
     ``qkv``: full-length projection buffer ``[L, b, h*3*D]`` (per head q,k,v interleaved);
     rows ``[0, c+t)`` are read, the slice's queries are rows ``[c, c+t)``.
     ``o``: ``[t*b, h*D]`` output of the slice (row = position*b + batch).
-    ``lse2``: fp32 ``[b*h, L]`` base-2 log-sum-exp, written at positions ``[c, c+t)``."""
-    st = cuda_lib().tp_attn_fwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, o.data_ptr(), o.stride(0),
-                                lse2.data_ptr(), lse2.stride(0),
-                                status_word(qkv.device).data_ptr(), _stream())
-    check(st, "tp_attn_fwd")
+    ``lse2``: fp32 ``[b*h, L]`` base-2 log-sum-exp, written at positions ``[c, c+t)``.
+    ``scale``: multiplier of q.k (0 = ``D ** -0.5``); heads narrower than ``D`` whose extra
+    columns are zero pass the scale of their real width."""
+    st = cuda_lib().tp_attn_fwd_scaled(_dt(qkv), D, float(scale), qkv.data_ptr(), b, h, t, c,
+                                       o.data_ptr(), o.stride(0), lse2.data_ptr(), lse2.stride(0),
+                                       status_word(qkv.device).data_ptr(), _stream())
+    check(st, "tp_attn_fwd_scaled")
     return o
 
 
 def attn_bwd(qkv, b: int, h: int, D: int, t: int, c: int, q_end: int, o, do_full, lse2, delta,
-             dqkv):
+             dqkv, scale: float = 0.0):
     """Slice-causal attention backward for the slice ``[c, c+t)``.
 
     Slices are processed last to first.  ``do_full`` is the full-length gradient of the
@@ -181,9 +183,10 @@ def attn_bwd(qkv, b: int, h: int, D: int, t: int, c: int, q_end: int, o, do_full
     before this call.  ``o`` is this slice's forward output ``[t*b, h*D]``; ``lse2`` and
     ``delta`` are fp32 ``[b*h, L]`` (``delta`` rows of this slice are written here).
     Writes the slice's complete ``d(qkv)`` ``[t*b, h*3*D]``."""
-    st = cuda_lib().tp_attn_bwd(_dt(qkv), D, qkv.data_ptr(), b, h, t, c, q_end, o.data_ptr(),
-                                o.stride(0), do_full.data_ptr(), do_full.stride(0),
-                                lse2.data_ptr(), lse2.stride(0), delta.data_ptr(), dqkv.data_ptr(),
-                                dqkv.stride(0), status_word(qkv.device).data_ptr(), _stream())
-    check(st, "tp_attn_bwd")
+    st = cuda_lib().tp_attn_bwd_scaled(_dt(qkv), D, float(scale), qkv.data_ptr(), b, h, t, c, q_end,
+                                       o.data_ptr(), o.stride(0), do_full.data_ptr(),
+                                       do_full.stride(0), lse2.data_ptr(), lse2.stride(0),
+                                       delta.data_ptr(), dqkv.data_ptr(), dqkv.stride(0),
+                                       status_word(qkv.device).data_ptr(), _stream())
+    check(st, "tp_attn_bwd_scaled")
     return dqkv

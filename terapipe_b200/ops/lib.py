@@ -91,6 +91,8 @@ SIGNATURES = {
     "tp_peer_sum": [P, I, P, I, I, P],
     "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
     "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
+    "tp_attn_fwd_scaled": [I, I, F, P, I, I, I, I, P, L, P, L, P, P],
+    "tp_attn_bwd_scaled": [I, I, F, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
 }
 
 

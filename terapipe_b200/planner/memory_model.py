@@ -62,15 +62,20 @@ def engine_memory_per_gpu(model_name, batch_size, tp=1, pp=1, n_layers=None,
     the full-length gradient buffers of the layer output and of the post-attention stream (2H)
     and 1/tp of those of the FFN pre-activation (4H), QKV (3H) and attention output (H);
     LayerNorm statistics (4 fp32) and log-sum-exp / delta rows (2 fp32 per local head).
-    Parameters cost 18 bytes each (16-bit model, fp32 master, two Adam moments, fp32 gradient)."""
+    Parameters cost 18 bytes each (16-bit model, fp32 master, two Adam moments, fp32 gradient).
+    Heads that are not 64 or 128 wide are stored 128 wide: QKV, the attention output, their
+    gradients and the two attention projection matrices grow by 128 / head_dim."""
     layers, hidden, seq_len, heads = MODEL_CONFIGS[model_name]
     layers = n_layers if n_layers is not None else layers
     per_stage = -(-layers // pp)
     tokens = batch_size * seq_len
-    act_elems = 4 * hidden + (3 * hidden + hidden + (8 if keep_gelu_input else 4) * hidden) / tp
-    grad_elems = 2 * hidden + (4 * hidden + 3 * hidden + hidden) / tp
+    head_dim = hidden // heads
+    pad = 1.0 if head_dim in (64, 128) else (64 if head_dim < 64 else 128) / head_dim
+    attn_w = (3 * hidden + hidden) * pad
+    act_elems = 4 * hidden + (attn_w + (8 if keep_gelu_input else 4) * hidden) / tp
+    grad_elems = 2 * hidden + (4 * hidden + attn_w) / tp
     act = tokens * (act_elems + grad_elems) * _F16 + tokens * (4 + 2 * heads / tp) * _F32
-    params = _layer_params(hidden, tp) * (_F16 + 4 * _F32)
+    params = (_layer_params(hidden, tp) + (pad - 1.0) * 4 * hidden * hidden / tp) * (_F16 + 4 * _F32)
     io = 4 * tokens * hidden * _F16
     return (per_stage * (act + params) + io) / 2 ** 30
 

@@ -25,7 +25,9 @@ def shard_path(directory: str, pp_rank: int, tp_rank: int, dp_rank: int = 0) -> 
 
 def _named(engine, buf) -> Dict[str, torch.Tensor]:
     from .engine import PARAM_ORDER
-    return {f"layers.layers.{l}.{name}": engine.param(l, name, buf).detach().float().cpu().clone()
+    # `get_param` gives the model's own shapes (an engine that pads heads for its kernels keeps
+    # the padding to itself), so a checkpoint does not depend on the engine's internal layout
+    return {f"layers.layers.{l}.{name}": engine.get_param(l, name, buf).detach().float().cpu().clone()
             for l in range(engine.n_layers) for name in PARAM_ORDER}
 
 
@@ -100,7 +102,7 @@ def load_checkpoint(engine, directory: str) -> dict:
                      ("exp_avg_sq", engine.exp_avg_sq)):
         for l in range(engine.n_layers):
             for name in PARAM_ORDER:
-                engine.param(l, name, buf).copy_(blob[key][f"layers.layers.{l}.{name}"])
+                engine.set_param(l, name, blob[key][f"layers.layers.{l}.{name}"], buf)
     engine.model.copy_(engine.master)
     engine.adam_state.copy_(blob["adam_state"])
     engine.step_count = blob["step"]

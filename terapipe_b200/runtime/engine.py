@@ -60,8 +60,10 @@ def _align(n: int, a: int = 8) -> int:
 class _Layout:
     """Offsets (in elements) of every parameter of the stage inside the flat buffers."""
 
-    def __init__(self, n_layers: int, H: int, F_: int, tp: int):
-        hl, fl = H // tp, F_ // tp
+    def __init__(self, n_layers: int, H: int, F_: int, tp: int, hl: Optional[int] = None):
+        # hl: local width of the attention projections as the kernels see it (heads padded to the
+        # kernels' head width); defaults to the model's own H / tp
+        hl, fl = (H // tp if hl is None else hl), F_ // tp
         self.shapes = {
             "attn_ln.weight": (H,), "attn_ln.bias": (H,),
             "attn.in_proj.weight": (3 * hl, H), "attn.in_proj.bias": (3 * hl,),
@@ -128,15 +130,23 @@ class StageEngine:
         assert heads % self.tp == 0 and Fw % self.tp == 0
         self.H, self.D = H, H // heads
         self.h = heads // self.tp
-        self.Hl, self.Fl = self.h * self.D, Fw // self.tp
-        if self.D not in (64, 128):
-            raise ValueError(f"head dim {self.D} is not supported by the attention kernels (64 or 128)")
+        # The attention kernels exist for 64- and 128-wide heads.  Any other width (80: gpt3-2b,
+        # 96: megatron-*, gpt3-7hm) runs as the next of the two: the rows of the query/key/value
+        # projection and the columns of the output projection that belong to the extra head
+        # columns are zero, so q.k, the attention output and every gradient of the real columns
+        # are unchanged, the gradients of the padding are exactly zero (Adam leaves it at zero),
+        # and only the softmax scale has to be told the real width.
+        if self.D > 128 or self.D % 8:
+            raise ValueError(f"head dim {self.D} is not supported (a multiple of 8 up to 128)")
+        self.Dk = self.D if self.D in (64, 128) else (64 if self.D < 64 else 128)
+        self.attn_scale = float(self.D) ** -0.5
+        self.Hl, self.Fl = self.h * self.Dk, Fw // self.tp
         self.L, self.B = config.seq_len, config.batch_size
         self.rows = self.L * self.B
         self.act = config.activation
         self.es = 2  # bytes per 16-bit element
 
-        self.layout = _Layout(self.n_layers, H, Fw, self.tp)
+        self.layout = _Layout(self.n_layers, H, Fw, self.tp, self.Hl)
         n = self.layout.total
         dev = self.device
         self.dp_sym = None
@@ -236,6 +246,41 @@ class StageEngine:
         off = self.layout.offsets[layer][name]
         return buf[off:off + math.prod(shape)].view(shape)
 
+    _HEAD_PADDED = ("attn.in_proj.weight", "attn.in_proj.bias", "attn.out_proj.weight")
+
+    def _pad_heads(self, name: str, w: torch.Tensor) -> torch.Tensor:
+        """A parameter (or gradient, or moment) of the model's own shape -> the shape the kernels
+        use: every head of the local q/k/v rows (output-projection columns) widened from D to
+        Dk with zeros.  Identity for the other parameters and when D is 64 or 128."""
+        if self.Dk == self.D or name not in self._HEAD_PADDED:
+            return w
+        h, D, pad = self.h, self.D, self.Dk - self.D
+        if name == "attn.in_proj.weight":
+            return torch.nn.functional.pad(w.reshape(h, 3, D, -1), (0, 0, 0, pad)).reshape(3 * self.Hl, -1)
+        if name == "attn.in_proj.bias":
+            return torch.nn.functional.pad(w.reshape(h, 3, D), (0, pad)).reshape(3 * self.Hl)
+        return torch.nn.functional.pad(w.reshape(-1, h, D), (0, pad)).reshape(-1, self.Hl)
+
+    def _unpad_heads(self, name: str, w: torch.Tensor) -> torch.Tensor:
+        """Inverse of :meth:`_pad_heads`: the kernels' shape -> the model's own shape."""
+        if self.Dk == self.D or name not in self._HEAD_PADDED:
+            return w
+        h, D, Dk = self.h, self.D, self.Dk
+        if name == "attn.in_proj.weight":
+            return w.reshape(h, 3, Dk, -1)[:, :, :D].reshape(3 * h * D, -1)
+        if name == "attn.in_proj.bias":
+            return w.reshape(h, 3, Dk)[:, :, :D].reshape(3 * h * D)
+        return w.reshape(-1, h, Dk)[:, :, :D].reshape(-1, h * D)
+
+    def get_param(self, layer: int, name: str, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The parameter in the model's own shape (a view unless heads are padded)."""
+        return self._unpad_heads(name, self.param(layer, name, buf))
+
+    def set_param(self, layer: int, name: str, value: torch.Tensor,
+                  buf: Optional[torch.Tensor] = None) -> None:
+        """Store a tensor of the model's own shape into the flat buffer ``buf``."""
+        self.param(layer, name, buf).copy_(self._pad_heads(name, value.to(self.device)))
+
     def _init_weights(self, init: str) -> None:
         """``"reference"``: the full master matrix of every layer is drawn on the CPU from
         the global generator seeded with ``seed`` in the portable layer's order, then sliced
@@ -270,7 +315,7 @@ class StageEngine:
                 else:
                     ncol = shape[1] // self.tp
                     w = w[:, self.tp_idx * ncol:(self.tp_idx + 1) * ncol]
-                self.param(local, name, self.master).copy_(w)
+                self.set_param(local, name, w, self.master)
                 del w
             if mine:
                 for name in ("attn_ln.weight", "fc_ln.weight"):
@@ -281,21 +326,20 @@ class StageEngine:
             self.master.copy_(self.model)
 
     def state_dict(self) -> Dict[str, torch.Tensor]:
-        return {f"layers.layers.{l}.{name}": self.param(l, name).clone()
+        return {f"layers.layers.{l}.{name}": self.get_param(l, name).clone()
                 for l in range(self.n_layers) for name in PARAM_ORDER}
 
     def load_state_dict(self, sd: Dict[str, torch.Tensor]) -> None:
         for l in range(self.n_layers):
             for name in PARAM_ORDER:
-                src = sd[f"layers.layers.{l}.{name}"].to(self.device)
-                self.param(l, name, self.master).copy_(src)
+                self.set_param(l, name, sd[f"layers.layers.{l}.{name}"], self.master)
         self.model.copy_(self.master)
         if self.dtype != torch.float32:
             self.master.copy_(self.model)
 
     def named_grads(self, unscale=True) -> Dict[str, torch.Tensor]:
         s = 1.0 / self.loss_scale if unscale else 1.0
-        return {f"layers.layers.{l}.{name}": self.param(l, name, self.grad).clone() * s
+        return {f"layers.layers.{l}.{name}": self.get_param(l, name, self.grad).clone() * s
                 for l in range(self.n_layers) for name in PARAM_ORDER}
 
     # ------------------------------------------------------------------ buffers
@@ -535,10 +579,10 @@ class StageEngine:
                           qkv, 3 * Hl, T, 3 * Hl, H, rpr, bias=self._p(l, "attn.in_proj.bias"))
             ao = self.ao[l].data_ptr() + r0 * Hl * es
             lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
-            rc = lib.tp_attn_fwd(dt, self.D, qkv_base, b, self.h, t, c, ao, Hl, lse, self.L,
-                                 self._status_ptr, s)
+            rc = lib.tp_attn_fwd_scaled(dt, self.Dk, self.attn_scale, qkv_base, b, self.h, t, c, ao, Hl,
+                                        lse, self.L, self._status_ptr, s)
             if rc:
-                F.check(rc, "tp_attn_fwd")
+                F.check(rc, "tp_attn_fwd_scaled")
             self._gemm_rs(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl,
                           self.xmid[l].data_ptr() + r0 * H * es, H, T, H, Hl, rpr,
                           bias=self._p(l, "attn.out_proj.bias"),
@@ -577,10 +621,10 @@ class StageEngine:
                        bias=self._p(l, "attn.in_proj.bias"))
             ao = self.ao[l].data_ptr() + r0 * Hl * es
             lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
-            rc = lib.tp_attn_fwd(dt, self.D, qkv_base, b, self.h, t, c, ao, Hl, lse, self.L,
-                                 self._status_ptr, s)
+            rc = lib.tp_attn_fwd_scaled(dt, self.Dk, self.attn_scale, qkv_base, b, self.h, t, c, ao, Hl,
+                                        lse, self.L, self._status_ptr, s)
             if rc:
-                F.check(rc, "tp_attn_fwd")
+                F.check(rc, "tp_attn_fwd_scaled")
             xmid = self.xmid[l].data_ptr() + r0 * H * es
             if self.ar is not None:
                 self._gemm_ar(ao, Hl, self._p(l, "attn.out_proj.weight"), Hl, f"xmid{l}", r0, T, H, Hl,
@@ -652,10 +696,11 @@ class StageEngine:
             dao_base = self.dAO[l].data_ptr() + self.L * boff * Hl * es
             lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
             delta = self.delta[l].data_ptr() + boff * self.h * self.L * 4
-            rc = lib.tp_attn_bwd(dt, self.D, qkv_base, b, self.h, t, c, self.L, ao, Hl, dao_base, Hl,
-                                 lse, self.L, delta, dqkv, 3 * Hl, self._status_ptr, s)
+            rc = lib.tp_attn_bwd_scaled(dt, self.Dk, self.attn_scale, qkv_base, b, self.h, t, c, self.L,
+                                        ao, Hl, dao_base, Hl, lse, self.L, delta, dqkv, 3 * Hl,
+                                        self._status_ptr, s)
             if rc:
-                F.check(rc, "tp_attn_bwd")
+                F.check(rc, "tp_attn_bwd_scaled")
             if self.ar is not None:
                 self._gemm_ar(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, "dln", 0, T, H, 3 * Hl,
                               b_mn=1)
@@ -716,10 +761,11 @@ class StageEngine:
             dao_base = self.dAO[l].data_ptr() + self.L * boff * Hl * es
             lse = self.lse[l].data_ptr() + boff * self.h * self.L * 4
             delta = self.delta[l].data_ptr() + boff * self.h * self.L * 4
-            rc = lib.tp_attn_bwd(dt, self.D, qkv_base, b, self.h, t, c, self.L, ao, Hl, dao_base, Hl,
-                                 lse, self.L, delta, dqkv, 3 * Hl, self._status_ptr, s)
+            rc = lib.tp_attn_bwd_scaled(dt, self.Dk, self.attn_scale, qkv_base, b, self.h, t, c, self.L,
+                                        ao, Hl, dao_base, Hl, lse, self.L, delta, dqkv, 3 * Hl,
+                                        self._status_ptr, s)
             if rc:
-                F.check(rc, "tp_attn_bwd")
+                F.check(rc, "tp_attn_bwd_scaled")
             self._gemm_rs(dqkv, 3 * Hl, self._p(l, "attn.in_proj.weight"), H, dln, H, T, H, 3 * Hl, rpr,
                           b_mn=1)
             x_mine = self.X[l].data_ptr() + m0 * H * es

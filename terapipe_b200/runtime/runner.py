@@ -63,7 +63,8 @@ class NCCLTransformerRunner:
             mpu.model_parallel_cuda_manual_seed(0)
         use_b200 = engine == "b200" or (engine == "auto" and torch.cuda.is_available()
                                         and mixed_precision
-                                        and config.attention_heads_dim in (64, 128))
+                                        and config.attention_heads_dim <= 128
+                                        and config.attention_heads_dim % 8 == 0)
         self.engine_kind = "b200" if use_b200 else "portable"
         if use_b200:
             from .engine import StageEngine

@@ -70,6 +70,11 @@ class _FakeEngine:
         off = self.layout.offsets[layer][name]
         return buf[off:off + math.prod(shape)].view(shape)
 
+    get_param = param
+
+    def set_param(self, layer, name, value, buf=None):
+        self.param(layer, name, buf).copy_(value)
+
 
 def test_checkpoint_roundtrip_and_reshard(tmp_path):
     from terapipe_b200.runtime import checkpointing as ck

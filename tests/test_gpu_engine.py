@@ -102,3 +102,50 @@ def test_trainer_step_and_checkpoint_roundtrip(tmp_path):
     # both continue identically
     a, b = tr.train_step(x), fresh.train_step(x)
     assert a == b
+
+
+@pytest.mark.parametrize("heads,hidden", [(4, 320), (4, 384)])
+def test_engine_with_head_dim_80_and_96_matches_portable_oracle(heads, hidden, tmp_path):
+    """Heads of 80 (gpt3-2b) and 96 columns (megatron-*, gpt3-7hm) run on the 128-wide attention
+    kernels with zero-padded projections: outputs, gradients (in the model's own shapes), an
+    optimizer step and a checkpoint must match what the unpadded model gives, and the padding
+    must stay exactly zero."""
+    from terapipe_b200.models import TransformerConfig
+    from terapipe_b200.runtime import checkpointing as ck
+    from terapipe_b200.runtime.engine import StageEngine
+    cfg = TransformerConfig(batch_size=2, seq_len=128, n_layers=2, embedding_dim=hidden,
+                            num_attention_heads=heads, n_devices=1)
+    g = torch.Generator().manual_seed(7)
+    x = torch.randn(cfg.seq_len, cfg.batch_size, cfg.embedding_dim, generator=g).cuda()
+    oracle = _oracle(cfg, x)
+    eng = StageEngine(cfg, [1, 1], [40, 24, 64], init="reference", use_graph=False, lr=1e-3)
+    assert eng.Dk == 128 and eng.D == hidden // heads
+    sd = eng.state_dict()
+    for (name, a), b in zip(sd.items(), oracle.layers.state_dict().values()):
+        assert a.shape == b.shape and _rel(a, b) < 5e-3, name
+    eng.set_input(x)
+    eng.compute_grads()
+    eng.check_status()
+    assert abs(eng.loss().item() - oracle.last_loss) < 2e-3
+    assert _rel(eng.output(), oracle_output(oracle, x)) < 2e-2
+    got = eng.named_grads()
+    for name, gw in oracle.named_grads().items():
+        assert got[name].shape == gw.shape and _rel(got[name], gw) < 2e-2, (name, _rel(got[name], gw))
+    # the padding receives no gradient and an optimizer step leaves it at zero
+    eng.grad.zero_()
+    for _ in range(2):
+        eng.step()
+    torch.cuda.synchronize()
+    eng.check_status()
+    for name in eng._HEAD_PADDED:
+        for buf in (eng.master, eng.model, eng.exp_avg_sq):
+            w = eng.param(0, name, buf)
+            assert w.shape != eng.get_param(0, name, buf).shape
+            # dropping the padding and putting zeros back reproduces the buffer
+            assert torch.equal(eng._pad_heads(name, eng._unpad_heads(name, w)), w), name
+    # a checkpoint holds the model's own shapes and restores the padded buffers
+    ck.save_checkpoint(eng, str(tmp_path))
+    fresh = StageEngine(cfg, [1, 1], [40, 24, 64], init="device", use_graph=False, lr=1e-3, seed=3)
+    ck.load_checkpoint(fresh, str(tmp_path))
+    for name in ("master", "exp_avg", "exp_avg_sq", "model"):
+        assert torch.equal(getattr(fresh, name), getattr(eng, name)), name

@@ -268,3 +268,43 @@ def test_assign_cache_backward_leaves_the_incoming_gradient_untouched():
     keep = torch.ones(6, dtype=torch.bool)
     keep[2:4] = False
     assert torch.equal(g_cache[:, keep], g_before[:, keep])
+
+
+def test_head_padding_keeps_attention_and_gradients():
+    """The engine's zero-padding of heads (80 -> 128 columns): padded projections with the
+    softmax scale of the real width give the same attention output and the same gradients for
+    the real entries, zero gradients for the padding, and pad / unpad are inverse."""
+    import types
+
+    from terapipe_b200.runtime.engine import StageEngine
+    h, D, Dk, H, T = 2, 80, 128, 160, 12
+    eng = types.SimpleNamespace(h=h, D=D, Dk=Dk, Hl=h * Dk, _HEAD_PADDED=StageEngine._HEAD_PADDED)
+    pad = lambda n, w: StageEngine._pad_heads(eng, n, w)
+    unpad = lambda n, w: StageEngine._unpad_heads(eng, n, w)
+    g = torch.Generator().manual_seed(0)
+    w_in = torch.randn(3 * h * D, H, generator=g, dtype=torch.float64) / 8
+    b_in = torch.randn(3 * h * D, generator=g, dtype=torch.float64)
+    w_out = torch.randn(H, h * D, generator=g, dtype=torch.float64) / 8
+    x = torch.randn(T, H, generator=g, dtype=torch.float64)
+    for n, w in (("attn.in_proj.weight", w_in), ("attn.in_proj.bias", b_in), ("attn.out_proj.weight", w_out)):
+        assert torch.equal(unpad(n, pad(n, w)), w)
+    assert torch.equal(pad("fc1.weight", w_in), w_in)
+
+    def attention(wi, bi, wo, d):
+        qkv = (x @ wi.t() + bi).view(T, h, 3, d)
+        q, k, v = (qkv[:, :, i].transpose(0, 1) for i in range(3))
+        s = (q @ k.transpose(1, 2)) * D ** -0.5
+        s = s.masked_fill(torch.ones(T, T).triu(1).bool(), float("-inf"))
+        o = (s.softmax(-1) @ v).transpose(0, 1).reshape(T, h * d)
+        return o @ wo.t()
+
+    plain = [t.clone().requires_grad_() for t in (w_in, b_in, w_out)]
+    padded = [pad(n, t).clone().requires_grad_() for n, t in
+              (("attn.in_proj.weight", w_in), ("attn.in_proj.bias", b_in), ("attn.out_proj.weight", w_out))]
+    y0, y1 = attention(*plain, D), attention(*padded, Dk)
+    assert torch.allclose(y0, y1, atol=1e-12)
+    y0.square().sum().backward()
+    y1.square().sum().backward()
+    for n, a, b in zip(("attn.in_proj.weight", "attn.in_proj.bias", "attn.out_proj.weight"), plain, padded):
+        assert torch.allclose(unpad(n, b.grad), a.grad, atol=1e-10), n
+        assert torch.equal(pad(n, unpad(n, b.grad)), b.grad), n    # the padding's gradient is zero

@@ -2,6 +2,10 @@
 
 * ``_tp_sm100.so``  — CUDA kernels, compiled by nvcc for sm_100a only
   (``-gencode arch=compute_100a,code=sm_100a``); cross-compiles on machines without a GPU.
+* ``_tp_sm100_checked.so`` — the same sources compiled with ``-DTP_CHECKED``: index checks next
+  to every raw-pointer access into peer staging, flag and statistics arrays; a failed check
+  writes a code into the launch's status word and skips the access.  Loaded instead of the
+  regular library when ``TERAPIPE_CHECKED=1``.
 * ``_tp_host.so``   — host C++ (slice-schedule dynamic program), compiled by g++.
 
 The libraries sit beside this file so that a source checkout carries them to wherever the
@@ -20,6 +24,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 CUDA_LIB = HERE / "_tp_sm100.so"
+CUDA_LIB_CHECKED = HERE / "_tp_sm100_checked.so"
 HOST_LIB = HERE / "_tp_host.so"
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -60,16 +65,19 @@ def cuda_sources():
     return sorted(CSRC.glob("*.cu"))
 
 
-def build_cuda(force=False, verbose=False, ptxas_info=False) -> Path:
+def build_cuda(force=False, verbose=False, ptxas_info=False, checked=False) -> Path:
+    lib = CUDA_LIB_CHECKED if checked else CUDA_LIB
     srcs = cuda_sources()
     deps = srcs + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h"))
-    if not force and not _stale(CUDA_LIB, deps):
-        return CUDA_LIB
+    if not force and not _stale(lib, deps):
+        return lib
     objs = []
-    build_dir = HERE / "build"
+    build_dir = HERE / ("build_checked" if checked else "build")
     build_dir.mkdir(exist_ok=True)
     procs = []
     flags = [f for f in NVCC_FLAGS if f != "-shared"]
+    if checked:
+        flags += ["-DTP_CHECKED"]
     if ptxas_info:
         flags += ["-Xptxas", "-v"]
     for src in srcs:
@@ -87,11 +95,14 @@ def build_cuda(force=False, verbose=False, ptxas_info=False) -> Path:
         if proc.returncode != 0:
             sys.stderr.write(out)
             raise RuntimeError(f"build failed: {' '.join(map(str, cmd))}")
-    _run([_nvcc(), "-shared", "-Xcompiler", "-fPIC", "-o", str(CUDA_LIB), *map(str, objs)], verbose)
-    CUDA_LIB.with_suffix(".stamp").write_text(_digest(deps))
+    # link beside the target and rename: a reader (or a copy of the tree) never sees half a library
+    tmp = lib.with_suffix(".so.tmp")
+    _run([_nvcc(), "-shared", "-Xcompiler", "-fPIC", "-o", str(tmp), *map(str, objs)], verbose)
+    os.replace(tmp, lib)
+    lib.with_suffix(".stamp").write_text(_digest(deps))
     if ptxas_info:
         print(log)
-    return CUDA_LIB
+    return lib
 
 
 def build_host(force=False, verbose=False) -> Path:
@@ -104,10 +115,13 @@ def build_host(force=False, verbose=False) -> Path:
     return HOST_LIB
 
 
-def build_all(force=False, verbose=False):
-    return build_host(force, verbose), build_cuda(force, verbose)
+def build_all(force=False, verbose=False, checked=True):
+    """Host library, kernel library and (unless ``checked=False``) the checked kernel library."""
+    out = (build_host(force, verbose), build_cuda(force, verbose))
+    if checked:
+        out += (build_cuda(force, verbose, checked=True),)
+    return out
 
 
 if __name__ == "__main__":
-    build_all(force="--force" in sys.argv, verbose=True)
-    print("built", HOST_LIB, CUDA_LIB)
+    print("built", *build_all(force="--force" in sys.argv, verbose=True))

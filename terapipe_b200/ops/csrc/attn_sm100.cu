@@ -292,6 +292,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     if (ok) {
       tc_fence_after();
       const float inv_l = 1.0f / l;
+      // checked build: the row's statistics slot and its columns of the output exist
+      const bool row_ok = qi < p.t && TP_CHECK(qpos >= 0 && qpos < p.lse_stride && (hi + 1) * D <= p.ld_o,
+                                               p.err, kErrCheckAttn);
       T* orow = static_cast<T*>(p.o) + (static_cast<long long>(qi) * p.b + bi) * p.ld_o + hi * D;
 #pragma unroll 1
       for (int ch = 0; ch < D / 32; ++ch) {
@@ -299,7 +302,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __syncwarp();
         tmem_ld_32x32(tO + lane_base + ch * 32, raw);
         tmem_ld_wait();
-        if (qi < p.t) {
+        if (row_ok) {
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             uint4 u;
@@ -311,7 +314,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           }
         }
       }
-      if (qi < p.t) p.lse2[static_cast<long long>(bh) * p.lse_stride + qpos] = m + log2f(l);
+      if (row_ok) p.lse2[static_cast<long long>(bh) * p.lse_stride + qpos] = m + log2f(l);
     }
   }
 
@@ -464,11 +467,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
         const int y0 = ystart + i * 64;
         // a block that runs past q_end takes its lse/delta through guarded plain loads instead
         const bool bulk_stats = MODE == 0 && y0 + 64 <= p.q_end && (y0 & 3) == 0 &&
-                                (p.lse_stride & 3) == 0;
+                                (p.lse_stride & 3) == 0 &&
+                                TP_CHECK(y0 >= 0 && y0 + 64 <= p.lse_stride, p.err, kErrCheckAttn);
         if (MODE == 0 && !bulk_stats) {
           const long long base = static_cast<long long>(bh) * p.lse_stride;
           for (int k = 0; k < 64; ++k) {
-            const bool in = y0 + k < p.q_end;
+            const bool in = y0 + k < p.q_end &&
+                            TP_CHECK(y0 + k >= 0 && y0 + k < p.lse_stride, p.err, kErrCheckAttn);
             sh->lse[st][k] = in ? __ldcg(p.lse2 + base + y0 + k) : 0.0f;
             sh->delta[st][k] = in ? __ldcg(p.delta + base + y0 + k) : 0.0f;
           }
@@ -528,7 +533,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQKV128,
     const int r = threadIdx.x & 127;           // row of the stationary tile = TMEM lane
     const uint32_t lane_base = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const int xabs = x0 + r;                   // absolute position of this thread's row
-    const bool x_ok = xabs < p.c + p.t;
+    // checked build: the row's statistics slot and its columns of the gradient exist
+    const bool x_ok = xabs < p.c + p.t &&
+                      TP_CHECK(xabs >= p.c && xabs < p.lse_stride && (hi + 1) * 3 * D <= p.ld_dqkv, p.err,
+                               kErrCheckAttn);
     float lse_r = 0.0f, delta_r = 0.0f;
     if (MODE == 1 && x_ok) {
       lse_r = p.lse2[static_cast<long long>(bh) * p.lse_stride + xabs];

@@ -118,7 +118,9 @@ __global__ void __launch_bounds__(256) dp_reduce_adam_kernel(const DpParams p) {
   if (threadIdx.x == 0) {
     if (blockIdx.x == 0)
       for (int r = 0; r < p.dp; ++r) st_release_sys_i(p.flags[r] + p.rank, epoch);
-    bool ok = true;
+    // checked build: group size within the pointer tables, owned range well formed
+    bool ok = TP_CHECK(p.dp >= 1 && p.dp <= kMaxDp && p.rank >= 0 && p.rank < p.dp, p.err, kErrCheckPeer) &&
+              TP_CHECK(p.begin >= 0 && p.begin <= p.end && ((p.begin | p.end) & 3) == 0, p.err, kErrCheckNorm);
     for (int r = 0; r < p.dp && ok; ++r) ok = spin_until(my_flags + r, epoch, p.err, kErrWaitPeer);
     s_ok = ok ? 1 : 0;
   }
@@ -307,7 +309,7 @@ __global__ void __launch_bounds__(256) ag_push_kernel(const uint4* __restrict__ 
 __global__ void group_barrier_kernel(const PeerPtrs pp) {
   const int epoch = pp.epoch + (pp.epoch_base ? *pp.epoch_base : 0);
   const int r = threadIdx.x;
-  if (r < pp.n) {
+  if (r < pp.n && TP_CHECK(pp.n <= kMaxDp && pp.rank >= 0 && pp.rank < pp.n, pp.err, kErrCheckPeer)) {
     __threadfence_system();
     st_release_sys_i(pp.flags[r] + pp.rank, epoch);
     spin_until(pp.flags[pp.rank] + r, epoch, pp.err, kErrWaitPeer);
@@ -356,7 +358,8 @@ extern "C" int tp_ag_push(const void* src, long long bytes, void* const* dst_ptr
 namespace tp {
 __global__ void ag_signal_kernel(const PeerPtrs pp) {
   const int r = threadIdx.x;
-  if (r < pp.n && r != pp.rank) {
+  if (r < pp.n && r != pp.rank &&
+      TP_CHECK(pp.n <= kMaxDp && pp.rank >= 0 && pp.rank < pp.n, pp.err, kErrCheckPeer)) {
     const int epoch = pp.epoch + (pp.epoch_base ? *pp.epoch_base : 0);
     __threadfence_system();
     st_release_sys_i(pp.flags[r] + pp.rank, epoch);
@@ -420,4 +423,28 @@ extern "C" int tp_set_wait_limit_ns(unsigned long long ns) {
   const int a = tp_set_wait_limit_ns_comm(ns), b = tp_set_wait_limit_ns_gemm(ns),
             c = tp_set_wait_limit_ns_attn(ns);
   return (a | b | c) ? kErrDriver : kOk;
+}
+
+// Which build this is: 1 when the kernels carry their index checks (-DTP_CHECKED), else 0.
+extern "C" int tp_checked_build(void) {
+#ifdef TP_CHECKED
+  return 1;
+#else
+  return 0;
+#endif
+}
+
+namespace tp {
+__global__ void checked_selftest_kernel(int value, int limit, int* err) {
+  if (TP_CHECK(value >= 0 && value < limit, err, kErrCheckSelfTest)) return;
+}
+}  // namespace tp
+
+// Runs the check `0 <= value < limit` inside a kernel, the way the kernels check their indices.
+// Checked build: a failing check leaves kErrCheckSelfTest in *err (nothing traps, nothing is
+// accessed).  Regular build: the check is compiled out and *err is never written.
+extern "C" int tp_checked_selftest(int value, int limit, int* err, void* stream) {
+  if (!err) return kErrBadArgument;
+  tp::checked_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(value, limit, err);
+  return cudaGetLastError() == cudaSuccess ? kOk : kErrLaunch;
 }

@@ -25,7 +25,32 @@ enum ErrorCode : int {
   kErrWaitTmemEmpty = 104,
   kErrWaitPeer = 105,
   kErrWaitAttn = 106,
+  // checked build only: an index check inside a kernel failed (the access was skipped)
+  kErrCheckTile = 121,      // GEMM tile outside the output grid
+  kErrCheckStaging = 122,   // slot of a peer staging / flag array beyond its capacity
+  kErrCheckPeer = 123,      // rank index outside the group
+  kErrCheckAttn = 124,      // attention row or key block outside the buffers
+  kErrCheckNorm = 125,      // LayerNorm / element-wise row, column or slot outside the buffers
+  kErrCheckSelfTest = 129,  // raised on purpose by tp_checked_selftest
 };
+
+// Checked build (-DTP_CHECKED, loaded with TERAPIPE_CHECKED=1): index checks compiled into the
+// kernels next to the accesses that no tensor map bounds (raw pointers into peer staging, flag
+// arrays, partial-sum slots).  A failed check writes its code into the launch's status word
+// (the first failure wins) and the guarded access is skipped; nothing traps, so the context
+// stays usable and the host reads the code like a wait time-out.  In the regular build
+// TP_CHECK(...) is the constant `true` and its condition is not evaluated.
+#ifdef TP_CHECKED
+#ifdef __CUDACC__
+__device__ __forceinline__ bool check_record(bool ok, int* err, int code) {
+  if (!ok && err != nullptr) atomicCAS(err, 0, code);
+  return ok;
+}
+#endif
+#define TP_CHECK(cond, err, code) (::tp::check_record((cond), (err), (code)))
+#else
+#define TP_CHECK(cond, err, code) (true)
+#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,

@@ -638,7 +638,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // bytes per warp instruction over NVLink), then one thread publishes the tile.  The
         // release store is cumulative over the writes ordered before it by the barrier.
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        {
+        // checked build: the tile's slot in the owner's staging and flag arrays exists
+        const bool slot_ok = TP_CHECK(tile >= 0 && tile < ar.max_tiles && ar.tp <= kMaxTp, p.err,
+                                      kErrCheckStaging);
+        if (slot_ok) {
           const int owner = tile % ar.tp;
           uint4* dst = reinterpret_cast<uint4*>(
               static_cast<T*>(ar.stage[owner]) +
@@ -649,7 +652,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
           for (int k = 0; k < kBM * BN * 2 / 16 / 128; ++k) dst[e + k * 128] = src[e + k * 128];
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (threadIdx.x == 64)
+        if (threadIdx.x == 64 && slot_ok)
           st_release_sys(ar.flag_a[tile % ar.tp] + static_cast<long long>(tile) * kMaxTp + ar.rank, ar_epoch);
       }
     }
@@ -663,6 +666,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int n_owned = (p.num_tiles - ar.rank + ar.tp - 1) / ar.tp;
     for (int j = blockIdx.x; j < n_owned; j += gridDim.x) {
       const int tile = j * ar.tp + ar.rank;
+      if (!TP_CHECK(tile >= 0 && tile < ar.max_tiles, p.err, kErrCheckStaging)) continue;
       if (threadIdx.x == 0) {
         bool ok = true;
         for (int src = 0; src < ar.tp && ok; ++src)
@@ -727,7 +731,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     // phase C: every tile of the output must have arrived in this rank's memory
     for (int tile = blockIdx.x * kGemmThreads + threadIdx.x; tile < p.num_tiles;
          tile += gridDim.x * kGemmThreads)
-      wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
+      if (TP_CHECK(tile < ar.max_tiles, p.err, kErrCheckStaging))
+        wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
   }
 
   // teardown: on an aborted run give in-flight bulk copies time to land before the CTA's
@@ -1027,6 +1032,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           bool waited = false;
           for (int src = m0 / p.ag_rows; src <= last_row / p.ag_rows && ok; ++src) {
             if (src == p.ag_rank || (ag_seen >> src) & 1u) continue;
+            if (!TP_CHECK(src >= 0 && src < kMaxTp, p.err, kErrCheckPeer)) continue;
             ok = wait_flag(p.ag_flags + src, target, wctx, kErrWaitPeer);
             ag_seen |= 1u << src;
             waited = true;
@@ -1144,6 +1150,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const uint32_t acc_phase = (it >> 1) & 1;
       int m_idx, n_idx;
       pair_tile_coords(p, tile, m_idx, n_idx);
+      // checked build: the tile order must stay inside the grid (the tile's own stores go through
+      // the tensor map, which clips; the peer accesses below are guarded one by one)
+      (void)TP_CHECK(m_idx >= 0 && m_idx < p.num_m_tiles && n_idx >= 0 && n_idx * BN < p.N, p.err,
+                     kErrCheckTile);
       const int m0 = m_idx * (2 * kBM) + static_cast<int>(cta) * kBM;
       const int n0 = n_idx * BN;
       const long long t_e = TRACE ? clock64() : 0;
@@ -1163,6 +1173,11 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
         const long long tile_elems = kBM * BN;
         const bool mine = row0 < p.M && owner == ar.rank;
+        // checked build: the block's slot in the staging and flag arrays, and the owner's rank
+        // (rows past M belong to no block: nothing of theirs is accessed)
+        const bool slot_ok = row0 >= p.M ||
+                             (TP_CHECK(unit >= 0 && unit < ar.max_tiles, p.err, kErrCheckStaging) &&
+                              TP_CHECK(owner >= 0 && owner < ar.tp && ar.tp <= kMaxTp, p.err, kErrCheckPeer));
         // Hand this warp's part of the block to the publishing warp (which keeps at most two
         // blocks outstanding).  A warp that owns its rows has nothing to publish and says so
         // BEFORE it waits for its peers: their publishing warps wait for all eight epilogue warps
@@ -1186,6 +1201,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           int got = 1;
           if (lane == 0) pub_arrive();
           if (lane == 0) {
+            if (!slot_ok) got = 0;
             for (int src = 0; src < ar.tp && got; ++src)
               if (src != ar.rank)
                 got = wait_flag(ar.flag_a[ar.rank] + static_cast<long long>(unit) * kMaxTp + src, ar_epoch,
@@ -1211,6 +1227,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             __syncwarp();
             tmem_ld_32x32(t_acc + c * 32, r);
             tmem_ld_wait();
+            if (!slot_ok) continue;   // checked build: nothing is stored outside the staging buffer
             uint8_t* sb = es.buf + (c & 2 ? 2048 : 0);
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
@@ -1243,7 +1260,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // phase A: this warp's chunks of the partial tile go to the owner's staging buffer
         const int m128 = m0 / kBM;
         const int ar_tile = m128 + n_idx * num_m128;
-        const bool in_range = m128 < num_m128;  // M may end inside the pair tile (warp-uniform)
+        // M may end inside the pair tile (warp-uniform); checked build: the tile's slot exists
+        const bool in_range = m128 < num_m128 &&
+                              TP_CHECK(ar_tile >= 0 && ar_tile < ar.max_tiles && ar.tp <= kMaxTp, p.err,
+                                       kErrCheckStaging);
         const int owner = ar_tile % ar.tp;
         const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
         T* tile_dst = static_cast<T*>(ar.stage[owner]) +
@@ -1320,6 +1340,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           } else {            // next_owned indexes the tiles this rank owns
             otile = next_owned * ar.tp + ar.rank;
           }
+          o_in_range = o_in_range && TP_CHECK(otile >= 0 && otile < ar.max_tiles, p.err, kErrCheckStaging);
           if (threadIdx.x == 64) {
             bool ready = true;
             if (o_in_range)
@@ -1333,7 +1354,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             if (o_in_range) ar_reduce_tile<T, BN>(p, ar, otile, num_m128, threadIdx.x - 64, 256, ar.exchange != 0, stage_half);
             if (!ar.exchange) {
               asm volatile("bar.sync 2, 256;" ::: "memory");
-              if (threadIdx.x >= 64 && threadIdx.x < 64 + ar.tp)
+              if (o_in_range && threadIdx.x >= 64 && threadIdx.x < 64 + ar.tp)
                 st_release_sys(ar.flag_b[threadIdx.x - 64] + otile, ar_epoch);
             }
             next_owned += ar.exchange ? 1 : static_cast<int>(gridDim.x);
@@ -1382,6 +1403,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
           if (row0 >= p.M) break;
           const int owner = min(row0 / ar.rows_per_rank, ar.tp - 1);
           if (owner == ar.rank || owner == last) continue;
+          if (!TP_CHECK(unit >= 0 && unit < ar.max_tiles, p.err, kErrCheckStaging) ||
+              !TP_CHECK(owner >= 0 && owner < ar.tp, p.err, kErrCheckPeer))
+            continue;
           if (!fenced) {
             __threadfence_system();
             fenced = true;
@@ -1410,6 +1434,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int o128 = (t2 % p.num_m_tiles) * 2 + static_cast<int>(cta);
         if (o128 >= num_m128) continue;  // uniform over the CTA
         const int tile = o128 + (t2 / p.num_m_tiles) * num_m128;
+        if (!TP_CHECK(tile >= 0 && tile < ar.max_tiles, p.err, kErrCheckStaging)) continue;
         if (threadIdx.x == 0) {
           bool ok = true;
           for (int src = 0; src < ar.tp && ok; ++src)
@@ -1425,6 +1450,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       const int n_owned = (num_ar_tiles - ar.rank + ar.tp - 1) / ar.tp;
       for (int j = *s_next; j < n_owned; j += gridDim.x) {
         const int tile = j * ar.tp + ar.rank;
+        if (!TP_CHECK(tile >= 0 && tile < ar.max_tiles, p.err, kErrCheckStaging)) continue;
         if (threadIdx.x == 0) {
           bool ok = true;
           for (int src = 0; src < ar.tp && ok; ++src)
@@ -1439,7 +1465,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       // phase C: every tile of the output must have arrived in this rank's memory
       for (int tile = blockIdx.x * nthreads + threadIdx.x; tile < num_ar_tiles; tile += gridDim.x * nthreads)
-        wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
+        if (TP_CHECK(tile < ar.max_tiles, p.err, kErrCheckStaging))
+          wait_flag(ar.flag_b[ar.rank] + tile, ar_epoch, wctx, kErrWaitPeer);
     }
     __syncthreads();
   }

@@ -11,7 +11,7 @@ from typing import Optional
 
 import torch
 
-from .lib import CommTimeout, KernelError, check, cuda_lib
+from .lib import CHECK_CODES, _ERRORS, CheckFailed, CommTimeout, KernelError, check, cuda_lib
 
 _ACT = {None: 0, "none": 0, "relu": 1, "gelu": 2}
 _status = {}
@@ -44,12 +44,15 @@ def status_word(device=None) -> torch.Tensor:
 
 
 def check_device_status(device=None, reset=True) -> None:
-    """Synchronising read of the status word; raises :class:`CommTimeout` if a wait ran out."""
+    """Synchronising read of the status word; raises :class:`CommTimeout` if a wait ran out and
+    :class:`CheckFailed` if an index check of the checked build failed."""
     word = status_word(device)
     code = int(word.item())
     if code != 0:
         if reset:
             word.zero_()
+        if code in CHECK_CODES:
+            raise CheckFailed(f"{_ERRORS.get(code, 'checked build: index check failed')} (code {code})")
         raise CommTimeout(f"a device-side wait timed out (code {code})")
 
 

@@ -23,7 +23,19 @@ _ERRORS = {-1: "bad argument", -2: "driver call failed (tensor map)", -3: "launc
            -4: "size beyond the built-in maximum", 101: "producer wait timed out",
            102: "MMA wait timed out", 103: "epilogue wait timed out",
            104: "TMEM-empty wait timed out", 105: "peer wait timed out",
-           106: "attention wait timed out"}
+           106: "attention wait timed out",
+           # checked build (TERAPIPE_CHECKED=1): an index check inside a kernel failed
+           121: "checked build: GEMM tile outside the output grid",
+           122: "checked build: staging / flag slot beyond its capacity",
+           123: "checked build: rank index outside the group",
+           124: "checked build: attention row or statistics slot outside the buffers",
+           125: "checked build: element range malformed",
+           129: "checked build: self-test check failed (as requested)"}
+CHECK_CODES = range(121, 130)
+
+
+class CheckFailed(KernelError):
+    """An index check of the checked kernel build failed; the guarded access was skipped."""
 
 
 def check(status: int, what: str) -> None:
@@ -32,13 +44,19 @@ def check(status: int, what: str) -> None:
 
 
 def cuda_lib() -> ctypes.CDLL:
-    """The sm_100a kernel library; built on first use when nvcc is present."""
+    """The sm_100a kernel library; built on first use when nvcc is present.  With
+    ``TERAPIPE_CHECKED=1`` in the environment the checked build is loaded instead: the same
+    kernels with index checks that report through the status word (see ``build.py``)."""
     global _cuda
     if _cuda is None:
-        if not build.CUDA_LIB.exists() or os.environ.get("TERAPIPE_REBUILD"):
-            build.build_cuda()
-        _cuda = ctypes.CDLL(str(build.CUDA_LIB))
+        checked = os.environ.get("TERAPIPE_CHECKED", "0") == "1"
+        path = build.CUDA_LIB_CHECKED if checked else build.CUDA_LIB
+        if not path.exists() or os.environ.get("TERAPIPE_REBUILD"):
+            build.build_cuda(checked=checked)
+        _cuda = ctypes.CDLL(str(path))
         _declare(_cuda)
+        if bool(_cuda.tp_checked_build()) != checked:
+            raise KernelError(f"{path.name} is not the {'checked' if checked else 'regular'} build")
     return _cuda
 
 
@@ -91,6 +109,8 @@ SIGNATURES = {
     "tp_peer_sum": [P, I, P, I, I, P],
     "tp_attn_fwd": [I, I, P, I, I, I, I, P, L, P, L, P, P],
     "tp_attn_bwd": [I, I, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
+    "tp_checked_build": [],
+    "tp_checked_selftest": [I, I, P, P],
     "tp_attn_fwd_scaled": [I, I, F, P, I, I, I, I, P, L, P, L, P, P],
     "tp_attn_bwd_scaled": [I, I, F, P, I, I, I, I, I, P, L, P, L, P, L, P, P, L, P, P],
 }

@@ -101,8 +101,11 @@ class Trainer:
 
     def _check_code(self, code: int) -> None:
         if code != 0:
-            from ..ops.lib import CommTimeout
+            from ..ops.lib import CHECK_CODES, CheckFailed, CommTimeout
             self.engine.status.zero_()
+            if code in CHECK_CODES:
+                raise CheckFailed(f"an index check of the checked kernel build failed during the "
+                                  f"step (code {code})")
             raise CommTimeout(f"a device-side wait timed out during the step (code {code}): "
                               "a peer did not reach the same kernel within the wait limit")
 

@@ -47,3 +47,18 @@ def test_every_entry_point_is_declared_with_the_right_arguments():
         assert have == want, f"{name} ({src}): table {have}, source {want}"
     for name in lib.SIGNATURES:
         assert name in entries, f"{name} is in the table but not defined in csrc/*.cu"
+
+
+def test_regular_and_checked_builds_export_the_same_entry_points():
+    """The checked library (-DTP_CHECKED) is the regular one plus index checks: both load without
+    a GPU, say which build they are, and export every entry point of the signature table."""
+    import ctypes
+
+    from terapipe_b200.ops import build
+    from terapipe_b200.ops.lib import SIGNATURES
+    build.build_cuda()
+    build.build_cuda(checked=True)
+    regular, checked = ctypes.CDLL(str(build.CUDA_LIB)), ctypes.CDLL(str(build.CUDA_LIB_CHECKED))
+    assert regular.tp_checked_build() == 0 and checked.tp_checked_build() == 1
+    for name in SIGNATURES:
+        assert hasattr(regular, name) and hasattr(checked, name), name

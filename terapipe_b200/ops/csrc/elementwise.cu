@@ -163,27 +163,57 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
   push_signal(pd);
 }
 
+// Backward geometry: 16 warps per CTA, so a CTA holds 16 / WPR rows at a time (8 rows of 2048
+// columns; one CTA per SM then covers 1184 rows, a whole 1024-row token slice, in one pass).
+template <int WPR> struct LnBwdGeom {
+  static constexpr int kWarps = 16;
+  static constexpr int kRowsPerCta = kWarps / WPR;
+  static constexpr int kThreads = kWarps * 32;
+};
+
+// Sum over the WPR warps of a row group; only those warps meet (named barrier 1 + grp), so the
+// row groups of a CTA run independently.  `red` is [2][kRowsPerCta][WPR] (ping-pong by `slot`).
+template <int WPR>
+__device__ __forceinline__ float group_sum_bwd(float v, float* red, int slot, int grp, int wr, int lane) {
+  v = warp_sum(v);
+  if (WPR == 1) return v;
+  float* r = red + (slot * LnBwdGeom<WPR>::kRowsPerCta + grp) * WPR;
+  if (lane == 0) r[wr] = v;
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(WPR * 32) : "memory");
+  float t = 0.0f;
+#pragma unroll
+  for (int i = 0; i < WPR; ++i) t += r[i];
+  return t;
+}
+
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ dres), g = dy * gamma.
-// Persistent CTAs stride over rows; every lane keeps partial sums of dgamma = sum dy*xhat and
-// dbeta = sum dy for its own columns.  At the end the row groups of a CTA fold their partials
-// in a fixed order through shared memory and the CTA writes one slot of
-// scratch[gridDim.x][2][H]; a second kernel adds the slots into the fp32 gradients.
+// Persistent CTAs stride over rows.  The partial sums of dgamma = sum dy*xhat and dbeta = sum dy
+// live in shared memory, one [2][H] region per row group, each lane adding to its own columns
+// (no conflicts, no synchronisation inside the loop, and no accumulator registers: 512 threads
+// fit).  At the end the regions are added in a fixed order and the CTA writes (or adds to) one
+// slot of scratch[gridDim.x][2][H]; a second kernel adds the slots into the fp32 gradients.
 template <typename T, int NV, int WPR>
-__global__ void __launch_bounds__(LnGeom<WPR>::kThreads)
+__global__ void __launch_bounds__(LnBwdGeom<WPR>::kThreads, 1)
 layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
                      const float* __restrict__ mean, const float* __restrict__ rstd,
                      const T* __restrict__ gamma, const T* __restrict__ dres, const PushDst pd,
                      float* __restrict__ scratch, int rows, int H, int accumulate_slots) {
-  using G = LnGeom<WPR>;
-  extern __shared__ float part_smem[];  // [2][H]
+  using G = LnBwdGeom<WPR>;
+  extern __shared__ __align__(16) float part_smem[];  // [kRowsPerCta][2][H]
   __shared__ float red[2 * 2 * G::kRowsPerCta * WPR + 1];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int grp = warp / WPR, wr = warp % WPR;
-  float pg[NV][8], pb[NV][8];
+  float* my_part = part_smem + static_cast<long long>(grp) * 2 * H;
 #pragma unroll
-  for (int i = 0; i < NV; ++i)
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { pg[i][j] = 0.0f; pb[i][j] = 0.0f; }
+  for (int i = 0; i < NV; ++i) {
+    const int col = ((i * WPR + wr) * 32 + lane) * 8;
+    if (col < H) {
+      const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+      float4* sgam = reinterpret_cast<float4*>(my_part + col);
+      float4* sbet = reinterpret_cast<float4*>(my_part + H + col);
+      sgam[0] = z; sgam[1] = z; sbet[0] = z; sbet[1] = z;
+    }
+  }
   pdl_wait();
   int parity = 0;
   for (long long base = static_cast<long long>(blockIdx.x) * G::kRowsPerCta; base < rows;
@@ -203,19 +233,29 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
         load8(x + row * H + col, xv);
         load8(dy + row * H + col, dyv);
         load8(gamma + col, gam);
+        float4* sgam = reinterpret_cast<float4*>(my_part + col);
+        float4* sbet = reinterpret_cast<float4*>(my_part + H + col);
+        float pg[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
           xh[i][j] = (xv[j] - mu) * rs;
           g[i][j] = dyv[j] * gam[j];
           s1 += g[i][j];
           s2 += g[i][j] * xh[i][j];
-          pg[i][j] += dyv[j] * xh[i][j];
-          pb[i][j] += dyv[j];
+          pg[j] = dyv[j] * xh[i][j];
+        }
+#pragma unroll
+        for (int hlf = 0; hlf < 2; ++hlf) {
+          float4 a = sgam[hlf], c = sbet[hlf];
+          a.x += pg[4 * hlf]; a.y += pg[4 * hlf + 1]; a.z += pg[4 * hlf + 2]; a.w += pg[4 * hlf + 3];
+          c.x += dyv[4 * hlf]; c.y += dyv[4 * hlf + 1]; c.z += dyv[4 * hlf + 2]; c.w += dyv[4 * hlf + 3];
+          sgam[hlf] = a;
+          sbet[hlf] = c;
         }
       }
     }
-    const float m1 = group_sum<WPR>(s1, red, 2 * parity, grp, wr, lane) / H;
-    const float m2 = group_sum<WPR>(s2, red, 2 * parity + 1, grp, wr, lane) / H;
+    const float m1 = group_sum_bwd<WPR>(s1, red, 2 * parity, grp, wr, lane) / H;
+    const float m2 = group_sum_bwd<WPR>(s2, red, 2 * parity + 1, grp, wr, lane) / H;
     if (row_ok) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
@@ -235,37 +275,17 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
       }
     }
   }
-  // fold the row groups of this CTA in a fixed order (16-byte accesses: no bank conflicts),
-  // then add the CTA's sums into its slot of the persistent partial buffer
-#pragma unroll 1
-  for (int gsel = 0; gsel < G::kRowsPerCta; ++gsel) {
-    if (grp == gsel) {
-#pragma unroll
-      for (int i = 0; i < NV; ++i) {
-        const int col = ((i * WPR + wr) * 32 + lane) * 8;
-        if (col < H) {
-          float4* sgam = reinterpret_cast<float4*>(part_smem + col);
-          float4* sbet = reinterpret_cast<float4*>(part_smem + H + col);
-#pragma unroll
-          for (int hlf = 0; hlf < 2; ++hlf) {
-            float4 a = make_float4(pg[i][4 * hlf], pg[i][4 * hlf + 1], pg[i][4 * hlf + 2], pg[i][4 * hlf + 3]);
-            float4 c = make_float4(pb[i][4 * hlf], pb[i][4 * hlf + 1], pb[i][4 * hlf + 2], pb[i][4 * hlf + 3]);
-            if (gsel != 0) {
-              const float4 oa = sgam[hlf], oc = sbet[hlf];
-              a.x += oa.x; a.y += oa.y; a.z += oa.z; a.w += oa.w;
-              c.x += oc.x; c.y += oc.y; c.z += oc.z; c.w += oc.w;
-            }
-            sgam[hlf] = a;
-            sbet[hlf] = c;
-          }
-        }
-      }
-    }
-    __syncthreads();
-  }
+  // add the row groups' regions in a fixed order (16-byte accesses), then write the CTA's sums
+  // to (or add them into) its slot of the persistent partial buffer
+  __syncthreads();
   float* sg = scratch + static_cast<long long>(blockIdx.x) * 2 * H;
   for (int c = threadIdx.x * 4; c < 2 * H; c += blockDim.x * 4) {
     float4 v = *reinterpret_cast<const float4*>(part_smem + c);
+#pragma unroll
+    for (int gsel = 1; gsel < G::kRowsPerCta; ++gsel) {
+      const float4 o = *reinterpret_cast<const float4*>(part_smem + static_cast<long long>(gsel) * 2 * H + c);
+      v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
+    }
     if (accumulate_slots) {
       const float4 o = __ldcg(reinterpret_cast<const float4*>(sg + c));
       v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
@@ -510,12 +530,12 @@ template <typename K> static void ln_allow_smem(K kern) {
   const void* key = reinterpret_cast<const void*>(kern);
   for (int i = 0; i < n_seen; ++i)
     if (seen[i] == key) return;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 2 * 16384 * 4);
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
   if (n_seen < 64) seen[n_seen++] = key;
 }
 
 static int ln_parts(int rows, int wpr) {
-  const int rpc = wpr >= 8 ? 1 : 8 / wpr;
+  const int rpc = 16 / wpr;   // LnBwdGeom<WPR>::kRowsPerCta
   int parts = (rows + rpc - 1) / rpc;
   const int cap = tp_layernorm_bwd_parts(rows);
   return parts > cap ? cap : parts;
@@ -532,12 +552,13 @@ static int layernorm_bwd_launch(int dtype, const void* dy, const void* x, const 
   int nv, wpr;
   if (!ln_geometry(H, &nv, &wpr)) return kErrBadArgument;
   const int parts = ln_parts(rows, wpr);
-  const size_t smem = static_cast<size_t>(2) * H * sizeof(float);
+  // one [2][H] fp32 region per row group of the CTA: at most 128 KB (H <= 1024 * WPR)
+  const size_t smem = static_cast<size_t>(16 / wpr) * 2 * H * sizeof(float);
 #define LN_BWD(T, NV, WPR)                                                                      \
   {                                                                                             \
     auto kern = layernorm_bwd_kernel<T, NV, WPR>;                                               \
     if (smem > 40 * 1024) ln_allow_smem(kern); /* dynamic + static must stay under 48 KB */    \
-    launch_pdl(kern, dim3(parts), dim3(LnGeom<WPR>::kThreads), smem, s, 1,                      \
+    launch_pdl(kern, dim3(parts), dim3(LnBwdGeom<WPR>::kThreads), smem, s, 1,                   \
                static_cast<const T*>(dy), static_cast<const T*>(x), mean, rstd,                 \
                static_cast<const T*>(gamma), static_cast<const T*>(dres), pd, scratch,           \
                rows, H, mode);                                                                  \

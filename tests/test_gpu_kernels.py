@@ -88,11 +88,14 @@ def test_gemm_activation_epilogues(act):
     F.check_device_status()
 
 
-@pytest.mark.parametrize("H", [256, 2048, 5120, 6144, 12288])  # 6144: 48 KB of dynamic shared memory + static
-def test_layernorm_fwd_bwd(H):
+# 6144: 48 KB of dynamic shared memory + static in the forward; 3000 x 2048 and 1500 x 5120: several
+# passes of the persistent backward CTAs; 77 x 1024: one warp per row, fewer rows than a CTA holds
+@pytest.mark.parametrize("rows,H", [(520, 256), (520, 2048), (520, 5120), (520, 6144), (520, 12288),
+                                    (3000, 2048), (1500, 5120), (77, 1024), (5, 2048)])
+def test_layernorm_fwd_bwd(rows, H):
     from terapipe_b200.ops import functional as F
     torch.manual_seed(4)
-    rows, dtype = 520, torch.float16
+    dtype = torch.float16
     x = torch.randn(rows, H, device="cuda", dtype=dtype)
     g = (1 + 0.1 * torch.randn(H, device="cuda")).to(dtype)
     b = (0.1 * torch.randn(H, device="cuda")).to(dtype)

@@ -60,8 +60,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return red[32];
 }
 
-template <typename T> __device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
-  const uint4 u = *reinterpret_cast<const uint4*>(p);
+template <typename T> __device__ __forceinline__ void unpack8(const uint4& u, float (&f)[8]) {
   const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
@@ -69,6 +68,9 @@ template <typename T> __device__ __forceinline__ void load8(const T* p, float (&
     f[2 * j] = t.x;
     f[2 * j + 1] = t.y;
   }
+}
+template <typename T> __device__ __forceinline__ void load8(const T* p, float (&f)[8]) {
+  unpack8<T>(*reinterpret_cast<const uint4*>(p), f);
 }
 template <typename T> __device__ __forceinline__ void store8(T* p, const float (&f)[8]) {
   uint4 u;
@@ -89,14 +91,16 @@ template <int WPR> struct LnGeom {
   static constexpr int kThreads = kWarps * 32;
 };
 
-// Sum over the WPR warps of a row group; `red` is [2][kRowsPerCta][WPR] (ping-pong by `slot`).
-template <int WPR>
-__device__ __forceinline__ float group_sum(float v, float* red, int slot, int grp, int wr, int lane) {
+// Sum over the WPR warps of a row group; `red` is [slots][RPC][WPR] (ping-pong by `slot`).  Only
+// the warps of the group meet (named barrier 1 + grp), so the row groups of a CTA run
+// independently.  RPC = row groups per CTA (at most 15 named barriers are free).
+template <int WPR, int RPC>
+__device__ __forceinline__ float group_sum_named(float v, float* red, int slot, int grp, int wr, int lane) {
   v = warp_sum(v);
   if (WPR == 1) return v;
-  float* r = red + (slot * LnGeom<WPR>::kRowsPerCta + grp) * WPR;
+  float* r = red + (slot * RPC + grp) * WPR;
   if (lane == 0) r[wr] = v;
-  __syncthreads();
+  asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(WPR * 32) : "memory");
   float t = 0.0f;
 #pragma unroll
   for (int i = 0; i < WPR; ++i) t += r[i];
@@ -116,19 +120,24 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
   const long long row = static_cast<long long>(blockIdx.x) * G::kRowsPerCta + grp;
   const bool row_ok = row < rows;
   float v[NV][8];
+  uint4 gq[NV], bq[NV];   // gamma / beta of this lane's columns, fetched with the row (16-bit, packed)
   float s = 0.0f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int col = ((i * WPR + wr) * 32 + lane) * 8;
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[i][j] = 0.0f;
+    gq[i] = make_uint4(0, 0, 0, 0);
+    bq[i] = make_uint4(0, 0, 0, 0);
     if (row_ok && col < H) {
       load8(x + row * H + col, v[i]);
+      gq[i] = *reinterpret_cast<const uint4*>(gamma + col);
+      bq[i] = *reinterpret_cast<const uint4*>(beta + col);
 #pragma unroll
       for (int j = 0; j < 8; ++j) s += v[i][j];
     }
   }
-  const float mean = group_sum<WPR>(s, red, 0, grp, wr, lane) / H;
+  const float mean = group_sum_named<WPR, G::kRowsPerCta>(s, red, 0, grp, wr, lane) / H;
   float q = 0.0f;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -141,7 +150,7 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
       }
     }
   }
-  const float rstd = rsqrtf(group_sum<WPR>(q, red, 1, grp, wr, lane) / H + eps);
+  const float rstd = rsqrtf(group_sum_named<WPR, G::kRowsPerCta>(q, red, 1, grp, wr, lane) / H + eps);
   if (row_ok) {
     if (wr == 0 && lane == 0) {
       mean_out[row] = mean;
@@ -152,8 +161,8 @@ layernorm_fwd_kernel(const T* __restrict__ x, const T* __restrict__ gamma,
       const int col = ((i * WPR + wr) * 32 + lane) * 8;
       if (col < H) {
         float g[8], b[8], o[8];
-        load8(gamma + col, g);
-        load8(beta + col, b);
+        unpack8<T>(gq[i], g);
+        unpack8<T>(bq[i], b);
 #pragma unroll
         for (int j = 0; j < 8; ++j) o[j] = (v[i][j] - mean) * rstd * g[j] + b[j];
         for (int d = 0; d < pd.n; ++d) store8(static_cast<T*>(pd.dst[d]) + row * H + col, o);
@@ -171,26 +180,12 @@ template <int WPR> struct LnBwdGeom {
   static constexpr int kThreads = kWarps * 32;
 };
 
-// Sum over the WPR warps of a row group; only those warps meet (named barrier 1 + grp), so the
-// row groups of a CTA run independently.  `red` is [2][kRowsPerCta][WPR] (ping-pong by `slot`).
-template <int WPR>
-__device__ __forceinline__ float group_sum_bwd(float v, float* red, int slot, int grp, int wr, int lane) {
-  v = warp_sum(v);
-  if (WPR == 1) return v;
-  float* r = red + (slot * LnBwdGeom<WPR>::kRowsPerCta + grp) * WPR;
-  if (lane == 0) r[wr] = v;
-  asm volatile("bar.sync %0, %1;" ::"r"(1 + grp), "r"(WPR * 32) : "memory");
-  float t = 0.0f;
-#pragma unroll
-  for (int i = 0; i < WPR; ++i) t += r[i];
-  return t;
-}
-
 // dx = rstd * (g - mean(g) - xhat * mean(g * xhat)) (+ dres), g = dy * gamma.
 // Persistent CTAs stride over rows.  The partial sums of dgamma = sum dy*xhat and dbeta = sum dy
 // live in shared memory, one [2][H] region per row group, each lane adding to its own columns
-// (no conflicts, no synchronisation inside the loop, and no accumulator registers: 512 threads
-// fit).  At the end the regions are added in a fixed order and the CTA writes (or adds to) one
+// (no synchronisation inside the loop, and no accumulator registers: 512 threads fit).  Inside a
+// region the two 16-byte halves of a lane's 8 columns lie in two planes, [array][half][H / 8][4],
+// so that neighbouring lanes touch neighbouring 16 bytes (no bank conflicts).  At the end the regions are added in a fixed order and the CTA writes (or adds to) one
 // slot of scratch[gridDim.x][2][H]; a second kernel adds the slots into the fp32 gradients.
 template <typename T, int NV, int WPR>
 __global__ void __launch_bounds__(LnBwdGeom<WPR>::kThreads, 1)
@@ -209,9 +204,9 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
     const int col = ((i * WPR + wr) * 32 + lane) * 8;
     if (col < H) {
       const float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-      float4* sgam = reinterpret_cast<float4*>(my_part + col);
-      float4* sbet = reinterpret_cast<float4*>(my_part + H + col);
-      sgam[0] = z; sgam[1] = z; sbet[0] = z; sbet[1] = z;
+      float4* sgam = reinterpret_cast<float4*>(my_part + (col >> 1));
+      float4* sbet = reinterpret_cast<float4*>(my_part + H + (col >> 1));
+      sgam[0] = z; sgam[H >> 3] = z; sbet[0] = z; sbet[H >> 3] = z;
     }
   }
   pdl_wait();
@@ -233,8 +228,8 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
         load8(x + row * H + col, xv);
         load8(dy + row * H + col, dyv);
         load8(gamma + col, gam);
-        float4* sgam = reinterpret_cast<float4*>(my_part + col);
-        float4* sbet = reinterpret_cast<float4*>(my_part + H + col);
+        float4* sgam = reinterpret_cast<float4*>(my_part + (col >> 1));      // half 0; half 1 is
+        float4* sbet = reinterpret_cast<float4*>(my_part + H + (col >> 1));  // H / 2 floats further
         float pg[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -246,16 +241,16 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
         }
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
-          float4 a = sgam[hlf], c = sbet[hlf];
+          float4 a = sgam[hlf * (H >> 3)], c = sbet[hlf * (H >> 3)];
           a.x += pg[4 * hlf]; a.y += pg[4 * hlf + 1]; a.z += pg[4 * hlf + 2]; a.w += pg[4 * hlf + 3];
           c.x += dyv[4 * hlf]; c.y += dyv[4 * hlf + 1]; c.z += dyv[4 * hlf + 2]; c.w += dyv[4 * hlf + 3];
-          sgam[hlf] = a;
-          sbet[hlf] = c;
+          sgam[hlf * (H >> 3)] = a;
+          sbet[hlf * (H >> 3)] = c;
         }
       }
     }
-    const float m1 = group_sum_bwd<WPR>(s1, red, 2 * parity, grp, wr, lane) / H;
-    const float m2 = group_sum_bwd<WPR>(s2, red, 2 * parity + 1, grp, wr, lane) / H;
+    const float m1 = group_sum_named<WPR, G::kRowsPerCta>(s1, red, 2 * parity, grp, wr, lane) / H;
+    const float m2 = group_sum_named<WPR, G::kRowsPerCta>(s2, red, 2 * parity + 1, grp, wr, lane) / H;
     if (row_ok) {
 #pragma unroll
       for (int i = 0; i < NV; ++i) {
@@ -280,10 +275,13 @@ layernorm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ x,
   __syncthreads();
   float* sg = scratch + static_cast<long long>(blockIdx.x) * 2 * H;
   for (int c = threadIdx.x * 4; c < 2 * H; c += blockDim.x * 4) {
-    float4 v = *reinterpret_cast<const float4*>(part_smem + c);
+    // columns [q, q + 4) of array c / H: half (q / 4) & 1 of the 8-column group q / 8
+    const int arr = c >= H ? 1 : 0, q = c - arr * H;
+    const int sidx = arr * H + ((q >> 2) & 1) * (H >> 1) + (q >> 3) * 4;
+    float4 v = *reinterpret_cast<const float4*>(part_smem + sidx);
 #pragma unroll
     for (int gsel = 1; gsel < G::kRowsPerCta; ++gsel) {
-      const float4 o = *reinterpret_cast<const float4*>(part_smem + static_cast<long long>(gsel) * 2 * H + c);
+      const float4 o = *reinterpret_cast<const float4*>(part_smem + static_cast<long long>(gsel) * 2 * H + sidx);
       v.x += o.x; v.y += o.y; v.z += o.z; v.w += o.w;
     }
     if (accumulate_slots) {

@@ -184,3 +184,22 @@ def test_fit_keeps_unmeasured_batches_infeasible_and_context_terms_non_negative(
     assert np.isinf(model.no_content_performance[1]).all() and np.isinf(model.no_content_performance[3]).all()
     assert np.isfinite(model.no_content_performance[2, 1:]).all() and np.isfinite(model.no_content_performance[4, 1:]).all()
     assert (np.asarray(model.context_coef)[1:] >= 0).all()
+
+
+def test_engine_memory_model_counts_padded_heads():
+    """Models whose heads are not 64 or 128 wide run with heads stored 128 wide: the memory model
+    charges QKV, attention output, their gradients and the two attention projections for it."""
+    from terapipe_b200.models import MODEL_CONFIGS
+    from terapipe_b200.planner import memory_model as mm
+    layers, hidden, seq, heads = MODEL_CONFIGS["gpt3-2b"]
+    assert hidden // heads == 80
+    padded = mm.engine_memory_per_gpu("gpt3-2b", 4)
+    # the same model as if its heads were 128 wide natively: a registry entry with 20 heads
+    MODEL_CONFIGS["_gpt3-2b-d128"] = (layers, hidden, seq, hidden // 128)
+    try:
+        native = mm.engine_memory_per_gpu("_gpt3-2b-d128", 4)
+    finally:
+        del MODEL_CONFIGS["_gpt3-2b-d128"]
+    assert padded > native * 1.05
+    # measured on a B200: 89.5 GB in the torch allocator for this configuration
+    assert 80.0 < padded < 100.0

@@ -286,6 +286,8 @@ class OursArm:
         import torch
         import torch.distributed as dist
         self.rank, self.world, self.local = rank, world, local
+        if not torch.cuda.is_available():
+            return "no CUDA device (the engine is sm_100a only)"
         torch.cuda.set_device(local)
         self.device = torch.device("cuda", local)
         if world > 1:
@@ -438,10 +440,11 @@ def main():
     warmup = max(args.warmup, 3)
     arm = make_arm(args)
     why = arm.setup(rank, world, local)
-    if why is not None:                      # the reference arm could not be set up
+    if why is not None:
         if rank == 0:
-            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
-        return
+            print(json.dumps({"impl": arm.name, "unavailable": why}), flush=True)
+        # a reference arm that cannot be set up is a valid outcome; this repository's own arm is not
+        sys.exit(0 if arm.name == "reference" else 1)
 
     out = {"metric": METRIC, "impl": arm.name, "n_gpus": world, "higher_is_better": True,
            "scaling": "strong", "dtype": args.dtype if arm.name == "ours" else "fp16"}

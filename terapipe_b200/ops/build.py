@@ -107,11 +107,13 @@ def build_cuda(force=False, verbose=False, ptxas_info=False, checked=False) -> P
 
 def build_host(force=False, verbose=False) -> Path:
     srcs = sorted((CSRC / "host").glob("*.cpp"))
-    if not force and not _stale(HOST_LIB, srcs):
+    deps = srcs + [CSRC / "tile_order.h"]      # shared with the kernels, walked by the host tests
+    if not force and not _stale(HOST_LIB, deps):
         return HOST_LIB
-    _run(["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-o", str(HOST_LIB), *map(str, srcs)],
-         verbose)
-    HOST_LIB.with_suffix(".stamp").write_text(_digest(srcs))
+    tmp = HOST_LIB.with_suffix(".so.tmp")
+    _run(["g++", "-O3", "-std=c++17", "-fPIC", "-shared", "-o", str(tmp), *map(str, srcs)], verbose)
+    os.replace(tmp, HOST_LIB)
+    HOST_LIB.with_suffix(".stamp").write_text(_digest(deps))
     return HOST_LIB
 
 

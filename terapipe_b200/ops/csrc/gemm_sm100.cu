@@ -34,23 +34,17 @@
 // allocations mapped through CUDA IPC; only ordinary loads and stores touch peer memory.
 #include "common.cuh"
 #include "ptx.cuh"
+#include "tile_order.h"
 
 namespace tp {
 
 struct GemmParams {
   int M, N, K;
   int num_m_tiles, num_tiles;
-  // CTA-pair kernel: tile order.  m_major = 0: consecutive tiles walk down a column of the output
-  // (tile -> m = tile % num_m_tiles), so the CTAs of a wave share few B tiles.  m_major = 1: the
-  // columns are taken in groups of order_group; inside a group the row blocks are split in two
-  // phases: first the `order_split` row blocks starting at m_first (wrapping around) for every
-  // column of the group, then the remaining row blocks for every column, row block fastest in
-  // both.  order_first_only = 1 applies the split to the first group only.  The all-gather
-  // variant puts the row blocks whose operands are local first; the reduce-scatter variant puts
-  // the row blocks this rank owns last, a whole phase after the peers produced their share.
-  // order_pipelined = 1 interleaves the phases of successive groups (A0 A1 B0 A2 B1 ... B_last):
-  // a group's second phase then runs one first phase after its own, while its B tiles are still
-  // in L2.
+  // CTA-pair kernel: tile order (fields and meaning as in TileOrder, tile_order.h).  The
+  // all-gather variant puts the row blocks whose operands are local first; the reduce-scatter
+  // variant puts the row blocks this rank owns last, a whole phase after the peers produced
+  // their share.
   int num_n_tiles, m_major, m_first, order_split, order_group, order_first_only, order_pipelined;
   // All-gather wait (CTA-pair kernel, A stored [M][K]): rows [s * ag_rows, (s + 1) * ag_rows) of A
   // were written into this GPU's memory by rank s; before loading rows of another rank the
@@ -382,54 +376,7 @@ __device__ __forceinline__ void epilogue_chunk(const GemmParams& p, const CUtens
   }
 }
 
-// Output-tile coordinates of the CTA-pair kernel (see GemmParams::m_major).
-__device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int& m_idx, int& n_idx) {
-  if (!p.m_major) {
-    m_idx = tile % p.num_m_tiles;
-    n_idx = tile / p.num_m_tiles;
-    return;
-  }
-  if (p.order_pipelined) {
-    const int G = p.order_group, split = p.order_split, rest = p.num_m_tiles - split;
-    const int ng = (p.num_n_tiles + G - 1) / G;
-    int t = tile, phase = -1, g = 0;
-    const int c0 = min(G, p.num_n_tiles);
-    if (t < split * c0) {
-      phase = 0;
-    } else {
-      t -= split * c0;
-      for (int k = 1; k < ng; ++k) {
-        const int ck = min(G, p.num_n_tiles - k * G);
-        if (t < split * ck) { phase = 0; g = k; break; }
-        t -= split * ck;
-        if (t < rest * G) { phase = 1; g = k - 1; break; }
-        t -= rest * G;
-      }
-      if (phase < 0) { phase = 1; g = ng - 1; }
-    }
-    int j;
-    if (phase == 0) { j = t % split; n_idx = g * G + t / split; }
-    else { j = split + t % rest; n_idx = g * G + t / rest; }
-    m_idx = (j + p.m_first) % p.num_m_tiles;
-    return;
-  }
-  const int per_group = p.num_m_tiles * p.order_group;
-  const int g = tile / per_group, r = tile % per_group;
-  const int cols = min(p.order_group, p.num_n_tiles - g * p.order_group);
-  int j;
-  if (p.order_first_only && g > 0) {
-    j = r % p.num_m_tiles;
-    n_idx = g * p.order_group + r / p.num_m_tiles;
-  } else if (r < p.order_split * cols) {
-    j = r % p.order_split;
-    n_idx = g * p.order_group + r / p.order_split;
-  } else {
-    const int r2 = r - p.order_split * cols, cnt = p.num_m_tiles - p.order_split;
-    j = p.order_split + r2 % cnt;
-    n_idx = g * p.order_group + r2 / cnt;
-  }
-  m_idx = (j + p.m_first) % p.num_m_tiles;
-}
+// (Output-tile coordinates of the CTA-pair kernel: pair_tile_coords in tile_order.h.)
 
 // Epilogue of one warp's 32 rows over `nc` 32-column chunks of an accumulator at TMEM address
 // `t_acc` (lane quarter already applied); the warp takes chunks c_first, c_first + c_step, ...
@@ -1629,15 +1576,8 @@ static int gemm_impl(int dtype, int a_mn, int b_mn, const void* A, long long lda
   if (ag) {
     // the first wave of tiles takes row blocks of this rank only: their operands are local
     // while the peers' rows are still arriving; later tiles use the ordinary order
-    const int own_tiles = (ag->rows_per_rank + BM - 1) / BM;
-    if (own_tiles < p.num_m_tiles) {
-      p.m_major = 1;
-      p.m_first = static_cast<int>((static_cast<long long>(ag->rank) * ag->rows_per_rank) / BM) % p.num_m_tiles;
-      p.order_split = own_tiles;
-      p.order_group = (max_pairs() + own_tiles - 1) / own_tiles;
-      if (p.order_group > p.num_n_tiles) p.order_group = p.num_n_tiles;
-      p.order_first_only = 1;
-    }
+    apply_tile_order(p, ag_tile_order(p.num_m_tiles, p.num_n_tiles, BM, ag->rank, ag->rows_per_rank,
+                                      max_pairs()));
     p.ag_flags = ag->flags; p.ag_epoch_base = ag->epoch_base; p.ag_epoch = ag->epoch;
     p.ag_rows = ag->rows_per_rank; p.ag_rank = ag->rank;
   }
@@ -1778,36 +1718,9 @@ extern "C" int tp_gemm_rs(int dtype, int b_mn, const void* A, long long lda, con
   p.num_tiles = p.num_m_tiles * p.num_n_tiles;
   if (((M + kBM - 1) / kBM) * p.num_n_tiles > max_tiles) return kErrTooLarge;
   // The row blocks of the other ranks first (starting after this rank's rows), this rank's own
-  // row blocks last.
-  p.m_major = 0; p.m_first = 0; p.order_split = 1; p.order_group = 1; p.order_first_only = 0; p.order_pipelined = 0;
-  {
-    const long long first_after = static_cast<long long>(rank + 1) * rows_per_rank;
-    const long long my_end = first_after < M ? first_after : M;
-    const long long my_begin = static_cast<long long>(rank) * rows_per_rank;
-    int own_tiles = my_begin >= M ? 0 : static_cast<int>((my_end + 2 * kBM - 1) / (2 * kBM) - my_begin / (2 * kBM));
-    if (own_tiles > 0 && own_tiles < p.num_m_tiles) {
-      p.m_major = 1;
-      p.m_first = first_after >= M ? 0 : static_cast<int>((first_after + 2 * kBM - 1) / (2 * kBM)) % p.num_m_tiles;
-      p.order_split = p.num_m_tiles - own_tiles;
-      // one group: every row block of the other ranks before any of this rank's, so that a
-      // partial is always consumed at least a wave after the peer produced it (column groups
-      // of one wave measured slower: the last group's two phases share a wave)
-      p.order_group = p.num_n_tiles;
-      // A large weight shard (it does not stay in L2 between the two phases) is walked in column
-      // groups with the phases of successive groups interleaved; the group is sized so that
-      // about 10 us of other tiles lie between a partial's production and its use.
-      if (static_cast<long long>(N) * K * 2 > (48ll << 20)) {
-        const float tile_us = 0.0046f * static_cast<float>(K);
-        int g = static_cast<int>(max_pairs() * 10.0f / (tile_us * p.order_split)) + 1;
-        if (g < 2) g = 2;
-        if (g < p.num_n_tiles) {
-          const int ng = (p.num_n_tiles + g - 1) / g;
-          p.order_group = (p.num_n_tiles + ng - 1) / ng;
-          p.order_pipelined = 1;
-        }
-      }
-    }
-  }
+  // row blocks last (tile_order.h).
+  apply_tile_order(p, rs_tile_order(M, N, K, p.num_m_tiles, p.num_n_tiles, 2 * kBM, rank, rows_per_rank,
+                                    max_pairs()));
   p.ag_flags = nullptr; p.ag_epoch_base = nullptr; p.ag_epoch = 0; p.ag_rows = 1; p.ag_rank = 0;
   CUtensorMap tmA, tmB, tmO;
   if (!make_tmap_2d(&tmA, A, K, M, lda, kBK, kBM, bf16)) return kErrDriver;

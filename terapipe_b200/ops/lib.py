@@ -63,13 +63,16 @@ def cuda_lib() -> ctypes.CDLL:
 def host_lib() -> ctypes.CDLL:
     global _host
     if _host is None:
-        if not build.HOST_LIB.exists():
-            build.build_host()
+        build.build_host()      # no-op when the sources are unchanged
         _host = ctypes.CDLL(str(build.HOST_LIB))
         f = _host.tp_plan_slices
         f.restype = ctypes.c_double
         f.argtypes = [c_void_p, c_longlong, c_longlong, c_longlong, c_longlong, c_longlong,
                       ctypes.c_double, c_void_p, c_void_p, c_void_p]
+        w = _host.tp_tile_order_walk
+        w.restype = c_longlong
+        w.argtypes = [c_int, c_int, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                      c_void_p]
     return _host
 
 

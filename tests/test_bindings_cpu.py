@@ -62,3 +62,55 @@ def test_regular_and_checked_builds_export_the_same_entry_points():
     assert regular.tp_checked_build() == 0 and checked.tp_checked_build() == 1
     for name in SIGNATURES:
         assert hasattr(regular, name) and hasattr(checked, name), name
+
+
+def _walk(kind, M, N, K, rank, rpr, pairs=74, tile_rows=256, tile_cols=128):
+    import ctypes
+
+    from terapipe_b200.ops.lib import host_lib
+    num_m, num_n = -(-M // tile_rows), -(-N // tile_cols)
+    order = (ctypes.c_int * 8)()
+    coords = (ctypes.c_int * (2 * num_m * num_n))()
+    n = host_lib().tp_tile_order_walk(kind, M, N, K, tile_rows, tile_cols, rank, rpr, pairs, order, coords)
+    assert n == num_m * num_n, (kind, M, N, K, rank, rpr, n)      # a bijection onto the tile grid
+    tiles = [(coords[2 * i], coords[2 * i + 1]) for i in range(n)]
+    names = ("num_m_tiles", "num_n_tiles", "m_major", "m_first", "order_split", "order_group",
+             "order_first_only", "order_pipelined")
+    return tiles, dict(zip(names, order))
+
+
+def test_gemm_tile_orders_cover_the_grid_and_respect_ownership():
+    """The tile orders the kernels run (csrc/tile_order.h, compiled here for the host): every
+    order visits every output tile exactly once; all-gather -> GEMM starts with row blocks whose
+    operand rows are local; GEMM -> reduce-scatter produces the other ranks' row blocks of a
+    column before this rank's own, in one group all of them before any of its own."""
+    for M, N, K in [(1024, 5120, 2560), (1024, 5120, 10240), (2048, 7680, 5120), (512, 12288, 6144),
+                    (768, 2560, 5120), (1536, 6144, 24576), (256, 5120, 2560), (4096, 1536, 12288)]:
+        tiles, o = _walk(0, M, N, K, 0, M)
+        assert not o["m_major"] and tiles[1] == ((1, 0) if o["num_m_tiles"] > 1 else (0, 1))
+        for tp in (2, 4, 8):
+            rpr = -(-M // tp)
+            rpr = -(-rpr // 32) * 32
+            for rank in range(tp):
+                lo, hi = rank * rpr, min((rank + 1) * rpr, M)
+                own = {m for m in range(-(-M // 256)) if lo < hi and m * 256 < hi and (m + 1) * 256 > lo}
+                # all-gather -> GEMM
+                tiles, o = _walk(1, M, N, K, rank, rpr)
+                if o["m_major"]:
+                    first_wave = tiles[:o["order_split"] * min(o["order_group"], o["num_n_tiles"])]
+                    assert all(m in own for m, _ in first_wave), (M, N, tp, rank)
+                # GEMM -> reduce-scatter
+                tiles, o = _walk(2, M, N, K, rank, rpr)
+                if not o["m_major"]:
+                    continue
+                pos = {t: i for i, t in enumerate(tiles)}
+                for n in range(o["num_n_tiles"]):
+                    others = [pos[(m, n)] for m in range(o["num_m_tiles"]) if m not in own]
+                    mine = [pos[(m, n)] for m in own]
+                    assert max(others) < min(mine), (M, N, K, tp, rank, n)
+                if not o["order_pipelined"]:
+                    assert max(pos[t] for t in tiles if t[0] not in own) < \
+                        min(pos[t] for t in tiles if t[0] in own)
+                else:
+                    # a column's own blocks follow its group's first phase by one more first phase
+                    assert o["order_group"] < o["num_n_tiles"]

@@ -516,23 +516,47 @@ def main():
         env.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(base_port + 101 + 7 * i),
                    RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(local))
         cmd = [sys.executable, os.path.abspath(__file__), "--child-block", name] + sys.argv[1:]
-        try:
-            res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
-                                 timeout=min(limit, remaining + 120))
-            entry = None
-            for line in res.stdout.splitlines():
-                if line.startswith("{"):
-                    entry = json.loads(line)
-            if entry is None:
-                tail = (res.stderr or "").strip().splitlines()[-3:]
-                entry = {"error": f"child exited with status {res.returncode}", "stderr_tail": tail}
-        except subprocess.TimeoutExpired as e:
-            err = e.stderr.decode(errors="replace") if isinstance(e.stderr, bytes) else (e.stderr or "")
-            entry = {"timed_out": True, "limit_s": limit,
-                     "stderr_tail": [ln[:200] for ln in err.strip().splitlines()[-12:]]}
+        entry = run_block_child(cmd, env, min(limit, remaining + 120), limit)
         if rank == 0:
             out[name] = entry
     emit()
+
+
+def _last_json(text):
+    """The last line of `text` that parses as a JSON object, or None."""
+    if isinstance(text, bytes):
+        text = text.decode(errors="replace")
+    entry = None
+    for line in (text or "").splitlines():
+        if line.startswith("{"):
+            try:
+                entry = json.loads(line)
+            except ValueError:
+                pass
+    return entry
+
+
+def run_block_child(cmd, env, timeout, limit):
+    """Run one further block as a child process and return its entry.  The child prints a JSON
+    line whenever it has something complete (for a tensor-parallel block: after every
+    communication mode), the last one counts; a child that is ended by the time limit or exits
+    with an error after such a line keeps that result, with a note of what happened."""
+    try:
+        res = subprocess.run(cmd, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                             timeout=timeout)
+        entry = _last_json(res.stdout)
+        tail = (res.stderr or "").strip().splitlines()[-3:]
+        if entry is None:
+            entry = {"error": f"child exited with status {res.returncode}", "stderr_tail": tail}
+        elif res.returncode != 0:
+            entry["child_exit_status"] = res.returncode
+            entry["stderr_tail"] = [ln[:200] for ln in tail]
+    except subprocess.TimeoutExpired as e:
+        err = e.stderr.decode(errors="replace") if isinstance(e.stderr, bytes) else (e.stderr or "")
+        entry = _last_json(e.stdout) or {}
+        entry.update({"timed_out": True, "limit_s": limit,
+                      "stderr_tail": [ln[:200] for ln in err.strip().splitlines()[-12:]]})
+    return entry
 
 
 def child_main(args):
@@ -559,17 +583,35 @@ def child_main(args):
         if arm.name == "ours" and spec["tp"] > 1:
             # both fused tensor-parallel forms; the block reports the faster one and lists both
             modes = {}
+
+            def summary():
+                ok = {m: b for m, b in modes.items() if "ms_per_step" in b}
+                best = min(ok, key=lambda m: ok[m]["ms_per_step"])
+                e = dict(ok[best])
+                e["tp_comm_modes"] = {m: ({"ms_per_step": b["ms_per_step"], "tokens_per_s": b["value"],
+                                           "e2e_ms_per_step": (b["e2e"] or {}).get("ms_per_step")}
+                                          if "ms_per_step" in b else b) for m, b in modes.items()}
+                return e
+
+            failed = None
             for mode in ("fused", "sp"):
                 try:
                     modes[mode] = arm.measure(spec, steps, warmup, tp_comm=mode)
                 except ValueError as e:      # raised identically on every rank before any kernel runs
                     modes[mode] = {"skipped": str(e)[:200]}
-            ok = {m: b for m, b in modes.items() if "ms_per_step" in b}
-            best = min(ok, key=lambda m: ok[m]["ms_per_step"])
-            entry = dict(ok[best])
-            entry["tp_comm_modes"] = {m: ({"ms_per_step": b["ms_per_step"], "tokens_per_s": b["value"],
-                                           "e2e_ms_per_step": (b["e2e"] or {}).get("ms_per_step")}
-                                          if "ms_per_step" in b else b) for m, b in modes.items()}
+                except Exception as e:       # noqa: BLE001 - the ranks may be out of step now: stop here
+                    modes[mode] = {"error": f"{type(e).__name__}: {str(e)[:200]}"}
+                    failed = e
+                if rank == 0 and any("ms_per_step" in b for b in modes.values()):
+                    print(json.dumps(summary()), flush=True)     # the parent keeps the last line
+                if failed is not None:
+                    break
+            if failed is not None:
+                if not any("ms_per_step" in b for b in modes.values()):
+                    raise failed
+                sys.stdout.flush()
+                os._exit(3)                  # no collective teardown with ranks that may be elsewhere
+            entry = summary()
         else:
             entry = arm.measure(spec, steps, warmup)
     if rank == 0:

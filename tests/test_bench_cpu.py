@@ -53,3 +53,24 @@ def test_both_arms_fill_the_same_config_keys():
     for k in keys:
         assert f"{k}=" in src_ref, f"reference arm does not fill config key {k}"
         assert f"{k}=" in src_ours, f"our arm does not fill config key {k}"
+
+
+def test_block_child_results_survive_a_late_failure_or_time_limit():
+    """A block's child prints a JSON line after every complete part; the parent keeps the last
+    one when the child later exits with an error or is ended by the time limit."""
+    bench = _bench()
+    env = dict(os.environ)
+    py = sys.executable
+    ok = bench.run_block_child([py, "-c", "print('noise'); print('{\"ms_per_step\": 2.0}'); "
+                                "print('{\"ms_per_step\": 1.0}')"], env, 30, 30)
+    assert ok == {"ms_per_step": 1.0}
+    late = bench.run_block_child([py, "-c", "import sys; print('{\"ms_per_step\": 2.0}', flush=True); "
+                                  "sys.stderr.write('boom\\n'); sys.exit(3)"], env, 30, 30)
+    assert late["ms_per_step"] == 2.0 and late["child_exit_status"] == 3 and late["stderr_tail"] == ["boom"]
+    none = bench.run_block_child([py, "-c", "import sys; sys.exit(2)"], env, 30, 30)
+    assert "error" in none and "ms_per_step" not in none
+    slow = bench.run_block_child([py, "-c", "import time; print('{\"ms_per_step\": 5.0}', flush=True); "
+                                  "time.sleep(60)"], env, 3, 3)
+    assert slow["timed_out"] is True and slow["ms_per_step"] == 5.0 and slow["limit_s"] == 3
+    hung = bench.run_block_child([py, "-c", "import time; time.sleep(60)"], env, 2, 2)
+    assert hung["timed_out"] is True and "ms_per_step" not in hung

@@ -74,3 +74,42 @@ def test_block_child_results_survive_a_late_failure_or_time_limit():
     assert slow["timed_out"] is True and slow["ms_per_step"] == 5.0 and slow["limit_s"] == 3
     hung = bench.run_block_child([py, "-c", "import time; time.sleep(60)"], env, 2, 2)
     assert hung["timed_out"] is True and "ms_per_step" not in hung
+
+
+_FAKE_CHILD = """
+import json, os, sys, types
+sys.argv = ["bench.py", "--child-block", "headline", "--gpus", "1"]
+sys.path.insert(0, {root!r})
+import importlib.util
+spec = importlib.util.spec_from_file_location("bench_module", os.path.join({root!r}, "bench.py"))
+bench = importlib.util.module_from_spec(spec); spec.loader.exec_module(bench)
+
+class Arm:
+    name = "ours"
+    def setup(self, rank, world, local): return None
+    def finish(self): pass
+    def measure(self, spec, steps, warmup, tp_comm=None, **kw):
+        if tp_comm == {fail!r}:
+            raise RuntimeError("peer wait timed out")
+        ms = {{"fused": 3.0, "sp": 2.0}}[tp_comm]
+        return {{"ms_per_step": ms, "value": 1000.0 / ms, "e2e": None, "config": {{"tp_comm": tp_comm}}}}
+
+bench.make_arm = lambda args: Arm()
+bench.child_main(bench.parse_args())
+"""
+
+
+def test_child_block_reports_the_modes_that_completed():
+    """A tensor-parallel block measures two communication modes in one child: both complete ->
+    the faster one is reported with both listed; the second fails -> the first is still there,
+    the failure is listed, and the child ends with a non-zero status."""
+    bench = _bench()
+    env = dict(os.environ, RANK="0", WORLD_SIZE="1", LOCAL_RANK="0")
+    both = bench.run_block_child([sys.executable, "-c", _FAKE_CHILD.format(root=ROOT, fail="none")], env, 60, 60)
+    assert both["ms_per_step"] == 2.0 and both["config"]["tp_comm"] == "sp"
+    assert set(both["tp_comm_modes"]) == {"fused", "sp"} and "child_exit_status" not in both
+    late = bench.run_block_child([sys.executable, "-c", _FAKE_CHILD.format(root=ROOT, fail="sp")], env, 60, 60)
+    assert late["ms_per_step"] == 3.0 and late["child_exit_status"] == 3
+    assert "RuntimeError" in late["tp_comm_modes"]["sp"]["error"]
+    first = bench.run_block_child([sys.executable, "-c", _FAKE_CHILD.format(root=ROOT, fail="fused")], env, 60, 60)
+    assert "error" in first and "ms_per_step" not in first
